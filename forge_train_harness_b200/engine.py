@@ -1,0 +1,375 @@
+"""Training engine: one process per GPU, static forward / manual backward, distributed optimizer.
+
+Public contract (the counterpart of ``TrainLoopConfig`` / ``run_training_loop`` in
+workload/src/training_engine_tensor/train_loop.py:120-167, 1508-2557): build a ``RunConfig``, call
+``run_training_loop(cfg)``; rank 0 prints one ``[LOSS] step= global_loss= grad_norm= time_s=
+mfu_e2e_standard=`` line per step and a ``[PHASE]`` banner.  Per step: zero the flat fp32 gradient,
+run ``grad_accum`` micro-batches (one pinned H2D copy each, CUDA-graph replay of forward + loss +
+backward when enabled), all-reduce the fp64 loss statistics, run the distributed optimizer (gradient
+reduce-scatter / all-reduce, 1/tokens scale, global-norm clip, AdamW on fp32 master, low-precision
+parameter all-gather), log, checkpoint.
+
+Differences from the reference, on purpose: step time is device-timed and the reported MFU divides by
+the MEASURED B200 bf16 peak and uses the max over ranks (the reference uses rank 0 and a hard-coded H100
+peak, train_loop.py:89, 2496-2504); nothing but the once-per-step log read synchronises the host (the
+reference's ``if total_norm > clip`` does, train_loop.py:2444); resume restores the data cursor instead
+of replaying batches (train_loop.py:1489-1505).
+"""
+from __future__ import annotations
+
+import os
+import random
+import sys
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .config.schema import RunConfig
+from .data.sources import BatchStager, Prefetcher, build_source, build_mtp_tensors
+from .models import params as P
+from .models.minicpm4 import ModelChunk
+from .models.store import ParamStore, pipeline_chunks
+from .ops import get_ops, rope_table
+from .optim.distributed import DistributedOptimizer
+from .optim.schedule import compute_lr
+from .parallel.pipeline import PipeLinks, build_schedule
+from .parallel.topology import Topology, build_topology, init_distributed
+from .parallel.tp import TPComm
+from .utils import wire
+from .utils.peaks import load_peaks, mfu_percent
+
+
+def _dtype_of(name: str):
+    return {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[name]
+
+
+class Trainer:
+    def __init__(self, cfg: RunConfig, *, device=None, ops=None, topo: Topology | None = None,
+                 init_mode: str = "reference", capture=None, quiet: bool = False):
+        self.cfg = cfg
+        t, m, par = cfg.train, cfg.model, cfg.parallel
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        self.quiet = quiet
+        geo0 = P.tp_geometry(m, par.tensor_parallel_size, 0)
+        self.topo = topo or build_topology(par.tensor_parallel_size, par.pipeline_parallel_size, geo0.kv_replicas)
+        topo = self.topo
+        self.rank, self.world = topo.rank, topo.world_size
+        self.dtype = _dtype_of(t.dtype)
+        self._seed_all(t.seed)
+        if t.deterministic:
+            os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+            torch.use_deterministic_algorithms(True, warn_only=True)
+        self.ops = ops or get_ops(self.device)
+        self.tpc = TPComm(topo.tp_group, topo.tp, topo.tp_rank, par.sequence_parallel)
+        chunks = pipeline_chunks(m, topo.pp, par.virtual_pipeline_stages, topo.pp_rank)
+        self.store = ParamStore(m, chunks, tp=topo.tp, tp_rank=topo.tp_rank, dp=topo.dp, dtype=self.dtype,
+                                device=self.device, bucket_elems=par.ddp_bucket_elems, pp=topo.pp)
+        self._init_weights(init_mode)
+        self.rope = rope_table(m.max_position_embeddings, m.head_dim, m.rotary_base, self.device)
+        self.capture = capture
+        self.chunks = [ModelChunk(m, self.store, c, self.ops, self.tpc, self.rope,
+                                  capture.module_hook if capture is not None and capture.level >= 2 else None)
+                       for c in chunks]
+        for c in self.chunks:
+            c.recompute = t.recompute
+        fused = None
+        if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 \
+                and os.environ.get("FORGE_FUSED_DP", "1") == "1":
+            from .parallel import fused_dp
+            fused = fused_dp.try_create(self.store, topo)
+        self.opt = DistributedOptimizer(self.store, topo, cfg.optim, self.ops, sharded=par.use_distributed_optimizer,
+                                        sequence_parallel=par.sequence_parallel, fused_backend=fused)
+        self.links = PipeLinks(topo)
+        self.grad_accum = cfg.grad_accum(topo.dp)
+        self.source = build_source(cfg.data, m, t.micro_batch_size, topo.dp_rank, topo.dp, t.seed)
+        self.prefetch = None
+        self.with_mtp = bool(m.mtp_num_layers) and topo.pp == 1
+        self.stager = BatchStager(t.micro_batch_size, m.seq_length, self.device, self.with_mtp)
+        self.step = t.start_step  # completed steps (absolute)
+        self.peaks = load_peaks()
+        self.flops_per_token = m.flops_per_token(self.with_mtp)
+        self._graph = None
+        self._graph_stats = None
+        self._graph_failed = False
+        self.stats = torch.zeros(4, dtype=torch.float64, device=self.device)
+        self.launch_count = 0
+        self.last = {}
+
+    # ------------------------------------------------------------------
+    def _seed_all(self, seed: int):
+        random.seed(seed)
+        np.random.seed(seed % (2 ** 32))
+        torch.manual_seed(seed)
+        if torch.cuda.is_available():
+            torch.cuda.manual_seed_all(seed)
+
+    def _init_weights(self, init_mode: str):
+        t = self.cfg.train
+        root = self.cfg.ckpt.checkpoint_root
+        canon = os.path.join(root, "canonical_state_fp32.pt") if root else ""
+        if canon and os.path.isfile(canon):
+            self.store.load_canonical_state(torch.load(canon, map_location="cpu", weights_only=True))
+        elif init_mode == "device":
+            self.store.init_device(t.seed, t.forge_init_ones)
+        else:
+            self.store.init_reference(t.seed, t.forge_init_ones)
+
+    def start_data(self):
+        if self.prefetch is None:
+            self.prefetch = Prefetcher(self.source, self.cfg.data.prefetch_size,
+                                       enabled=self.cfg.data.prefetch_size > 0)
+
+    # ------------------------------------------------------------------
+    def _mb_stats(self, out: dict, batch: dict):
+        nll = out["nll"]
+        s = torch.zeros(4, dtype=torch.float64, device=self.device)
+        s[0] = nll.sum(dtype=torch.float64)
+        s[1] = batch["mask"].sum(dtype=torch.float64)
+        if "mtp_nll" in out:
+            s[2] = out["mtp_nll"].sum(dtype=torch.float64)
+            s[3] = batch["mtp_mask"].sum(dtype=torch.float64)
+        return s
+
+    def _fwd_bwd(self, batch: dict):
+        """One micro-batch through the single local chunk (no pipeline).  Returns fp64[4] stats."""
+        ch = self.chunks[0]
+        out, cache = ch.forward(batch)
+        if self.capture is not None:
+            self.capture.per_token_loss(out["nll"], self.cfg.train.micro_batch_size)
+        stats = self._mb_stats(out, batch)
+        ch.backward(batch, cache)
+        return stats
+
+    def _try_capture_graph(self, batch: dict):
+        """Capture forward + loss + backward of ONE micro-batch (train_loop.py:1926-2125)."""
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._fwd_bwd(batch)  # warm-up: allocator, lazy handles
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.store.zero_grad()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._graph_stats = self._fwd_bwd(batch)
+            self._graph = g
+        except Exception as e:  # fall back to eager, as the reference does
+            self._graph, self._graph_failed = None, True
+            if not self.quiet and self.rank == 0:
+                print(f"[debug] CUDA graph capture failed, running eager: {e}", file=sys.stderr, flush=True)
+            torch.cuda.synchronize()
+            self.store.zero_grad()
+
+    def _use_graph(self) -> bool:
+        t = self.cfg.train
+        return (t.cuda_graph and self.device.type == "cuda" and self.topo.pp == 1 and self.topo.tp == 1
+                and self.capture is None and not self._graph_failed)
+
+    # ------------------------------------------------------------------
+    def _run_microbatches_nopp(self):
+        for mb in range(self.grad_accum):
+            if self.capture is not None:
+                self.capture.begin_microbatch(mb)
+            batch = self.stager.stage(self.prefetch.get())
+            if self._use_graph():
+                if self._graph is None:
+                    self._try_capture_graph(batch)
+                if self._graph is not None:
+                    self._graph.replay()
+                    self.stats += self._graph_stats
+                    continue
+            self.stats += self._fwd_bwd(batch)
+
+    def _run_microbatches_pp(self):
+        topo, t, m = self.topo, self.cfg.train, self.cfg.model
+        n_mb = self.grad_accum
+        batches = []
+        for _ in range(n_mb):
+            b = self.prefetch.get()
+            d = {"ids": b["tokens"].reshape(-1).to(torch.int32).to(self.device, non_blocking=True),
+                 "labels": b["labels"].reshape(-1).to(torch.int32).to(self.device, non_blocking=True),
+                 "mask": b["loss_mask"].reshape(-1).to(self.device, non_blocking=True), "seq_len": m.seq_length}
+            batches.append(d)
+        vpp = self.cfg.parallel.virtual_pipeline_stages
+        sched = build_schedule(topo.pp, topo.pp_rank, vpp, n_mb)
+        rows = t.micro_batch_size * m.seq_length
+        if self.tpc.sp:
+            rows //= topo.tp
+        shape = (rows, m.hidden_size)
+        caches = {}
+        for kind, v, i in sched:
+            ch = self.chunks[v]
+            if kind == "F":
+                x_in = None if ch.spec.has_embedding else self.links.recv_act(shape, self.dtype, self.device)
+                out, cache = ch.forward(batches[i], x_in)
+                caches[(v, i)] = cache
+                if ch.spec.has_head:
+                    self.stats += self._mb_stats(out, batches[i])
+                else:
+                    self.links.send_act(out)
+            else:
+                g_out = None if ch.spec.has_head else self.links.recv_grad(shape, self.dtype, self.device)
+                g_in = ch.backward(batches[i], caches.pop((v, i)), g_out)
+                if g_in is not None:
+                    self.links.send_grad(g_in)
+        self.links.drain()
+
+    # ------------------------------------------------------------------
+    def train_step(self) -> dict:
+        """Runs one optimizer step.  Returns device tensors (no host sync): loss, grad_norm, tokens."""
+        topo = self.topo
+        self.start_data()
+        step_abs = self.step + 1
+        if self.capture is not None:
+            self.capture.begin_step(self.step)
+        self.store.zero_grad()
+        self.stats.zero_()
+        if topo.pp == 1:
+            self._run_microbatches_nopp()
+        else:
+            self._run_microbatches_pp()
+        stats = self.stats
+        if topo.world_size > 1:
+            if not (topo.is_last_stage and topo.tp_rank == 0):
+                stats = torch.zeros_like(stats)
+            else:
+                stats = stats.clone()
+            if self.capture is not None:
+                self.capture.loss_scalar("pre", stats)
+            dist.all_reduce(stats)
+        elif self.capture is not None:
+            self.capture.loss_scalar("pre", stats)
+        n_main = torch.clamp(stats[1], min=1.0)
+        inv_tokens = (1.0 / n_main).to(torch.float32)
+        loss = stats[0] / n_main
+        if self.with_mtp:
+            loss = loss + self.cfg.model.mtp_loss_weight * stats[2] / torch.clamp(stats[3], min=1.0)
+        if self.capture is not None:
+            self.capture.grads("pre", self.store)
+        lr = compute_lr(step_abs, self.cfg.optim)
+        norm = self.opt.step(lr, inv_tokens)
+        if self.capture is not None:
+            self.capture.grads("post", self.store, scale=inv_tokens)
+            self.capture.loss_scalar("post", stats)
+        self.step = step_abs
+        self.last = {"loss": loss, "grad_norm": norm, "tokens": stats[1], "lr": lr}
+        return self.last
+
+    # ------------------------------------------------------------------
+    def data_state(self) -> dict:
+        return self.prefetch.state_dict() if self.prefetch is not None else self.source.state_dict()
+
+    def rng_state(self) -> dict:
+        d = {"torch": torch.get_rng_state(), "numpy": np.random.get_state(), "python": random.getstate()}
+        if self.device.type == "cuda":
+            d["cuda"] = torch.cuda.get_rng_state(self.device)
+        return d
+
+    def set_rng_state(self, d: dict):
+        torch.set_rng_state(d["torch"])
+        np.random.set_state(d["numpy"])
+        random.setstate(d["python"])
+        if self.device.type == "cuda" and "cuda" in d:
+            torch.cuda.set_rng_state(d["cuda"], self.device)
+
+    def close(self):
+        if self.prefetch is not None:
+            self.prefetch.stop()
+            self.prefetch = None
+
+
+# ---------------------------------------------------------------------------
+
+def _max_over_ranks(x: float, device) -> float:
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+    return x
+
+
+def run_training_loop(cfg: RunConfig, *, trainer: Trainer | None = None, loss_tag: str | None = None,
+                      teardown: bool = False, out=None) -> list[wire.LossRecord]:
+    """Train ``cfg.train.num_steps`` steps.  Returns the per-step records rank 0 printed."""
+    from .ckpt import manager as ckpt
+    out = out or sys.stdout
+    t0_wall = time.time()
+    created = init_distributed()
+    tr = trainer or Trainer(cfg)
+    t, oc, m = cfg.train, cfg.optim, cfg.model
+    tag = loss_tag or t.loss_tag
+    rank0 = tr.rank == 0
+    if t.resume_from:
+        ckpt.load(tr, t.resume_from, weights_only=t.init_weights_only)
+        if rank0:
+            print(wire.format_resume_startup(time.time() - t0_wall), file=out, flush=True)
+    if rank0:
+        print(wire.format_phase_line(t.phase_name or "train", tr.step, oc.lr, oc.min_lr, oc.lr_warmup_iters,
+                                     oc.lr_decay_iters, oc.lr_wsd_decay_iters, t.init_weights_only,
+                                     cfg.data.data_path or cfg.data.data_loader), file=out, flush=True)
+    cuda = tr.device.type == "cuda"
+    peak = tr.peaks.get("bf16_tflops_sustained", tr.peaks["bf16_tflops"])
+    tokens_per_step = t.micro_batch_size * m.seq_length * tr.grad_accum * tr.topo.dp
+    records = []
+    sink = open(t.metrics_jsonl, "a") if (t.metrics_jsonl and rank0) else None
+    end_step = tr.step + t.num_steps
+    while tr.step < end_step:
+        if cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        tw = time.perf_counter()
+        res = tr.train_step()
+        if cuda:
+            e1.record()
+            e1.synchronize()
+            dt = e0.elapsed_time(e1) / 1e3
+        else:
+            dt = time.perf_counter() - tw
+        dt_max = _max_over_ranks(dt, tr.device)
+        loss, gn = float(res["loss"]), float(res["grad_norm"])
+        mfu = mfu_percent(tr.flops_per_token, tokens_per_step, dt_max, tr.world, peak)
+        rec = wire.LossRecord(tag, tr.step, loss, gn, dt_max, mfu)
+        records.append(rec)
+        if rank0:
+            print(wire.format_loss_line(tr.step, loss, gn, dt_max, mfu, tag,
+                                        tokens_per_sec_per_gpu=tokens_per_step / dt_max / tr.world,
+                                        step_time_max_ranks_s=dt_max), file=out, flush=True)
+            if sink:
+                import json
+                sink.write(json.dumps({"step": tr.step, "loss": loss, "grad_norm": gn, "time_s": dt_max,
+                                       "mfu": mfu, "lr": res["lr"]}) + "\n")
+                sink.flush()
+        if t.save_path and (tr.step == end_step or (t.save_interval and tr.step % t.save_interval == 0)):
+            ckpt.save(tr, t.save_path)
+    if sink:
+        sink.close()
+    if tr.capture is not None:
+        tr.capture.dump()
+    if trainer is None:
+        tr.close()
+    if teardown:
+        ordered_teardown(created)
+    return records
+
+
+def ordered_teardown(destroy_pg: bool = True):
+    """Drain the GPU, barrier, destroy the process group, free cached memory (train_loop.py:2689-2726)."""
+    import gc
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    for _ in range(3):
+        gc.collect()
+    if dist.is_initialized():
+        try:
+            dist.barrier()
+        finally:
+            if destroy_pg:
+                dist.destroy_process_group()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+    print("ALL DONE", flush=True)

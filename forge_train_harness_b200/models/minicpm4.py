@@ -1,0 +1,274 @@
+"""MiniCPM4-architecture decoder as a static op list with a hand-derived backward.
+
+Forward (per layer): RMSNorm -> QKV GEMM -> [per-head q/k RMSNorm] -> RoPE -> causal GQA
+attention -> out-proj GEMM -> residual*depth_scale fused with the FFN RMSNorm -> FC1 GEMM ->
+SwiGLU -> FC2 GEMM -> residual*depth_scale fused with the next layer's attention RMSNorm;
+then final RMSNorm -> LM-head GEMM scaled by 1/width_mult -> fused cross-entropy
+(workload/src/training_engine_tensor/train_loop.py:504-718).  The backward is the reverse
+walk with closed-form gradients and fp32 weight-gradient accumulation into ``main_grad``
+(train_loop.py:778-1110); no autograd is involved.  The optional Eagle/MTP branch follows
+ref/reference/model_pure_mup_mtp.py:287-322, 393-433.  muP: embedding * mup_emb_scale,
+residual branches * mup_depth_scale/sqrt(L), logits / width_mult.
+
+One ``ModelChunk`` is a pipeline model chunk (a run of layers, optionally with the embedding
+and/or the head).  Tensor / sequence parallelism enters only through ``TPComm`` and the local
+geometry, so the same op list serves TP = 1 and TP > 1.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..config.schema import ModelConfig
+from ..parallel.tp import TPComm
+from . import params as P
+from .store import ChunkSpec, ParamStore
+
+
+@dataclass
+class LayerCache:
+    x: torch.Tensor = None  # residual stream entering the layer
+    rstd1: torch.Tensor = None
+    n1f: torch.Tensor = None  # normed input of the QKV GEMM (gathered under SP)
+    qkv_pre: torch.Tensor = None  # only with qk_norm
+    qk_rstd: torch.Tensor = None
+    qkv: torch.Tensor = None  # after RoPE
+    att: torch.Tensor = None
+    lse: torch.Tensor = None
+    h: torch.Tensor = None  # residual stream after attention
+    rstd2: torch.Tensor = None
+    n2f: torch.Tensor = None
+    gu: torch.Tensor = None
+    inter: torch.Tensor = None
+    m: torch.Tensor = None  # FC2 output, pending residual
+
+
+@dataclass
+class ChunkCache:
+    layers: list = field(default_factory=list)
+    ids: torch.Tensor = None
+    x_last: torch.Tensor = None  # input of the final norm
+    rstd_f: torch.Tensor = None
+    nf: torch.Tensor = None  # final-norm output (sharded rows under SP)
+    nff: torch.Tensor = None
+    dlogits: torch.Tensor = None
+    mtp: dict = None
+
+
+class ModelChunk:
+    def __init__(self, cfg: ModelConfig, store: ParamStore, spec: ChunkSpec, ops, tp: TPComm,
+                 rope_table: torch.Tensor, capture=None):
+        self.cfg, self.store, self.spec, self.ops, self.tp = cfg, store, spec, ops, tp
+        self.geo = P.tp_geometry(cfg, tp.size, tp.rank)
+        self.rope = rope_table
+        self.ds = cfg.depth_scale(0)
+        self.ds_mtp = cfg.depth_scale(cfg.mtp_num_layers)
+        self.capture = capture  # optional hook: capture(kind, fqn, tensor)
+        self.recompute = False
+
+    # ------------------------------------------------------------------
+    def _cap(self, kind, fqn, t):
+        if self.capture is not None:
+            self.capture(kind, fqn, t)
+
+    def _embed(self, ids):
+        ops, geo, tp = self.ops, self.geo, self.tp
+        w = self.store.p("tok_embeddings.weight")
+        e = ops.embedding_fwd(ids, w, self.cfg.emb_scale, geo.vocab_start, tp.size > 1)
+        if tp.size > 1:
+            e = tp.row_output_fwd(e)
+        return e
+
+    def _embed_bwd(self, dx, ids):
+        tp = self.tp
+        if tp.size > 1:
+            dx = tp.row_output_bwd(dx)
+        self.ops.embedding_bwd(dx, ids, self.store.g("tok_embeddings.weight"), self.cfg.emb_scale,
+                               self.geo.vocab_start)
+
+    # ------------------------------------------------------------------
+    def _layer_fwd(self, prefix, x, pending, ds, seq_len):
+        """``pending`` is the previous FC2 output still to be added (None at a chunk start)."""
+        ops, st, tp, geo, cfg = self.ops, self.store, self.tp, self.geo, self.cfg
+        c = LayerCache()
+        w_an = st.p(prefix + "attention_norm.weight")
+        if pending is None:
+            n1, c.rstd1 = ops.rmsnorm_fwd(x, w_an, cfg.norm_epsilon)
+        else:
+            x, n1, c.rstd1 = ops.residual_rmsnorm_fwd(x, pending, ds, w_an, cfg.norm_epsilon)
+        c.x = x
+        self._cap("fwd", prefix + "attention_norm", n1)
+        c.n1f = tp.col_input_fwd(n1)
+        qkv = ops.linear_fwd(c.n1f, st.p(prefix + "wqkv.weight"))
+        self._cap("fwd", prefix + "wqkv", qkv)
+        if cfg.qk_norm:
+            c.qkv_pre = qkv
+            qkv, c.qk_rstd = ops.qk_norm_fwd(qkv, st.p(prefix + "q_norm.weight"), st.p(prefix + "k_norm.weight"),
+                                             cfg.norm_epsilon, geo.n_kv_local, geo.g_local, geo.head_dim)
+        ops.rope_fwd_(qkv, self.rope, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
+        c.qkv = qkv
+        c.att, c.lse = ops.attention_fwd(qkv, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
+        a = ops.linear_fwd(c.att, st.p(prefix + "wo.weight"))
+        a = tp.row_output_fwd(a)
+        self._cap("fwd", prefix + "wo", a)
+        c.h, n2, c.rstd2 = ops.residual_rmsnorm_fwd(x, a, ds, st.p(prefix + "ffn_norm.weight"), cfg.norm_epsilon)
+        self._cap("fwd", prefix + "ffn_norm", n2)
+        c.n2f = tp.col_input_fwd(n2)
+        c.gu = ops.linear_fwd(c.n2f, st.p(prefix + "wfc1.weight"))
+        self._cap("fwd", prefix + "wfc1", c.gu)
+        c.inter = ops.swiglu_fwd(c.gu)
+        m = ops.linear_fwd(c.inter, st.p(prefix + "w2.weight"))
+        c.m = tp.row_output_fwd(m)
+        self._cap("fwd", prefix + "w2", c.m)
+        if self.recompute:
+            c.inter = None
+        return c
+
+    def _layer_bwd(self, prefix, c: LayerCache, g_next, ds, seq_len):
+        """``g_next`` = dL/d(h + m*ds).  Returns dL/dx (without the previous layer's pending scale)."""
+        ops, st, tp, geo, cfg = self.ops, self.store, self.tp, self.geo, self.cfg
+        self._cap("bwd", prefix + "w2", g_next)
+        dm = tp.row_output_bwd(g_next)
+        inter = c.inter if c.inter is not None else ops.swiglu_fwd(c.gu)
+        ops.linear_wgrad(dm, inter, st.g(prefix + "w2.weight"), ds)
+        d_inter = ops.linear_dgrad(dm, st.p(prefix + "w2.weight"), ds)
+        d_gu = ops.swiglu_bwd(d_inter, c.gu)
+        ops.linear_wgrad(d_gu, c.n2f, st.g(prefix + "wfc1.weight"))
+        d_n2 = tp.col_input_bwd(ops.linear_dgrad(d_gu, st.p(prefix + "wfc1.weight")))
+        g_h = ops.rmsnorm_bwd(d_n2, c.h, st.p(prefix + "ffn_norm.weight"), c.rstd2,
+                              st.g(prefix + "ffn_norm.weight"), g_next)
+        self._cap("bwd", prefix + "wo", g_h)
+        da = tp.row_output_bwd(g_h)
+        ops.linear_wgrad(da, c.att, st.g(prefix + "wo.weight"), ds)
+        d_att = ops.linear_dgrad(da, st.p(prefix + "wo.weight"), ds)
+        d_qkv = ops.attention_bwd(d_att, c.qkv, c.att, c.lse, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
+        ops.rope_bwd_(d_qkv, self.rope, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
+        if cfg.qk_norm:
+            d_qkv = ops.qk_norm_bwd(d_qkv, c.qkv_pre, c.qk_rstd, st.p(prefix + "q_norm.weight"),
+                                    st.p(prefix + "k_norm.weight"), st.g(prefix + "q_norm.weight"),
+                                    st.g(prefix + "k_norm.weight"), geo.n_kv_local, geo.g_local, geo.head_dim)
+        self._cap("bwd", prefix + "wqkv", d_qkv)
+        ops.linear_wgrad(d_qkv, c.n1f, st.g(prefix + "wqkv.weight"))
+        d_n1 = tp.col_input_bwd(ops.linear_dgrad(d_qkv, st.p(prefix + "wqkv.weight")))
+        g_x = ops.rmsnorm_bwd(d_n1, c.x, st.p(prefix + "attention_norm.weight"), c.rstd1,
+                              st.g(prefix + "attention_norm.weight"), g_h)
+        return g_x
+
+    # ------------------------------------------------------------------
+    def _head_fwd(self, x, pending, ds, labels, mask, grad_scale, norm_name, cache_out: dict):
+        """Final norm -> LM head (alpha = 1/width_mult) -> fused CE.  Returns per-token NLL."""
+        ops, st, tp, geo, cfg = self.ops, self.store, self.tp, self.geo, self.cfg
+        w = st.p(norm_name)
+        if pending is None:
+            nf, rstd = ops.rmsnorm_fwd(x, w, cfg.norm_epsilon)
+        else:
+            x, nf, rstd = ops.residual_rmsnorm_fwd(x, pending, ds, w, cfg.norm_epsilon)
+        nff = tp.col_input_fwd(nf)
+        alpha = 1.0 / cfg.width_mult
+        logits = ops.linear_fwd(nff, st.p(st.head_weight_name()), alpha)
+        self._cap("fwd", "output", logits)
+        nll = ops.cross_entropy_fwd_bwd(logits, labels, mask, grad_scale, geo.vocab_start,
+                                        tp.group if tp.size > 1 else None)
+        cache_out.update(x_last=x, rstd_f=rstd, nf=nf, nff=nff, dlogits=logits)
+        return nll
+
+    def _head_bwd(self, c: dict, norm_name, extra_dnf=None):
+        ops, st, tp, cfg = self.ops, self.store, self.tp, self.cfg
+        alpha = 1.0 / cfg.width_mult
+        wname = st.head_weight_name()
+        ops.linear_wgrad(c["dlogits"], c["nff"], st.g(wname), alpha)
+        d_nf = tp.col_input_bwd(ops.linear_dgrad(c["dlogits"], st.p(wname), alpha))
+        if extra_dnf is not None:
+            d_nf = d_nf + extra_dnf
+        return ops.rmsnorm_bwd(d_nf, c["x_last"], st.p(norm_name), c["rstd_f"], st.g(norm_name), None)
+
+    # ------------------------------------------------------------------
+    def forward(self, batch: dict, x_in: torch.Tensor | None = None):
+        """Returns ``(x_out, cache)``; on a head chunk ``x_out`` is ``{"nll": ..., "mtp_nll": ...}``."""
+        cfg, ops, tp = self.cfg, self.ops, self.tp
+        S = batch["seq_len"]
+        cache = ChunkCache()
+        if self.spec.has_embedding:
+            cache.ids = batch["ids"]
+            x = self._embed(batch["ids"])
+            self._cap("fwd", "tok_embeddings", x)
+        else:
+            x = x_in
+        pending = None
+        for li in self.spec.layers:
+            c = self._layer_fwd(f"layers.{li}.", x, pending, self.ds, S)
+            cache.layers.append(c)
+            x, pending = c.h, c.m
+        if not self.spec.has_head:
+            x_out = ops.residual_add(x, pending, self.ds) if pending is not None else x
+            return x_out, cache
+        hc: dict = {}
+        labels, mask = batch["labels"], batch["mask"]
+        out = {"nll": self._head_fwd(x, pending, self.ds, labels, mask, 1.0, "norm.weight", hc)}
+        cache.x_last, cache.rstd_f, cache.nf, cache.nff, cache.dlogits = (
+            hc["x_last"], hc["rstd_f"], hc["nf"], hc["nff"], hc["dlogits"])
+        if cfg.mtp_num_layers and "mtp_ids" in batch:
+            out["mtp_nll"] = self._mtp_fwd(batch, cache, S)
+        return out, cache
+
+    def backward(self, batch: dict, cache: ChunkCache, g_out: torch.Tensor | None = None):
+        """Accumulates weight gradients; returns dL/dx_in (None on an embedding chunk)."""
+        S = batch["seq_len"]
+        if self.spec.has_head:
+            extra = self._mtp_bwd(batch, cache, S) if cache.mtp is not None else None
+            g = self._head_bwd({"dlogits": cache.dlogits, "nff": cache.nff, "x_last": cache.x_last,
+                                "rstd_f": cache.rstd_f}, "norm.weight", extra)
+            cache.dlogits = None
+        else:
+            g = g_out
+        for li, c in zip(reversed(self.spec.layers), reversed(cache.layers)):
+            g = self._layer_bwd(f"layers.{li}.", c, g, self.ds, S)
+        if self.spec.has_embedding:
+            self._cap("bwd", "tok_embeddings", g)
+            self._embed_bwd(g, cache.ids)
+            return None
+        return g
+
+    # ------------------------------------------------------------------
+    # Eagle / MTP branch (single extra layer, shared embedding and LM head)
+    # ------------------------------------------------------------------
+    def _mtp_fwd(self, batch, cache: ChunkCache, S):
+        cfg, ops, st, tp = self.cfg, self.ops, self.store, self.tp
+        if tp.size > 1:
+            raise NotImplementedError("the MTP branch runs with tensor_parallel_size = 1")
+        m: dict = {}
+        m["ids"] = batch["mtp_ids"]
+        emb = self._embed(m["ids"])
+        m["emb"] = emb
+        a, m["rstd_a"] = ops.rmsnorm_fwd(emb, st.p("mtp.emb_input_layernorm.weight"), cfg.norm_epsilon)
+        m["hn"] = cache.nf
+        b, m["rstd_b"] = ops.rmsnorm_fwd(cache.nf, st.p("mtp.hidden_input_layernorm.weight"), cfg.norm_epsilon)
+        m["cat"] = torch.cat([a, b], dim=-1)
+        h0 = ops.linear_fwd(m["cat"], st.p("mtp.eagle_fc.weight"))
+        m["layer"] = self._layer_fwd("mtp.layer.", h0, None, self.ds_mtp, S)
+        hc: dict = {}
+        w = cfg.mtp_loss_weight
+        nll = self._head_fwd(m["layer"].h, m["layer"].m, self.ds_mtp, batch["mtp_labels"], batch["mtp_mask"],
+                             w, "mtp.final_layernorm.weight", hc)
+        m["head"] = hc
+        cache.mtp = m
+        return nll
+
+    def _mtp_bwd(self, batch, cache: ChunkCache, S):
+        """Returns the MTP branch's gradient w.r.t. the main final-norm output."""
+        cfg, ops, st = self.cfg, self.ops, self.store
+        m = cache.mtp
+        g = self._head_bwd(m["head"], "mtp.final_layernorm.weight")
+        g_h0 = self._layer_bwd("mtp.layer.", m["layer"], g, self.ds_mtp, S)
+        ops.linear_wgrad(g_h0, m["cat"], st.g("mtp.eagle_fc.weight"))
+        d_cat = ops.linear_dgrad(g_h0, st.p("mtp.eagle_fc.weight"))
+        H = cfg.hidden_size
+        d_a, d_b = d_cat[:, :H].contiguous(), d_cat[:, H:].contiguous()
+        d_emb = ops.rmsnorm_bwd(d_a, m["emb"], st.p("mtp.emb_input_layernorm.weight"), m["rstd_a"],
+                                st.g("mtp.emb_input_layernorm.weight"), None)
+        self._embed_bwd(d_emb, m["ids"])
+        d_nf = ops.rmsnorm_bwd(d_b, m["hn"], st.p("mtp.hidden_input_layernorm.weight"), m["rstd_b"],
+                               st.g("mtp.hidden_input_layernorm.weight"), None)
+        cache.mtp = None
+        return d_nf
