@@ -43,7 +43,7 @@ class SyntheticTokens:
     def __init__(self, vocab: int, seq_len: int, micro_batch: int, dp_rank: int, dp_size: int, seed: int = 0):
         self.vocab, self.seq_len, self.mbs, self.dp_rank, self.dp_size, self.seed = \
             vocab, seq_len, micro_batch, dp_rank, dp_size, seed
-        self.cursor = 0  # global micro-batch index (same on every DP rank)
+        self.cursor = 0  # globally consumed samples (same on every DP rank, independent of the DP degree)
 
     def state_dict(self):
         return {"kind": "synthetic", "cursor": self.cursor, "seed": self.seed}
@@ -52,7 +52,7 @@ class SyntheticTokens:
         self.cursor = int(sd["cursor"])
 
     def seek_microbatches(self, n: int):
-        self.cursor = int(n)
+        self.cursor = int(n) * self.mbs * self.dp_size
 
     def _sample(self, idx: int) -> torch.Tensor:
         g = torch.Generator().manual_seed((self.seed * 1_000_003 + idx) & 0x7FFFFFFFFFFFFFFF)
@@ -62,9 +62,9 @@ class SyntheticTokens:
         return self
 
     def __next__(self):
-        base = self.cursor * self.mbs * self.dp_size + self.dp_rank * self.mbs
+        base = self.cursor + self.dp_rank * self.mbs
         w = torch.stack([self._sample(base + b) for b in range(self.mbs)])
-        self.cursor += 1
+        self.cursor += self.mbs * self.dp_size
         return {"tokens": w[:, :-1].contiguous(), "labels": w[:, 1:].contiguous(),
                 "loss_mask": torch.ones(self.mbs, self.seq_len, dtype=torch.float32)}
 

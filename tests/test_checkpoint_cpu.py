@@ -1,0 +1,86 @@
+"""Save -> resume equivalence (bitwise), legacy codec, resharding across TP/PP/DP layouts, crash tolerance."""
+import os
+
+import pytest
+import torch
+
+import forge_train_harness_b200 as fth
+from forge_train_harness_b200.ckpt import manager as ckpt
+from tests._mp import run_ranks
+from tests.test_parallel_cpu import base_cfg
+
+
+def _run(cfg, n):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    return tr, [tuple(float(x) for x in (r["loss"], r["grad_norm"])) for r in (tr.train_step() for _ in range(n))]
+
+
+@pytest.mark.parametrize("fmt", ["megatron_dist", "legacy"])
+def test_resume_bitwise(tmp_path, fmt):
+    cfg = base_cfg(steps=6).replace(ckpt={"format": fmt})
+    tr, full = _run(cfg, 6)
+    tr.close()
+    tr, first = _run(cfg, 3)
+    ckpt.save(tr, str(tmp_path))
+    tr.close()
+    tr2 = fth.Trainer(cfg, device="cpu", quiet=True)
+    assert ckpt.load(tr2, str(tmp_path)) == 3
+    rest = [tuple(float(x) for x in (r["loss"], r["grad_norm"])) for r in (tr2.train_step() for _ in range(3))]
+    tr2.close()
+    assert first + rest == full  # bitwise: identical floats
+
+
+def test_weights_only_load_resets_optimizer(tmp_path):
+    cfg = base_cfg(steps=2)
+    tr, _ = _run(cfg, 2)
+    ckpt.save(tr, str(tmp_path))
+    w = tr.store.flat_param.clone()
+    tr.close()
+    tr2 = fth.Trainer(cfg.replace(train={"seed": 99}), device="cpu", quiet=True)
+    ckpt.load(tr2, str(tmp_path), weights_only=True)
+    assert torch.equal(tr2.store.flat_param, w)
+    assert tr2.step == 0 and tr2.opt.step_count == 0 and float(tr2.opt.m.abs().sum()) == 0.0
+    tr2.close()
+
+
+def test_incomplete_checkpoint_is_ignored(tmp_path):
+    cfg = base_cfg(steps=2)
+    tr, _ = _run(cfg, 2)
+    ckpt.save(tr, str(tmp_path))
+    tr.close()
+    os.makedirs(tmp_path / "iter_0000009.tmp" / "mp_rank_00")  # a writer died mid-save
+    os.makedirs(tmp_path / "iter_0000007")  # no metadata.json -> incomplete
+    (tmp_path / ckpt.TRACKER).write_text("7")  # tracker points at the broken one
+    assert ckpt.latest_iteration(str(tmp_path)) == 2
+
+
+def _save_layout(rank, world, cfg, path, n):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    out = [float(tr.train_step()["loss"]) for _ in range(n)]
+    ckpt.save(tr, path)
+    tr.close()
+    return out
+
+
+def _load_layout(rank, world, cfg, path, n):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    ckpt.load(tr, path)
+    out = [float(tr.train_step()["loss"]) for _ in range(n)]
+    tr.close()
+    return out
+
+
+def test_reshard_tp2pp2_to_dp2_zero_and_single(tmp_path):
+    a = base_cfg(tensor_parallel_size=2, pipeline_parallel_size=2, sequence_parallel=True, gbs=8)
+    full = run_ranks(4, _save_layout, a.replace(train={"num_steps": 5}), str(tmp_path / "full"), 5)[0]
+    first = run_ranks(4, _save_layout, a, str(tmp_path / "ck"), 3)[0]
+    b = base_cfg(use_distributed_optimizer=True, gbs=8, ddp_bucket_elems=20000)
+    rest = run_ranks(2, _load_layout, b, str(tmp_path / "ck"), 2)[0]
+    for x, y in zip(full, first + rest):
+        assert abs(x - y) / abs(x) < 2e-4
+    c = base_cfg(gbs=8)
+    tr = fth.Trainer(c, device="cpu", quiet=True)
+    assert ckpt.load(tr, str(tmp_path / "ck")) == 3
+    l4 = float(tr.train_step()["loss"])
+    tr.close()
+    assert abs(l4 - full[3]) / abs(full[3]) < 2e-4

@@ -1,0 +1,87 @@
+"""gloo multi-rank parity: DP + ZeRO-1, TP (+SP, KV replication), PP (1F1B, interleaved), all vs one process."""
+import pytest
+import torch
+
+import forge_train_harness_b200 as fth
+from tests._mp import run_ranks
+
+
+def base_cfg(steps=3, mbs=2, gbs=4, **par):
+    model = fth.preset("tiny")
+    import dataclasses
+    model = dataclasses.replace(model, seq_length=32, padded_vocab_size=512, num_layers=4, hidden_size=64,
+                                ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=16,
+                                mup_base_hidden_size=32)
+    return fth.RunConfig(model=model, optim=fth.OptimConfig(lr=2e-3, lr_schedule="constant"),
+                         parallel=fth.ParallelConfig(**par),
+                         train=fth.TrainConfig(num_steps=steps, micro_batch_size=mbs, global_batch_size=gbs, seed=3,
+                                               dtype="fp32", cuda_graph=False),
+                         data=fth.DataConfig(prefetch_size=0))
+
+
+def _train(rank, world, cfg):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    out = []
+    for _ in range(cfg.train.num_steps):
+        r = tr.train_step()
+        out.append((float(r["loss"]), float(r["grad_norm"])))
+    tr.close()
+    return out
+
+
+def single(cfg):
+    tr = fth.Trainer(cfg.replace(parallel={"tensor_parallel_size": 1, "pipeline_parallel_size": 1,
+                                           "virtual_pipeline_stages": 1, "sequence_parallel": False,
+                                           "use_distributed_optimizer": False}), device="cpu", quiet=True)
+    out = []
+    for _ in range(cfg.train.num_steps):
+        r = tr.train_step()
+        out.append((float(r["loss"]), float(r["grad_norm"])))
+    tr.close()
+    return out
+
+
+def check(ref, got, tol=2e-4):
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) / abs(l0) < tol, (ref, got)
+        assert abs(g0 - g1) / abs(g0) < 10 * tol, (ref, got)
+
+
+@pytest.mark.parametrize("zero", [False, True])
+def test_dp2(zero):
+    cfg = base_cfg(use_distributed_optimizer=zero, ddp_bucket_elems=20000)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg), res[0])
+    assert res[0] == res[1]
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2(sp):
+    cfg = base_cfg(tensor_parallel_size=2, sequence_parallel=sp)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg), res[0])
+
+
+def test_tp4_kv_replication_sp():
+    cfg = base_cfg(tensor_parallel_size=4, sequence_parallel=True)
+    res = run_ranks(4, _train, cfg)
+    check(single(cfg), res[0])
+
+
+def test_pp2_1f1b():
+    cfg = base_cfg(pipeline_parallel_size=2, gbs=8)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg), res[0])
+
+
+def test_pp2_interleaved():
+    cfg = base_cfg(pipeline_parallel_size=2, virtual_pipeline_stages=2, gbs=8)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg), res[0])
+
+
+def test_tp2_pp2_dp2_sp_zero_interleaved():
+    cfg = base_cfg(tensor_parallel_size=2, pipeline_parallel_size=2, virtual_pipeline_stages=2, sequence_parallel=True,
+                   use_distributed_optimizer=True, gbs=16, ddp_bucket_elems=20000)
+    res = run_ranks(8, _train, cfg)
+    check(single(cfg), res[0])
