@@ -1,0 +1,38 @@
+// C ABI of the sm_100a kernel library (every launcher takes raw device pointers and a stream, returns 0 on
+// success or a negative code for an unsupported shape / failed launch).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int fth_rmsnorm_fwd(const void* x, const void* res, float res_scale, const void* w, void* r_out, void* y, float* rstd,
+                    int M, int H, float eps, float out_scale, cudaStream_t stream);
+int fth_rmsnorm_bwd_blocks(int M, int H);
+int fth_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                    float* dw_partial, float* dw_main_grad, int M, int H, float out_scale, cudaStream_t stream);
+int fth_rope(void* qkv, const float* table, int M, int S, int n_kv, int g, int d, float sign, cudaStream_t stream);
+int fth_swiglu_fwd(const void* gu, void* out, int M, int F, cudaStream_t stream);
+int fth_swiglu_bwd(const void* dinter, const void* gu, void* dgu, int M, int F, cudaStream_t stream);
+int fth_residual_add(const void* h, const void* a, float scale, void* out, size_t n, cudaStream_t stream);
+int fth_embedding_fwd(const int* ids, const void* w, void* out, int M, int H, int vocab_start, int vocab_local, float scale,
+                      cudaStream_t stream);
+int fth_embedding_bwd(const void* dout, const int* ids, float* main_grad, int M, int H, int vocab_start, int vocab_local,
+                      float scale, cudaStream_t stream);
+int fth_cross_entropy(void* logits, const int* labels, const float* mask, float* nll, float* st_max, float* st_sum,
+                      float* st_tgt, const float* lse_in, int M, int V, int vocab_start, float grad_scale, int mode,
+                      cudaStream_t stream);
+int fth_adamw_segments(float* master, float* m, float* v, const float* grad, void* param, int param_is_bf16,
+                       const void* seg_table, int n_segs, float lr, float beta1, float beta2, float eps, float weight_decay,
+                       float bc1, float rsqrt_bc2, const float* grad_scale, cudaStream_t stream);
+int fth_sumsq_blocks(void);
+int fth_sumsq(const float* x, size_t n, double* partial, float* out, cudaStream_t stream);
+int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, long long ldb, int b_mn_major, void* c,
+                  long long ldc, int M, int N, int K, float alpha, int epi, int bn, int max_ctas, int* status,
+                  cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,242 @@
+// Torch bindings: tensors in, raw pointers + the current CUDA stream out to the extern "C" launchers.
+// Output tensors and scratch buffers come from torch's caching allocator (graph-capture safe).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "api.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+
+void need_bf16(const at::Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), n, " must be a contiguous CUDA bf16 tensor");
+}
+void need_f32(const at::Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), n, " must be a contiguous CUDA fp32 tensor");
+}
+void need_i32(const at::Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), n, " must be a contiguous CUDA int32 tensor");
+}
+
+at::Tensor g_status;  // one int per process: first non-zero code a kernel reported
+
+int* status_ptr() {
+  if (!g_status.defined()) g_status = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA));
+  return g_status.data_ptr<int>();
+}
+
+int read_status(bool reset) {
+  if (!g_status.defined()) return 0;
+  int v = g_status.cpu().item<int>();
+  if (reset && v) g_status.zero_();
+  return v;
+}
+
+std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& res, double res_scale,
+                                    const at::Tensor& w, double eps, double out_scale) {
+  need_bf16(x, "x");
+  need_bf16(w, "w");
+  const int M = x.size(0), H = x.size(1);
+  at::Tensor y = at::empty_like(x), rstd = at::empty({M}, x.options().dtype(at::kFloat));
+  at::Tensor r;
+  const void* resp = nullptr;
+  void* rp = nullptr;
+  if (res.has_value()) {
+    need_bf16(*res, "res");
+    r = at::empty_like(x);
+    resp = res->data_ptr();
+    rp = r.data_ptr();
+  }
+  check(fth_rmsnorm_fwd(x.data_ptr(), resp, (float)res_scale, w.data_ptr(), rp, y.data_ptr(), rstd.data_ptr<float>(), M, H,
+                        (float)eps, (float)out_scale, cur_stream()), "rmsnorm_fwd");
+  if (res.has_value()) return {r, y, rstd};
+  return {y, rstd};
+}
+
+at::Tensor rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd,
+                       const c10::optional<at::Tensor>& dres, at::Tensor& dw_main_grad, double out_scale) {
+  need_bf16(dy, "dy");
+  need_bf16(x, "x");
+  need_bf16(w, "w");
+  need_f32(rstd, "rstd");
+  need_f32(dw_main_grad, "dw_main_grad");
+  const int M = x.size(0), H = x.size(1);
+  const int nb = fth_rmsnorm_bwd_blocks(M, H);
+  TORCH_CHECK(nb > 0, "unsupported hidden size for rmsnorm_bwd");
+  at::Tensor dx = at::empty_like(x);
+  at::Tensor partial = at::empty({nb, H}, x.options().dtype(at::kFloat));
+  const void* dr = nullptr;
+  if (dres.has_value()) {
+    need_bf16(*dres, "dres");
+    dr = dres->data_ptr();
+  }
+  check(fth_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(),
+                        partial.data_ptr<float>(), dw_main_grad.data_ptr<float>(), M, H, (float)out_scale, cur_stream()),
+        "rmsnorm_bwd");
+  return dx;
+}
+
+void rope_(at::Tensor& qkv, const at::Tensor& table, int64_t S, int64_t n_kv, int64_t g, int64_t d, double sign) {
+  need_bf16(qkv, "qkv");
+  need_f32(table, "table");
+  TORCH_CHECK(qkv.size(1) == n_kv * (g + 2) * d && table.size(1) == d && table.size(0) >= S, "rope shape mismatch");
+  check(fth_rope(qkv.data_ptr(), table.data_ptr<float>(), (int)qkv.size(0), (int)S, (int)n_kv, (int)g, (int)d, (float)sign,
+                 cur_stream()), "rope");
+}
+
+at::Tensor swiglu_fwd(const at::Tensor& gu) {
+  need_bf16(gu, "gate_up");
+  const int M = gu.size(0), F = gu.size(1) / 2;
+  at::Tensor out = at::empty({M, F}, gu.options());
+  check(fth_swiglu_fwd(gu.data_ptr(), out.data_ptr(), M, F, cur_stream()), "swiglu_fwd");
+  return out;
+}
+
+at::Tensor swiglu_bwd(const at::Tensor& dinter, const at::Tensor& gu) {
+  need_bf16(gu, "gate_up");
+  need_bf16(dinter, "dinter");
+  const int M = gu.size(0), F = gu.size(1) / 2;
+  at::Tensor out = at::empty_like(gu);
+  check(fth_swiglu_bwd(dinter.data_ptr(), gu.data_ptr(), out.data_ptr(), M, F, cur_stream()), "swiglu_bwd");
+  return out;
+}
+
+at::Tensor residual_add(const at::Tensor& h, const at::Tensor& a, double scale) {
+  need_bf16(h, "h");
+  need_bf16(a, "a");
+  at::Tensor out = at::empty_like(h);
+  check(fth_residual_add(h.data_ptr(), a.data_ptr(), (float)scale, out.data_ptr(), (size_t)h.numel(), cur_stream()),
+        "residual_add");
+  return out;
+}
+
+at::Tensor embedding_fwd(const at::Tensor& ids, const at::Tensor& w, double scale, int64_t vocab_start) {
+  need_i32(ids, "ids");
+  need_bf16(w, "weight");
+  const int M = ids.numel(), H = w.size(1);
+  at::Tensor out = at::empty({M, H}, w.options());
+  check(fth_embedding_fwd(ids.data_ptr<int>(), w.data_ptr(), out.data_ptr(), M, H, (int)vocab_start, (int)w.size(0),
+                          (float)scale, cur_stream()), "embedding_fwd");
+  return out;
+}
+
+void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& main_grad, double scale, int64_t vocab_start) {
+  need_bf16(dout, "dout");
+  need_i32(ids, "ids");
+  need_f32(main_grad, "main_grad");
+  check(fth_embedding_bwd(dout.data_ptr(), ids.data_ptr<int>(), main_grad.data_ptr<float>(), (int)ids.numel(),
+                          (int)main_grad.size(1), (int)vocab_start, (int)main_grad.size(0), (float)scale, cur_stream()),
+        "embedding_bwd");
+}
+
+// mode 0: returns nll; logits overwritten with the gradient.
+at::Tensor cross_entropy(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, double grad_scale,
+                         int64_t vocab_start) {
+  need_bf16(logits, "logits");
+  need_i32(labels, "labels");
+  need_f32(mask, "mask");
+  const int M = logits.size(0), V = logits.size(1);
+  at::Tensor nll = at::empty({M}, mask.options());
+  check(fth_cross_entropy(logits.data_ptr(), labels.data_ptr<int>(), mask.data_ptr<float>(), nll.data_ptr<float>(), nullptr,
+                          nullptr, nullptr, nullptr, M, V, (int)vocab_start, (float)grad_scale, 0, cur_stream()),
+        "cross_entropy");
+  return nll;
+}
+
+std::vector<at::Tensor> ce_stats(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, int64_t vocab_start) {
+  need_bf16(logits, "logits");
+  need_i32(labels, "labels");
+  need_f32(mask, "mask");
+  const int M = logits.size(0), V = logits.size(1);
+  at::Tensor mx = at::empty({M}, mask.options()), sm = at::empty({M}, mask.options()), tg = at::empty({M}, mask.options());
+  check(fth_cross_entropy(logits.data_ptr(), labels.data_ptr<int>(), mask.data_ptr<float>(), nullptr, mx.data_ptr<float>(),
+                          sm.data_ptr<float>(), tg.data_ptr<float>(), nullptr, M, V, (int)vocab_start, 1.f, 1, cur_stream()),
+        "ce_stats");
+  return {mx, sm, tg};
+}
+
+void ce_grad(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, const at::Tensor& lse, double grad_scale,
+             int64_t vocab_start) {
+  need_bf16(logits, "logits");
+  need_i32(labels, "labels");
+  need_f32(mask, "mask");
+  need_f32(lse, "lse");
+  check(fth_cross_entropy(logits.data_ptr(), labels.data_ptr<int>(), mask.data_ptr<float>(), nullptr, nullptr, nullptr, nullptr,
+                          lse.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)vocab_start, (float)grad_scale,
+                          2, cur_stream()), "ce_grad");
+}
+
+void adamw_segments(at::Tensor& master, at::Tensor& m, at::Tensor& v, const at::Tensor& grad, at::Tensor& param,
+                    const at::Tensor& table, int64_t n_segs, double lr, double beta1, double beta2, double eps, double wd,
+                    int64_t step, const at::Tensor& grad_scale) {
+  need_f32(master, "master");
+  need_f32(m, "m");
+  need_f32(v, "v");
+  need_f32(grad, "grad");
+  need_f32(grad_scale, "grad_scale");
+  TORCH_CHECK(param.is_cuda() && param.is_contiguous(), "param must be a contiguous CUDA tensor");
+  const bool bf = param.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(bf || param.scalar_type() == at::kFloat, "param must be bf16 or fp32");
+  const double bc1 = 1.0 - std::pow(beta1, (double)step), bc2 = 1.0 - std::pow(beta2, (double)step);
+  check(fth_adamw_segments(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr<float>(),
+                           param.data_ptr(), bf ? 1 : 0, table.data_ptr(), (int)n_segs, (float)lr, (float)beta1, (float)beta2,
+                           (float)eps, (float)wd, (float)bc1, (float)(1.0 / std::sqrt(bc2)), grad_scale.data_ptr<float>(),
+                           cur_stream()), "adamw_segments");
+}
+
+at::Tensor sumsq(const at::Tensor& x) {
+  need_f32(x, "x");
+  at::Tensor partial = at::empty({fth_sumsq_blocks()}, x.options().dtype(at::kDouble));
+  at::Tensor out = at::empty({}, x.options());
+  check(fth_sumsq(x.data_ptr<float>(), (size_t)x.numel(), partial.data_ptr<double>(), out.data_ptr<float>(), cur_stream()),
+        "sumsq");
+  return out;
+}
+
+// C = alpha * A B^T (see gemm_sm100.cu).  `a`/`b` are 2-D bf16 with unit inner stride; `*_mn` says the stored
+// matrix is [K, M|N] instead of [M|N, K].  epi: 0 bf16 store, 1 fp32 accumulate into `c`, 2 fp32 store.
+at::Tensor gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, c10::optional<at::Tensor> c, double alpha,
+                int64_t epi, int64_t bn, int64_t max_ctas) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "bf16 CUDA inputs");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "2-D operands with unit inner stride");
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "reduction dims differ: ", K, " vs ", Kb);
+  at::Tensor out;
+  if (c.has_value()) {
+    out = *c;
+    TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "bad output");
+    TORCH_CHECK(out.scalar_type() == (epi == 0 ? at::kBFloat16 : at::kFloat), "output dtype does not match epilogue");
+  } else {
+    TORCH_CHECK(epi != 1, "accumulating epilogue needs an output tensor");
+    out = at::empty({M, N}, a.options().dtype(epi == 0 ? at::kBFloat16 : at::kFloat));
+  }
+  check(fth_gemm_bf16(a.data_ptr(), a.stride(0), a_mn ? 1 : 0, b.data_ptr(), b.stride(0), b_mn ? 1 : 0, out.data_ptr(),
+                      out.stride(0), (int)M, (int)N, (int)K, (float)alpha, (int)epi, (int)bn, (int)max_ctas, status_ptr(),
+                      cur_stream()), "gemm_bf16");
+  return out;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope_", &rope_);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("residual_add", &residual_add);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("cross_entropy", &cross_entropy);
+  m.def("ce_stats", &ce_stats);
+  m.def("ce_grad", &ce_grad);
+  m.def("adamw_segments", &adamw_segments);
+  m.def("sumsq", &sumsq);
+  m.def("gemm", &gemm);
+  m.def("read_status", &read_status);
+}

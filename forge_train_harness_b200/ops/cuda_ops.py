@@ -1,0 +1,149 @@
+"""``sm100`` op versions: thin Python wrappers over the in-tree sm_100a extension ``_C``.
+
+Importing this module REQUIRES the extension (``forge_train_harness_b200/_C.so``, built by
+``python -m forge_train_harness_b200.csrc.build``); there is no silent fallback.  Tensors are bf16
+activations / weights and fp32 gradients, laid out as ``torch_ops`` documents.
+"""
+from __future__ import annotations
+
+import importlib.util
+import math
+import os
+import struct
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_SO = os.path.join(_PKG, "_C.so")
+
+
+def _load():
+    if not os.path.exists(_SO):
+        from ..csrc.build import build
+        build()
+    spec = importlib.util.spec_from_file_location("forge_train_harness_b200._C", _SO)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_C = _load()
+
+ADAM_CHUNK = 8192  # elements per thread block of the segment AdamW kernel
+
+
+def check_status(reset: bool = True) -> None:
+    """Raise if any kernel reported a bounded wait that gave up (host sync: call after an event sync)."""
+    code = _C.read_status(reset)
+    if code:
+        names = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
+                 3: "accumulator never committed", 4: "accumulator never drained", 5: "peer flag never set", 6: "timeout"}
+        raise RuntimeError(f"sm_100a kernel reported status {code}: {names.get(code, 'unknown')}")
+
+
+class Sm100Ops:
+    name = "sm100"
+
+    # ---- embedding -------------------------------------------------------
+    @staticmethod
+    def embedding_fwd(ids, weight, scale, vocab_start=0, sharded=False):
+        return _C.embedding_fwd(ids, weight, float(scale), int(vocab_start))
+
+    @staticmethod
+    def embedding_bwd(dout, ids, main_grad, scale, vocab_start=0):
+        _C.embedding_bwd(dout, ids, main_grad, float(scale), int(vocab_start))
+
+    # ---- RMSNorm ---------------------------------------------------------
+    @staticmethod
+    def rmsnorm_fwd(x, w, eps, out_scale=1.0):
+        y, rstd = _C.rmsnorm_fwd(x, None, 0.0, w, float(eps), float(out_scale))
+        return y, rstd
+
+    @staticmethod
+    def residual_rmsnorm_fwd(h, a, scale, w, eps, out_scale=1.0):
+        r, y, rstd = _C.rmsnorm_fwd(h, a, float(scale), w, float(eps), float(out_scale))
+        return r, y, rstd
+
+    @staticmethod
+    def residual_add(h, a, scale):
+        return _C.residual_add(h, a, float(scale))
+
+    @staticmethod
+    def rmsnorm_bwd(dy, x, w, rstd, dw_main_grad, dres=None, out_scale=1.0):
+        return _C.rmsnorm_bwd(dy, x, w, rstd, dres, dw_main_grad, float(out_scale))
+
+    # ---- linear: tcgen05 GEMMs --------------------------------------------
+    @staticmethod
+    def linear_fwd(x, w, alpha=1.0):
+        return _C.gemm(x, False, w, False, None, float(alpha), 0, 0, 0)
+
+    @staticmethod
+    def linear_dgrad(dy, w, alpha=1.0):
+        return _C.gemm(dy, False, w, True, None, float(alpha), 0, 0, 0)
+
+    @staticmethod
+    def linear_wgrad(dy, x, main_grad, alpha=1.0):
+        _C.gemm(dy, True, x, True, main_grad, float(alpha), 1, 0, 0)
+
+    # ---- RoPE ---------------------------------------------------------------
+    @staticmethod
+    def rope_fwd_(qkv, table, seq_len, n_kv, g, d):
+        _C.rope_(qkv, table, seq_len, n_kv, g, d, 1.0)
+        return qkv
+
+    @staticmethod
+    def rope_bwd_(dqkv, table, seq_len, n_kv, g, d):
+        _C.rope_(dqkv, table, seq_len, n_kv, g, d, -1.0)
+        return dqkv
+
+    # ---- SwiGLU ---------------------------------------------------------------
+    @staticmethod
+    def swiglu_fwd(gate_up):
+        return _C.swiglu_fwd(gate_up)
+
+    @staticmethod
+    def swiglu_bwd(dinter, gate_up):
+        return _C.swiglu_bwd(dinter, gate_up)
+
+    # ---- cross-entropy -----------------------------------------------------------
+    @staticmethod
+    def cross_entropy_fwd_bwd(logits, labels, mask, grad_scale=1.0, vocab_start=0, tp_group=None):
+        if tp_group is None:
+            return _C.cross_entropy(logits, labels, mask, float(grad_scale), int(vocab_start))
+        import torch.distributed as dist
+        mx, sm, tg = _C.ce_stats(logits, labels, mask, int(vocab_start))
+        gmx = mx.clone()
+        dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=tp_group)
+        st = torch.stack([sm * torch.exp(mx - gmx), tg])
+        dist.all_reduce(st, group=tp_group)
+        lse = gmx + torch.log(st[0])
+        _C.ce_grad(logits, labels, mask, lse, float(grad_scale), int(vocab_start))
+        return (lse - st[1]) * mask
+
+    # ---- optimizer ---------------------------------------------------------------
+    @staticmethod
+    def build_adam_table(segs, device):
+        rows = []
+        for so, fo, n, lr_mult, wd_on in segs:
+            off = 0
+            while off < n:
+                c = min(ADAM_CHUNK, n - off)
+                rows.append(struct.pack("<qqiffi", so + off, fo + off, c, float(lr_mult), 1.0 if wd_on else 0.0, 0))
+                off += c
+        buf = torch.frombuffer(bytearray(b"".join(rows)), dtype=torch.uint8).to(device)
+        return buf, len(rows)
+
+    @staticmethod
+    def adamw_segments(master, m, v, grad_flat, param_flat, segs, lr, beta1, beta2, eps, weight_decay, step,
+                       grad_scale, table=None):
+        if table is None:
+            table = Sm100Ops.build_adam_table(segs, master.device)
+        buf, n = table
+        gs = grad_scale.reshape(1).to(torch.float32)
+        _C.adamw_segments(master, m, v, grad_flat, param_flat, buf, n, float(lr), float(beta1), float(beta2), float(eps),
+                          float(weight_decay), int(step), gs)
+        return table
+
+    @staticmethod
+    def sumsq(x):
+        return _C.sumsq(x.contiguous())

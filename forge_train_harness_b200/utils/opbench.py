@@ -1,0 +1,123 @@
+"""Per-op device timing at production shapes, reported against the measured roofline.
+
+``python -m forge_train_harness_b200.utils.opbench [--model minicpm4_0.5b] [--mbs 4]`` times each sm_100a op with
+CUDA events (warm-up, L2 flushed between iterations by writing a buffer larger than L2) and prints achieved
+TFLOP/s or GB/s and the fraction of the measured peak.  The counterpart of the reference's per-phase CUDA-event
+stub (tools/profile_step.py:113-216), but per kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..config.schema import preset
+from ..ops.torch_ops import rope_table
+from .peaks import load_peaks
+
+
+def timeit(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e-3
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="minicpm4_0.5b")
+    ap.add_argument("--mbs", type=int, default=4)
+    ap.add_argument("--only", default="")
+    ap.add_argument("--json", default="")
+    a = ap.parse_args(argv)
+    from ..ops.cuda_ops import Sm100Ops as ops, _C, check_status
+    cfg = preset(a.model)
+    peaks = load_peaks()
+    pk_f, pk_b = peaks["bf16_tflops"], peaks["hbm_gbs"]
+    M, H, F, V, S = a.mbs * cfg.seq_length, cfg.hidden_size, cfg.ffn_hidden_size, cfg.padded_vocab_size, cfg.seq_length
+    d, nkv, g = cfg.head_dim, cfg.num_query_groups, cfg.q_per_kv
+    dev = "cuda"
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+    r = lambda *s: torch.randn(*s, device=dev, dtype=torch.float32).mul_(0.5).to(torch.bfloat16)
+    rows = []
+
+    def rec(name, t, flops=0.0, bytes_=0.0):
+        row = {"op": name, "ms": t * 1e3}
+        if flops:
+            row["tflops"] = flops / t / 1e12
+            row["frac_of_measured_bf16_peak"] = row["tflops"] / pk_f
+        if bytes_:
+            row["gbs"] = bytes_ / t / 1e9
+            row["frac_of_measured_hbm"] = row["gbs"] / pk_b
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+
+    def want(n):
+        return not a.only or any(k in n for k in a.only.split(","))
+
+    gemms = [("qkv", cfg.qkv_dim, H), ("wo", H, cfg.q_dim), ("fc1", 2 * F, H), ("fc2", H, F), ("lm_head", V, H)]
+    for name, N, K in gemms:
+        if not want("gemm") and not want(name):
+            continue
+        x, w, dy = r(M, K), r(N, K), r(M, N)
+        mg = torch.zeros(N, K, device=dev)
+        fl = 2.0 * M * N * K
+        for bn in (128, 256):
+            rec(f"gemm_fwd_{name}_bn{bn}", timeit(lambda: _C.gemm(x, False, w, False, None, 1.0, 0, bn, 0), flush=flush), fl)
+            rec(f"gemm_dgrad_{name}_bn{bn}", timeit(lambda: _C.gemm(dy, False, w, True, None, 1.0, 0, bn, 0), flush=flush), fl)
+            rec(f"gemm_wgrad_{name}_bn{bn}", timeit(lambda: _C.gemm(dy, True, x, True, mg, 1.0, 1, bn, 0), flush=flush), fl)
+        rec(f"cublas_fwd_{name}", timeit(lambda: x @ w.t(), flush=flush), fl)
+        rec(f"cublas_dgrad_{name}", timeit(lambda: dy @ w, flush=flush), fl)
+        rec(f"cublas_wgrad_{name}", timeit(lambda: dy.t() @ x, flush=flush), fl)
+        del x, w, dy, mg
+    if want("norm"):
+        x, res, w = r(M, H), r(M, H), r(H)
+        rec("rmsnorm_fwd", timeit(lambda: ops.rmsnorm_fwd(x, w, 1e-6), flush=flush), bytes_=2.0 * M * H * 2)
+        rec("residual_rmsnorm_fwd", timeit(lambda: ops.residual_rmsnorm_fwd(x, res, 0.3, w, 1e-6), flush=flush), bytes_=4.0 * M * H * 2)
+        _, rstd = ops.rmsnorm_fwd(x, w, 1e-6)
+        gw = torch.zeros(H, device=dev)
+        rec("rmsnorm_bwd", timeit(lambda: ops.rmsnorm_bwd(res, x, w, rstd, gw, res), flush=flush), bytes_=4.0 * M * H * 2)
+    if want("swiglu"):
+        gu, di = r(M, 2 * F), r(M, F)
+        rec("swiglu_fwd", timeit(lambda: ops.swiglu_fwd(gu), flush=flush), bytes_=3.0 * M * F * 2)
+        rec("swiglu_bwd", timeit(lambda: ops.swiglu_bwd(di, gu), flush=flush), bytes_=5.0 * M * F * 2)
+        del gu, di
+    if want("rope"):
+        qkv, tab = r(M, cfg.qkv_dim), rope_table(S, d, cfg.rotary_base, dev)
+        rec("rope", timeit(lambda: ops.rope_fwd_(qkv, tab, S, nkv, g, d), flush=flush), bytes_=2.0 * M * (cfg.q_dim + cfg.kv_dim) * 2)
+    if want("ce"):
+        lg = r(M, V)
+        lab = torch.randint(0, V, (M,), device=dev, dtype=torch.int32)
+        mk = torch.ones(M, device=dev)
+        rec("cross_entropy_fwd_bwd", timeit(lambda: ops.cross_entropy_fwd_bwd(lg, lab, mk), iters=5, flush=flush), bytes_=2.0 * M * V * 2)
+        del lg
+    if want("attn") and hasattr(ops, "attention_fwd"):
+        qkv = r(M, cfg.qkv_dim)
+        fl = 4.0 * a.mbs * cfg.num_attention_heads * S * S * d / 2  # causal
+        out, lse = ops.attention_fwd(qkv, S, nkv, g, d)
+        rec("attention_fwd", timeit(lambda: ops.attention_fwd(qkv, S, nkv, g, d), flush=flush), fl)
+        if hasattr(ops, "attention_bwd"):
+            do = r(M, cfg.q_dim)
+            rec("attention_bwd", timeit(lambda: ops.attention_bwd(do, qkv, out, lse, S, nkv, g, d), flush=flush), 2.5 * fl)
+    torch.cuda.synchronize()
+    check_status()
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump({"peaks": peaks, "model": a.model, "mbs": a.mbs, "rows": rows}, f, indent=1)
+    return rows
+
+
+if __name__ == "__main__":
+    main()

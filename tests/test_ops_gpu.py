@@ -1,0 +1,149 @@
+"""sm_100a kernels vs the plain-PyTorch fp32 reference of the same op (small and ragged shapes)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from forge_train_harness_b200.ops.cuda_ops import Sm100Ops, check_status
+    yield Sm100Ops
+    torch.cuda.synchronize()
+    check_status()
+
+
+from forge_train_harness_b200.ops.torch_ops import TorchOps as T, rope_table  # noqa: E402
+
+
+def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"max err {err} vs ref max {ref}"
+
+
+@pytest.mark.parametrize("M,H", [(64, 1024), (37, 4096), (16, 256), (130, 1536), (9, 64)])
+def test_rmsnorm(ops, M, H):
+    x, a, w = rnd(M, H), rnd(M, H), rnd(H, scale=0.3) + 1
+    y, rstd = ops.rmsnorm_fwd(x, w, 1e-6, 0.25)
+    y0, rstd0 = T.rmsnorm_fwd(x.float(), w.float(), 1e-6, 0.25)
+    close(y, y0)
+    close(rstd, rstd0, 1e-3, 1e-4)
+    r, y, rstd = ops.residual_rmsnorm_fwd(x, a, 0.3, w, 1e-6)
+    r0, y0, _ = T.residual_rmsnorm_fwd(x, a, 0.3, w, 1e-6)
+    assert torch.equal(r, r0)
+    close(y, y0)
+    dy, dres = rnd(M, H), rnd(M, H)
+    g = torch.zeros(H, device="cuda") + 1.5
+    g0 = g.clone()
+    dx = ops.rmsnorm_bwd(dy, x, w, rstd0.contiguous(), g, dres, 0.5)
+    dx0 = T.rmsnorm_bwd(dy.float(), x.float(), w.float(), rstd0, g0, dres.float(), 0.5)
+    close(dx, dx0)
+    close(g, g0, 1e-3, 1e-2)
+    close(ops.residual_add(x, a, 0.7), T.residual_add(x, a, 0.7))
+
+
+@pytest.mark.parametrize("nkv,g,d,S,B", [(2, 8, 64, 128, 2), (1, 4, 128, 64, 3)])
+def test_rope(ops, nkv, g, d, S, B):
+    tab = rope_table(S, d, 10000.0, "cuda")
+    q = rnd(B * S, nkv * (g + 2) * d)
+    q0 = T.rope_fwd_(q.clone().float(), tab, S, nkv, g, d)
+    ops.rope_fwd_(q, tab, S, nkv, g, d)
+    close(q, q0)
+    ops.rope_bwd_(q, tab, S, nkv, g, d)
+    T.rope_bwd_(q0, tab, S, nkv, g, d)
+    close(q, q0)
+
+
+def test_swiglu(ops):
+    gu, d = rnd(100, 2 * 512), rnd(100, 512)
+    close(ops.swiglu_fwd(gu), T.swiglu_fwd(gu.float()))
+    close(ops.swiglu_bwd(d, gu), T.swiglu_bwd(d.float(), gu.float()))
+
+
+def test_embedding(ops):
+    V, H, M = 1000, 256, 333
+    w = rnd(V, H)
+    ids = torch.randint(0, V, (M,), device="cuda", dtype=torch.int32)
+    close(ops.embedding_fwd(ids, w, 12.0), T.embedding_fwd(ids, w, 12.0))
+    close(ops.embedding_fwd(ids, w[100:600].contiguous(), 12.0, 100, True), T.embedding_fwd(ids, w[100:600], 12.0, 100, True))
+    dout = rnd(M, H)
+    g, g0 = torch.zeros(500, H, device="cuda"), torch.zeros(500, H, device="cuda")
+    ops.embedding_bwd(dout, ids, g, 12.0, 100)
+    T.embedding_bwd(dout, ids, g0, 12.0, 100)
+    close(g, g0, 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("M,V", [(50, 73448), (33, 512), (20, 151936)])
+def test_cross_entropy(ops, M, V):
+    logits = rnd(M, V, scale=3.0)
+    labels = torch.randint(0, V, (M,), device="cuda", dtype=torch.int32)
+    mask = (torch.rand(M, device="cuda") > 0.2).float()
+    l0 = logits.clone().float()
+    nll0 = T.cross_entropy_fwd_bwd(l0, labels, mask, 0.3)
+    nll = ops.cross_entropy_fwd_bwd(logits, labels, mask, 0.3)
+    close(nll, nll0, 1e-3, 2e-2)
+    err = (logits.float() - l0).abs().max().item()
+    assert err < 4e-3, err
+
+
+def test_adamw_and_sumsq(ops):
+    n = 50000
+    master = torch.randn(n, device="cuda")
+    m, v = torch.randn(n, device="cuda") * 0.1, torch.rand(n, device="cuda") * 0.01
+    grad = torch.randn(2 * n, device="cuda")
+    param = torch.zeros(2 * n, device="cuda", dtype=torch.bfloat16)
+    segs = [(0, 256, 20000, 0.25, True), (20000, 30000 + 256, 29999, 1.0, False)]
+    ref = [t.clone() for t in (master, m, v)]
+    pref = torch.zeros(2 * n, device="cuda", dtype=torch.bfloat16)
+    gs = torch.tensor(0.5, device="cuda")
+    T.adamw_segments(*ref, grad, pref, segs, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, gs)
+    ops.adamw_segments(master, m, v, grad, param, segs, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, gs)
+    close(master, ref[0], 1e-5, 1e-5)
+    close(m, ref[1], 1e-5, 1e-5)
+    close(v, ref[2], 1e-5, 1e-6)
+    assert torch.equal(param, pref) or (param.float() - pref.float()).abs().max() < 1e-2
+    x = torch.randn(1234567, device="cuda")
+    close(ops.sumsq(x), T.sumsq(x), 1e-5, 1e-3)
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 1280, 1024), (200, 264, 72), (4096, 1024, 4096), (130, 73448 // 8, 320)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_variants(ops, M, N, K, bn):
+    from forge_train_harness_b200.ops.cuda_ops import _C, check_status
+    K8 = (K + 7) // 8 * 8
+    x, w = rnd(M, K8, scale=0.5), rnd(N, K8, scale=0.5)
+    y = _C.gemm(x, False, w, False, None, 0.5, 0, bn, 0)
+    torch.cuda.synchronize()
+    check_status()
+    close(y, 0.5 * (x.float() @ w.float().t()), 1e-2, 1e-2 * math.sqrt(K8) * 0.25)
+    if N % 8 == 0 and M % 8 == 0:
+        dy = rnd(M, N, scale=0.5)
+        dx = _C.gemm(dy, False, w, True, None, 1.0, 0, bn, 0)
+        close(dx, dy.float() @ w.float(), 1e-2, 1e-2 * math.sqrt(N) * 0.25)
+        g = torch.ones(N, K8, device="cuda")
+        _C.gemm(dy, True, x, True, g, 2.0, 1, bn, 0)
+        close(g, 1.0 + 2.0 * (dy.float().t() @ x.float()), 1e-2, 1e-2 * math.sqrt(M) * 0.25)
+        torch.cuda.synchronize()
+        check_status()
+
+
+def test_gemm_repeated_calls_and_views(ops):
+    """Operands that are strided row views (unit inner stride) and repeated in-place updates."""
+    big = rnd(512, 2048, scale=0.5)
+    x = big[:, 256:256 + 512]
+    w = rnd(384, 512, scale=0.5)
+    for _ in range(3):
+        y = ops.linear_fwd(x, w)
+        close(y, x.float() @ w.float().t(), 1e-2, 0.1)
+        w.mul_(0.9)
