@@ -33,6 +33,9 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
                   long long ldc, int M, int N, int K, float alpha, int epi, int bn, int max_ctas, int* status,
                   cudaStream_t stream);
 
+int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv, int g, int d, int* status,
+                  cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -221,6 +221,18 @@ at::Tensor gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, 
   return out;
 }
 
+// Causal GQA attention on the packed QKV activation.  Returns {out [M, n_kv*g*d] bf16, lse [B, n_kv*g, S] fp32}.
+std::vector<at::Tensor> flash_fwd(const at::Tensor& qkv, int64_t S, int64_t n_kv, int64_t g, int64_t d) {
+  need_bf16(qkv, "qkv");
+  const int64_t M = qkv.size(0), B = M / S;
+  TORCH_CHECK(M % S == 0 && qkv.size(1) == n_kv * (g + 2) * d, "qkv shape mismatch");
+  at::Tensor out = at::empty({M, n_kv * g * d}, qkv.options());
+  at::Tensor lse = at::empty({B, n_kv * g, S}, qkv.options().dtype(at::kFloat));
+  check(fth_flash_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), (int)B, (int)S, (int)n_kv, (int)g, (int)d,
+                      status_ptr(), cur_stream()), "flash_fwd");
+  return {out, lse};
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -238,5 +250,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_segments", &adamw_segments);
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
+  m.def("flash_fwd", &flash_fwd);
   m.def("read_status", &read_status);
 }

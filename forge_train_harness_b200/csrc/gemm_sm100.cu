@@ -36,16 +36,18 @@ struct GemmSmem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kEpiOffset = STAGES * kStageBytes;  // two 128-row x 128-byte staging buffers
+  static constexpr int kEpiBytes = 2 * BM * 128;
+  static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // + barriers + alignment slack
 };
 
 enum EpiMode : int { kEpiBf16 = 0, kEpiF32Accum = 1, kEpiF32Store = 2 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 void* __restrict__ c_ptr, int M, int N, int K, long long ldc, float alpha, int epi_mode,
+                 const __grid_constant__ CUtensorMap tmap_c, int M, int N, int K, float alpha, int accumulate,
                  int group_m, int* __restrict__ status) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
@@ -163,56 +165,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncwarp();
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
+    // TMEM -> registers -> 128B-swizzled shared staging -> TMA store (bf16) or TMA reduce-add (fp32 accumulate).
+    // One chunk is 128 rows x 128 bytes (64 bf16 or 32 fp32 columns); two staging buffers alternate.
     const int q = warp % 4;  // TMEM lane quarter this warp may read
+    const int r_in_tile = q * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    constexpr int CW = OUT_F32 ? 32 : 64;  // columns per chunk
+    unsigned char* stg = smem + S::kEpiOffset;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int buf = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, mb, nb);
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kTimeoutTmemFull)) break;
       tc_fence_after();
-      const int row = mb * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
+      for (int c = 0; c < BN / CW; ++c) {
+        const int col0 = nb * BN + c * CW;
+        if (col0 >= N) break;  // uniform across the epilogue warps
+        uint32_t r[CW];
+        tmem_ld_32x32(taddr + c * CW, r);
+        if constexpr (CW == 64) tmem_ld_32x32(taddr + c * CW + 32, r + 32);
         tmem_wait_ld();
-        const int col0 = nb * BN + c * 32;
-        if (row < M && col0 < N) {
-          if (epi_mode == kEpiBf16) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_ptr) + (size_t)row * ldc + col0;
+        if (issuer) tma_wait_group_read<1>();  // the store that last used this buffer has read it
+        named_barrier_sync(1, 128);
+        unsigned char* row_ptr = stg + buf * (BM * 128) + r_in_tile * 128;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (col0 + v * 8 < N) {  // N % 8 == 0 is checked on the host
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]) * alpha;
-                store8(dst + v * 8, f);
-              }
-            }
+        for (int p8 = 0; p8 < 8; ++p8) {
+          uint4 v;
+          if constexpr (OUT_F32) {
+            v.x = __float_as_uint(__uint_as_float(r[p8 * 4 + 0]) * alpha);
+            v.y = __float_as_uint(__uint_as_float(r[p8 * 4 + 1]) * alpha);
+            v.z = __float_as_uint(__uint_as_float(r[p8 * 4 + 2]) * alpha);
+            v.w = __float_as_uint(__uint_as_float(r[p8 * 4 + 3]) * alpha);
           } else {
-            float* dst = reinterpret_cast<float*>(c_ptr) + (size_t)row * ldc + col0;
+            float f[8];
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              if (col0 + v * 4 < N) {  // N % 4 == 0 is checked on the host
-                float4 o = make_float4(__uint_as_float(r[v * 4]) * alpha, __uint_as_float(r[v * 4 + 1]) * alpha,
-                                       __uint_as_float(r[v * 4 + 2]) * alpha, __uint_as_float(r[v * 4 + 3]) * alpha);
-                if (epi_mode == kEpiF32Accum) {
-                  float4 p = *reinterpret_cast<float4*>(dst + v * 4);
-                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                }
-                *reinterpret_cast<float4*>(dst + v * 4) = o;
-              }
-            }
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p8 * 8 + e]) * alpha;
+            bf16x8 pk = pack8(f);
+            v = *reinterpret_cast<uint4*>(&pk);
           }
+          *reinterpret_cast<uint4*>(row_ptr + ((p8 ^ (r_in_tile & 7)) * 16)) = v;
         }
+        fence_proxy_async();
+        named_barrier_sync(1, 128);
+        if (issuer) {
+          if (OUT_F32 && accumulate) tma_reduce_add_2d(&tmap_c, stg + buf * (BM * 128), col0, mb * BM);
+          else tma_store_2d(&tmap_c, stg + buf * (BM * 128), col0, mb * BM);
+          tma_commit_group();
+        }
+        buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (issuer) tma_wait_group<0>();
   }
 
   // ---------------- teardown ----------------
@@ -248,20 +259,27 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix with `ld` elements between rows; box = [box_rows, 64].
-int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
-                      uint32_t box_cols) {
+// 2-D tensor map over a row-major [rows, cols] matrix with `ld` elements between rows, 128-byte swizzle.
+static int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int esize, const void* ptr, uint64_t rows, uint64_t cols,
+                        uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn enc = get_encode();
   if (enc == nullptr) return -10;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) return -11;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * esize) & 15)) return -11;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
+  cuuint64_t strides[1] = {ld * esize};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -12;
+}
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_cols) {
+  return make_tmap_2d(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, rows, cols, ld, box_rows, box_cols);
+}
+int make_tmap_f32_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     uint32_t box_cols) {
+  return make_tmap_2d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, rows, cols, ld, box_rows, box_cols);
 }
 
 static int sm_count() {
@@ -275,11 +293,11 @@ static int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* c, int M, int N, int K, long long ldc,
-                       float alpha, int epi, int* status, int max_ctas, cudaStream_t stream) {
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int M, int N, int K,
+                       float alpha, int accumulate, int* status, int max_ctas, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -20;
@@ -289,7 +307,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* c, in
   int tiles = m_tiles * n_tiles;
   int grid = tiles < max_ctas ? tiles : max_ctas;
   int group_m = m_tiles < 16 ? m_tiles : 16;
-  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, c, M, N, K, ldc, alpha, epi, group_m, status);
+  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, tc, M, N, K, alpha, accumulate, group_m, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -307,7 +325,7 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
                   long long ldc, int M, int N, int K, float alpha, int epi, int bn, int max_ctas, int* status,
                   cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (epi == kEpiBf16 ? (N % 8 || ldc % 8) : (N % 4 || ldc % 4)) return -2;
+  if (epi == kEpiBf16 ? (ldc % 8) : (ldc % 4)) return -2;
   if (max_ctas <= 0) max_ctas = sm_count();
   if (bn == 0) {
     // fewer, fatter tiles unless that leaves the last wave mostly empty
@@ -325,8 +343,17 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
   if (!b_mn_major) r = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, BK);
   else r = make_tmap_bf16_2d(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
   if (r) return r;
-#define FTH_GEMM_CASE(BN_, ST_, AM_, BM_) \
-  return launch_gemm<BN_, ST_, AM_, BM_>(ta, tb, c, M, N, K, ldc, alpha, epi, status, max_ctas, stream)
+  CUtensorMap tc;
+  const bool f32 = epi != kEpiBf16;
+  if (f32) r = make_tmap_f32_2d(&tc, c, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, BM, 32);
+  else r = make_tmap_bf16_2d(&tc, c, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, BM, 64);
+  if (r) return r;
+  const int accum = epi == kEpiF32Accum ? 1 : 0;
+#define FTH_GEMM_CASE(BN_, ST_, AM_, BM_)                                                                             \
+  do {                                                                                                                \
+    if (f32) return launch_gemm<BN_, ST_, AM_, BM_, true>(ta, tb, tc, M, N, K, alpha, accum, status, max_ctas, stream); \
+    return launch_gemm<BN_, ST_, AM_, BM_, false>(ta, tb, tc, M, N, K, alpha, accum, status, max_ctas, stream);         \
+  } while (0)
   if (bn == 256) {
     if (!a_mn_major && !b_mn_major) FTH_GEMM_CASE(256, 4, false, false);
     if (!a_mn_major && b_mn_major) FTH_GEMM_CASE(256, 4, false, true);

@@ -96,6 +96,19 @@ class Sm100Ops:
         _C.rope_(dqkv, table, seq_len, n_kv, g, d, -1.0)
         return dqkv
 
+    # ---- attention -----------------------------------------------------------
+    @staticmethod
+    def attention_supported(seq_len, d):
+        return seq_len % 128 == 0 and d in (64, 128)
+
+    @staticmethod
+    def attention_fwd(qkv, seq_len, n_kv, g, d):
+        if not Sm100Ops.attention_supported(seq_len, d):
+            from .torch_ops import TorchOps
+            return TorchOps.attention_fwd(qkv, seq_len, n_kv, g, d)
+        out, lse = _C.flash_fwd(qkv, seq_len, n_kv, g, d)
+        return out, lse
+
     # ---- SwiGLU ---------------------------------------------------------------
     @staticmethod
     def swiglu_fwd(gate_up):
