@@ -36,6 +36,10 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
 int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv, int g, int d, int* status,
                   cudaStream_t stream);
 
+size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d);
+int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const float* lse, void* dqkv, void* scratch_f32,
+                  int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

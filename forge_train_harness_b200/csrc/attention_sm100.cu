@@ -294,6 +294,346 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __rest
   if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+
+// =====================================================================================================================
+// Backward.
+//
+// Pre-pass (flash_bwd_prep_kernel): delta[b,h,s] = sum_d dO*O and lse2 = lse*log2(e), one warp per (row, head).
+// Main kernel: one CTA per (batch, query head, 128-key block n).  K and V tiles stay resident in shared memory; the CTA
+// walks the query blocks m >= n.  Per step, with every product on tcgen05 and every accumulator in tensor memory:
+//     S^T  = K Q^T          (128 keys x 128 queries)            SS-MMA
+//     dP^T = V dO^T                                              SS-MMA
+//     P^T  = exp2(S^T*c - lse2[q]),  dS^T = P^T (dP^T - delta[q]) * scale      (one thread per key row)
+//     dV  += P^T dO          A = P^T from tensor memory          TS-MMA   (dO tile reused as an MN-major B operand)
+//     dK  += dS^T Q          A = dS^T from tensor memory         TS-MMA   (Q tile reused as an MN-major B operand)
+//     dQ   = dS K            A = dS^T from shared memory as an MN-major operand, B = K tile MN-major
+// Working on the transposed score tile means no operand ever needs a transposing copy: thread r owns key row r of
+// S^T / dP^T, so P^T and dS^T are produced directly in the lane layout tcgen05 wants for an A operand.  dQ tiles are
+// summed across the key blocks by TMA reduce-add into an fp32 image of the packed dQKV activation; dK / dV (summed over
+// the query heads of a KV group, i.e. over CTAs) use the same path.  A finalize kernel rounds that image to bf16.
+// =====================================================================================================================
+
+constexpr int kBwdThreads = 192;  // warps 0-3 compute (one key row per thread), warp 4 TMA, warp 5 MMA
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kTile = 128 * D * 2;                       // 128 x D bf16
+  static constexpr int kStages = (D == 64) ? 2 : 1;               // Q + dO ring
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kTile;
+  static constexpr int kQdOOff = 2 * kTile;                       // per stage: Q tile, dO tile
+  static constexpr int kDsOff = kQdOOff + kStages * 2 * kTile;    // dS^T as an MN-major operand: 2 x [128 x 128 B]
+  static constexpr int kStgOff = kDsOff + 32768;                  // fp32 staging: 2 x [128 rows x 128 B]
+  static constexpr int kVecOff = kStgOff + 32768;                 // per stage: lse2[128], delta[128] fp32
+  static constexpr int kBarOff = kVecOff + kStages * 1024;
+  static constexpr int kTotal = kBarOff + 512 + 1024;
+};
+
+__global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                      const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
+                                      int B, int S, int nq, int d) {
+  const int warps_per_block = blockDim.x / 32;
+  const long long total = (long long)B * S * nq;
+  const int lane = threadIdx.x % 32;
+  for (long long w = (long long)blockIdx.x * warps_per_block + threadIdx.x / 32; w < total; w += (long long)gridDim.x * warps_per_block) {
+    const int h = w % nq;
+    const long long row = w / nq;  // b*S + s
+    const size_t base = (size_t)row * nq * d + (size_t)h * d;
+    float acc = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+      float a[8], b8[8];
+      load8(o + base + c, a);
+      load8(d_o + base + c, b8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += a[e] * b8[e];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const int b = row / S, s = row % S;
+      const size_t idx = ((size_t)b * nq + h) * S + s;
+      delta[idx] = acc;
+      lse2[idx] = lse[idx] * 1.4426950408889634f;
+    }
+  }
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                 const __grid_constant__ CUtensorMap tmap_dqkv, const float* __restrict__ lse2, const float* __restrict__ delta,
+                 int S, int n_kv, int g, float scale, float scale_log2, int* __restrict__ status) {
+  using L = BwdSmem<D>;
+  constexpr int QS = L::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* kv_full = bars;            // [1]
+  uint64_t* q_full = bars + 1;         // [QS]
+  uint64_t* q_empty = q_full + QS;     // [QS]
+  uint64_t* sdp_full = q_empty + QS;   // S^T and dP^T ready
+  uint64_t* pds_full = sdp_full + 1;   // P^T, dS^T written (128 arrivals)
+  uint64_t* dq_full = pds_full + 1;    // dV, dK, dQ MMAs of this step finished
+  uint64_t* dq_drained = dq_full + 1;  // dQ read out of tensor memory (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n_blk = S / 128;
+  const int n = n_blk - 1 - (int)blockIdx.x;   // key block; cheapest last
+  const int head = blockIdx.y;                  // kv-group-major query head index j*g + i
+  const int b = blockIdx.z;
+  const int j = head / g, i = head % g;
+  const int nq = n_kv * g;
+  const int q_col = (j * (g + 2) + i) * D, k_col = (j * (g + 2) + g) * D, v_col = k_col + D;
+  const int do_col = head * D;
+  const int grow0 = b * S;
+  const int steps = n_blk - n;                  // query blocks m = n .. n_blk-1
+  const float* lse2_h = lse2 + ((size_t)b * nq + head) * S;
+  const float* delta_h = delta + ((size_t)b * nq + head) * S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < QS; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_drained, 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // columns: S^T/P^T [0,128)  dP^T/dS^T [128,256)  D=64: dQ [256,320) dK [320,384) dV [384,448)
+  //                                                 D=128: dK [256,384) dV [384,512), dQ reuses [0,128) once P^T is consumed
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128;
+  const uint32_t tm_dq = (D == 64) ? tmem_base + 256 : tmem_base;
+  const uint32_t tm_dk = (D == 64) ? tmem_base + 320 : tmem_base + 256;
+  const uint32_t tm_dv = (D == 64) ? tmem_base + 384 : tmem_base + 384;
+  constexpr bool kDqAliasesS = (D != 64);
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_qkv);
+      tma_prefetch_desc(&tmap_do);
+      mbar_expect_tx(kv_full, 2 * L::kTile);
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_2d(smem + L::kKOff + c * 16384, &tmap_qkv, k_col + c * 64, grow0 + n * 128, kv_full);
+        tma_load_2d(smem + L::kVOff + c * 16384, &tmap_qkv, v_col + c * 64, grow0 + n * 128, kv_full);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int st = 0; st < steps; ++st) {
+        const int m = n + st;
+        if (!mbar_wait(&q_empty[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) break;
+        unsigned char* sq = smem + L::kQdOOff + stage * 2 * L::kTile;
+        unsigned char* sdo = sq + L::kTile;
+        float* vec = reinterpret_cast<float*>(smem + L::kVecOff + stage * 1024);
+        mbar_expect_tx(&q_full[stage], 2 * L::kTile + 1024);
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_2d(sq + c * 16384, &tmap_qkv, q_col + c * 64, grow0 + m * 128, &q_full[stage]);
+          tma_load_2d(sdo + c * 16384, &tmap_do, do_col + c * 64, grow0 + m * 128, &q_full[stage]);
+        }
+        bulk_load_1d(vec, lse2_h + m * 128, 512, &q_full[stage]);
+        bulk_load_1d(vec + 128, delta_h + m * 128, 512, &q_full[stage]);
+        if (++stage == QS) { stage = 0; phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 128, false, false);   // S^T, dP^T: both operands K-major
+      constexpr uint32_t idesc_dkv = make_idesc_bf16(128, D, false, true);     // A from TMEM, B MN-major
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);       // A = dS^T in smem (MN-major), B = K MN-major
+      const uint32_t k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff);
+      const uint32_t ds_addr = smem_u32(smem + L::kDsOff);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, status, kTimeoutSmemFull);
+      int stage = 0;
+      uint32_t phase = 0, ph_pds = 0, ph_drain = 0;
+      auto issue_sdp = [&](uint32_t q_addr, uint32_t do_addr) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_bf16_ss(tm_s, make_smem_desc(k_addr + off, 0, 1024), make_smem_desc(q_addr + off, 0, 1024), idesc_st, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_bf16_ss(tm_dp, make_smem_desc(v_addr + off, 0, 1024), make_smem_desc(do_addr + off, 0, 1024), idesc_st, kk != 0);
+        }
+        umma_commit(sdp_full);
+      };
+      if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, status, kTimeoutSmemFull);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t q0a = smem_u32(smem + L::kQdOOff);
+        issue_sdp(q0a, q0a + L::kTile);
+      }
+      for (int st = 0; st < steps && ok; ++st) {
+        const uint32_t q_addr = smem_u32(smem + L::kQdOOff + stage * 2 * L::kTile);
+        const uint32_t do_addr = q_addr + L::kTile;
+        if (!mbar_wait(pds_full, ph_pds, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+        ph_pds ^= 1;
+        tc_fence_after();
+        // dV += P^T dO ; dK += dS^T Q   (K dimension = 128 queries, 8 steps of 16)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ts(tm_dv, tm_s + kk * 8, make_smem_desc(do_addr + kk * 2048, 16384, 1024), idesc_dkv, (st | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ts(tm_dk, tm_dp + kk * 8, make_smem_desc(q_addr + kk * 2048, 16384, 1024), idesc_dkv, (st | kk) != 0);
+        // dQ = dS K : M = queries, N = D, K dimension = 128 keys
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ss(tm_dq, make_smem_desc(ds_addr + kk * 2048, 16384, 1024), make_smem_desc(k_addr + kk * 2048, 16384, 1024),
+                       idesc_dq, kk != 0);
+        umma_commit(dq_full);
+        umma_commit(&q_empty[stage]);
+        int nstage = stage + 1;
+        uint32_t nphase = phase;
+        if (nstage == QS) { nstage = 0; nphase ^= 1; }
+        if (st + 1 < steps) {
+          if (!mbar_wait(&q_full[nstage], nphase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          if (kDqAliasesS) {
+            if (!mbar_wait(dq_drained, ph_drain, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
+            ph_drain ^= 1;
+          }
+          tc_fence_after();
+          const uint32_t qn = smem_u32(smem + L::kQdOOff + nstage * 2 * L::kTile);
+          issue_sdp(qn, qn + L::kTile);
+        }
+        stage = nstage;
+        phase = nphase;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- compute warps: thread r owns key row r ----------------
+    const int r = warp * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const int key = n * 128 + r;
+    unsigned char* ds_row0 = smem + L::kDsOff + r * 128;          // chunk 0 (queries 0..63); chunk 1 is +16384
+    unsigned char* stg = smem + L::kStgOff;
+    const bool issuer = (threadIdx.x == 0);
+    uint32_t ph_sdp = 0, ph_dq = 0;
+    int stage = 0;
+    uint32_t qphase = 0;
+    bool ok = true;
+    int sbuf = 0;
+    // staged TMA reduce-add of a [128 x D] fp32 tensor-memory tile into the fp32 dQKV image
+    auto drain_tile = [&](uint32_t tm_src, int col, int row) {
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_src + lane_off + c * 32, v);
+        tmem_wait_ld();
+        if (issuer) tma_wait_group_read<1>();
+        named_barrier_sync(1, 128);
+        unsigned char* rowp = stg + sbuf * 16384 + r * 128;
+#pragma unroll
+        for (int p8 = 0; p8 < 8; ++p8)
+          *reinterpret_cast<uint4*>(rowp + ((p8 ^ (r & 7)) * 16)) = make_uint4(v[p8 * 4], v[p8 * 4 + 1], v[p8 * 4 + 2], v[p8 * 4 + 3]);
+        fence_proxy_async();
+        named_barrier_sync(1, 128);
+        if (issuer) {
+          tma_reduce_add_2d(&tmap_dqkv, stg + sbuf * 16384, col + c * 32, row);
+          tma_commit_group();
+        }
+        sbuf ^= 1;
+      }
+    };
+    for (int st = 0; st < steps && ok; ++st) {
+      const int m = n + st;
+      // q_full is also what delivers lse2 / delta of this query block
+      if (!mbar_wait(&q_full[stage], qphase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+      const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024);
+      if (!mbar_wait(sdp_full, ph_sdp, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      ph_sdp ^= 1;
+      tc_fence_after();
+      const bool diag = (m == n);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32], pk[16], dk[16];
+        tmem_ld_32x32(tm_s + lane_off + c * 32, sv);
+        tmem_ld_32x32(tm_dp + lane_off + c * 32, dv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int qc = c * 32 + e;
+          float p0 = exp2f(__uint_as_float(sv[e]) * scale_log2 - vec[qc]);
+          float p1 = exp2f(__uint_as_float(sv[e + 1]) * scale_log2 - vec[qc + 1]);
+          if (diag) {
+            if (key > m * 128 + qc) p0 = 0.f;
+            if (key > m * 128 + qc + 1) p1 = 0.f;
+          }
+          float d0 = p0 * (__uint_as_float(dv[e]) - vec[128 + qc]) * scale;
+          float d1 = p1 * (__uint_as_float(dv[e + 1]) - vec[128 + qc + 1]) * scale;
+          pk[e / 2] = pack_bf16(p0, p1);
+          dk[e / 2] = pack_bf16(d0, d1);
+        }
+        tmem_st_32x16(tm_s + lane_off + c * 16, pk);     // P^T  (aliases S^T columns already consumed)
+        tmem_st_32x16(tm_dp + lane_off + c * 16, dk);    // dS^T (aliases dP^T columns already consumed)
+        // dS^T row r, queries [32c, 32c+32) -> smem MN-major operand: chunk = c/2, 16-byte pieces 4*(c%2) .. +3
+        unsigned char* rowp = ds_row0 + (c / 2) * 16384;
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) {
+          const int piece = (c % 2) * 4 + p4;
+          *reinterpret_cast<uint4*>(rowp + ((piece ^ (r & 7)) * 16)) = make_uint4(dk[p4 * 4], dk[p4 * 4 + 1], dk[p4 * 4 + 2], dk[p4 * 4 + 3]);
+        }
+      }
+      tmem_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      // drain dQ of this step
+      if (!mbar_wait(dq_full, ph_dq, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      ph_dq ^= 1;
+      tc_fence_after();
+      drain_tile(tm_dq, q_col, grow0 + m * 128);
+      tc_fence_before();
+      mbar_arrive(dq_drained);
+      if (++stage == QS) { stage = 0; qphase ^= 1; }
+    }
+    if (ok) {
+      // the last dq_full also covers the final dK / dV accumulation
+      drain_tile(tm_dk, k_col, grow0 + n * 128);
+      drain_tile(tm_dv, v_col, grow0 + n * 128);
+    }
+    if (issuer) tma_wait_group<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { __nanosleep(200); }
+    __syncthreads();
+  }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// fp32 image -> bf16 packed dQKV
+__global__ void dqkv_finalize_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n8) {
+  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it < n8; it += (size_t)gridDim.x * blockDim.x) {
+    float f[8];
+    load8(src + it * 8, f);
+    store8(dst + it * 8, f);
+  }
+}
+
+int make_tmap_f32_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     uint32_t box_cols);
+
 }  // namespace fth
 
 using namespace fth;
@@ -319,6 +659,56 @@ int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv
     if (!set) { cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kTotal); set = true; }
     flash_fwd_kernel<128><<<grid, kFwdThreads, FwdSmem<128>::kTotal, stream>>>(tm, (__nv_bfloat16*)out, lse, S, n_kv, g, scale_log2, status);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+// Scratch: `scratch_f32` holds [B*S, qkv_dim] fp32 (zeroed here) followed by delta and lse2, each [B, nq, S] fp32.
+size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d) {
+  return ((size_t)B * S * n_kv * (g + 2) * d + 2 * (size_t)B * n_kv * g * S) * sizeof(float);
+}
+
+int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const float* lse, void* dqkv, void* scratch_f32,
+                  int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream) {
+  if (S % 128 || (d != 64 && d != 128)) return -2;
+  const int nq = n_kv * g;
+  const uint64_t rs = (uint64_t)n_kv * (g + 2) * d;
+  const size_t n_img = (size_t)B * S * rs;
+  float* img = reinterpret_cast<float*>(scratch_f32);
+  float* delta = img + n_img;
+  float* lse2 = delta + (size_t)B * nq * S;
+  cudaMemsetAsync(img, 0, n_img * sizeof(float), stream);
+  {
+    long long warps = (long long)B * S * nq;
+    int blocks = (int)((warps + 7) / 8);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    flash_bwd_prep_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, lse, delta, lse2,
+                                                     B, S, nq, d);
+  }
+  CUtensorMap tq, tdo, tdq;
+  int r = make_tmap_bf16_2d(&tq, qkv, (uint64_t)B * S, rs, rs, 128, 64);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tdo, d_out, (uint64_t)B * S, (uint64_t)nq * d, (uint64_t)nq * d, 128, 64);
+  if (r) return r;
+  r = make_tmap_f32_2d(&tdq, img, (uint64_t)B * S, rs, rs, 128, 32);
+  if (r) return r;
+  const float scale = 1.f / sqrtf((float)d);
+  dim3 grid(S / 128, nq, B);
+  if (d == 64) {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(flash_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::kTotal); set = true; }
+    flash_bwd_kernel<64><<<grid, kBwdThreads, BwdSmem<64>::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
+                                                                            scale * 1.4426950408889634f, status);
+  } else {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kTotal); set = true; }
+    flash_bwd_kernel<128><<<grid, kBwdThreads, BwdSmem<128>::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
+                                                                              scale * 1.4426950408889634f, status);
+  }
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  size_t n8 = n_img / 8;
+  int blocks = (int)((n8 + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dqkv_finalize_kernel<<<blocks, 256, 0, stream>>>(img, (__nv_bfloat16*)dqkv, n8);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

@@ -10,7 +10,14 @@ namespace {
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
-void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+// Number of kernels of this library launched (or captured into a CUDA graph) by this process.
+int64_t g_launches = 0;
+int64_t launch_count() { return g_launches; }
+
+void check(int rc, const char* what, int kernels = 1) {
+  TORCH_CHECK(rc == 0, what, " failed with code ", rc);
+  g_launches += kernels;
+}
 
 void need_bf16(const at::Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), n, " must be a contiguous CUDA bf16 tensor");
@@ -76,7 +83,7 @@ at::Tensor rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tens
   }
   check(fth_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(),
                         partial.data_ptr<float>(), dw_main_grad.data_ptr<float>(), M, H, (float)out_scale, cur_stream()),
-        "rmsnorm_bwd");
+        "rmsnorm_bwd", 2);
   return dx;
 }
 
@@ -193,7 +200,7 @@ at::Tensor sumsq(const at::Tensor& x) {
   at::Tensor partial = at::empty({fth_sumsq_blocks()}, x.options().dtype(at::kDouble));
   at::Tensor out = at::empty({}, x.options());
   check(fth_sumsq(x.data_ptr<float>(), (size_t)x.numel(), partial.data_ptr<double>(), out.data_ptr<float>(), cur_stream()),
-        "sumsq");
+        "sumsq", 2);
   return out;
 }
 
@@ -233,6 +240,21 @@ std::vector<at::Tensor> flash_fwd(const at::Tensor& qkv, int64_t S, int64_t n_kv
   return {out, lse};
 }
 
+at::Tensor flash_bwd(const at::Tensor& dout, const at::Tensor& qkv, const at::Tensor& out, const at::Tensor& lse, int64_t S,
+                     int64_t n_kv, int64_t g, int64_t d) {
+  need_bf16(dout, "dout");
+  need_bf16(qkv, "qkv");
+  need_bf16(out, "out");
+  need_f32(lse, "lse");
+  const int64_t M = qkv.size(0), B = M / S;
+  at::Tensor dqkv = at::empty_like(qkv);
+  const size_t bytes = fth_flash_bwd_scratch_bytes((int)B, (int)S, (int)n_kv, (int)g, (int)d);
+  at::Tensor scratch = at::empty({(int64_t)(bytes / 4)}, qkv.options().dtype(at::kFloat));
+  check(fth_flash_bwd(dout.data_ptr(), qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), dqkv.data_ptr(),
+                      scratch.data_ptr(), (int)B, (int)S, (int)n_kv, (int)g, (int)d, status_ptr(), cur_stream()), "flash_bwd", 3);
+  return dqkv;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -251,5 +273,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
   m.def("flash_fwd", &flash_fwd);
+  m.def("flash_bwd", &flash_bwd);
   m.def("read_status", &read_status);
+  m.def("launch_count", &launch_count);
 }

@@ -95,6 +95,8 @@ class Trainer:
         self._graph = None
         self._graph_stats = None
         self._graph_failed = False
+        self.graph_launches = 0  # sm_100a kernels recorded in the captured micro-batch graph
+        self.graph_replays = 0
         self.stats = torch.zeros(4, dtype=torch.float64, device=self.device)
         self.launch_count = 0
         self.last = {}
@@ -155,8 +157,10 @@ class Trainer:
             torch.cuda.synchronize()
             self.store.zero_grad()
             g = torch.cuda.CUDAGraph()
+            n0 = self._launch_count()
             with torch.cuda.graph(g):
                 self._graph_stats = self._fwd_bwd(batch)
+            self.graph_launches = self._launch_count() - n0
             self._graph = g
         except Exception as e:  # fall back to eager, as the reference does
             self._graph, self._graph_failed = None, True
@@ -164,6 +168,12 @@ class Trainer:
                 print(f"[debug] CUDA graph capture failed, running eager: {e}", file=sys.stderr, flush=True)
             torch.cuda.synchronize()
             self.store.zero_grad()
+
+    def _launch_count(self) -> int:
+        if self.device.type != "cuda" or self.ops.name != "sm100":
+            return 0
+        from .ops.cuda_ops import _C
+        return int(_C.launch_count())
 
     def _use_graph(self) -> bool:
         t = self.cfg.train
@@ -181,6 +191,7 @@ class Trainer:
                     self._try_capture_graph(batch)
                 if self._graph is not None:
                     self._graph.replay()
+                    self.graph_replays += 1
                     self.stats += self._graph_stats
                     continue
             self.stats += self._fwd_bwd(batch)

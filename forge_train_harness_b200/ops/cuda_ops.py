@@ -109,6 +109,13 @@ class Sm100Ops:
         out, lse = _C.flash_fwd(qkv, seq_len, n_kv, g, d)
         return out, lse
 
+    @staticmethod
+    def attention_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d):
+        if not Sm100Ops.attention_supported(seq_len, d):
+            from .torch_ops import TorchOps
+            return TorchOps.attention_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d)
+        return _C.flash_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d)
+
     # ---- SwiGLU ---------------------------------------------------------------
     @staticmethod
     def swiglu_fwd(gate_up):

@@ -150,6 +150,24 @@ def test_flash_fwd(ops, B, S, nkv, g, d):
     close(out, out0, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("B,S,nkv,g,d", [(1, 128, 1, 1, 64), (2, 256, 2, 2, 64), (1, 384, 1, 2, 128), (2, 512, 2, 8, 64), (1, 1024, 1, 4, 128)])
+def test_flash_bwd(ops, B, S, nkv, g, d):
+    from forge_train_harness_b200.ops.cuda_ops import check_status
+    qkv = rnd(B * S, nkv * (g + 2) * d, scale=1.0)
+    out, lse = ops.attention_fwd(qkv, S, nkv, g, d)
+    dout = rnd(B * S, nkv * g * d, scale=1.0)
+    dqkv = ops.attention_bwd(dout, qkv, out, lse, S, nkv, g, d)
+    torch.cuda.synchronize()
+    check_status()
+    out0, lse0 = T.attention_fwd(qkv.float(), S, nkv, g, d)
+    dqkv0 = T.attention_bwd(dout.float(), qkv.float(), out0, lse0, S, nkv, g, d)
+    v = dqkv.view(B * S, nkv, g + 2, d).float()
+    v0 = dqkv0.view(B * S, nkv, g + 2, d)
+    close(v[:, :, :g], v0[:, :, :g], 3e-2, 3e-2)       # dQ
+    close(v[:, :, g], v0[:, :, g], 3e-2, 3e-2)         # dK
+    close(v[:, :, g + 1], v0[:, :, g + 1], 3e-2, 3e-2)  # dV
+
+
 def test_gemm_repeated_calls_and_views(ops):
     """Operands that are strided row views (unit inner stride) and repeated in-place updates."""
     big = rnd(512, 2048, scale=0.5)
