@@ -38,7 +38,7 @@ int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv
 
 size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d);
 int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const float* lse, void* dqkv, void* scratch_f32,
-                  int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream);
+                  const float* rope_table, int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -194,49 +194,52 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __rest
       tc_fence_after();
       const bool diag = (kb * 128 + 127 > q0 + t * 128);  // block touches the causal boundary
       const int kpos0 = kb * 128;
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tm_s[t] + lane_off + c * 32, r);
-        tmem_wait_ld();
+      // the whole 128-wide row of S lives in registers: four back-to-back tensor-memory loads, one wait
+      uint32_t sr[128];
+      tmem_ld_32x32(tm_s[t] + lane_off, sr);
+      tmem_ld_32x32(tm_s[t] + lane_off + 32, sr + 32);
+      tmem_ld_32x32(tm_s[t] + lane_off + 64, sr + 64);
+      tmem_ld_32x32(tm_s[t] + lane_off + 96, sr + 96);
+      tmem_wait_ld();
+      if (diag) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float v = __uint_as_float(r[e]);
-          if (diag && kpos0 + c * 32 + e > qrow) v = -INFINITY;
-          mx = fmaxf(mx, v);
-        }
+        for (int e = 0; e < 128; ++e)
+          if (kpos0 + e > qrow) sr[e] = 0xff800000u;  // -inf
       }
-      mx *= scale_log2;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 128; e += 8) {
+        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])));
+        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])));
+        mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sr[e + 4]), __uint_as_float(sr[e + 5])));
+        mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sr[e + 6]), __uint_as_float(sr[e + 7])));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
       float m_new = fmaxf(m_run, mx);
       // keep the stale max unless it moved a lot (P stays <= 2^8); always take it on the first block
       float m_use = (m_new - m_run > kRescaleThreshold) ? m_new : m_run;
       if (m_run == -INFINITY) m_use = m_new;
       const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
       const bool need_fix = (m_use != m_run) && kb > 0;
-      // pass 2: P = exp2(s*scale - m), row sum, packed bf16 into the S columns
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], pk[16];
-        tmem_ld_32x32(tm_s[t] + lane_off + c * 32, r);
-        tmem_wait_ld();
+      // P = exp2(s*scale - m) as packed bf16 written over the S columns (chunk c of P aliases S columns
+      // [16c, 16c+16), which this thread has already read), row sum in four partial sums
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v0 = __uint_as_float(r[e]) * scale_log2 - m_use, v1 = __uint_as_float(r[e + 1]) * scale_log2 - m_use;
-          float p0 = exp2f(v0), p1 = exp2f(v1);
-          if (diag) {
-            if (kpos0 + c * 32 + e > qrow) p0 = 0.f;
-            if (kpos0 + c * 32 + e + 1 > qrow) p1 = 0.f;
-          }
-          rs += p0 + p1;
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sr[c * 32 + e]), scale_log2, -m_use));
+          const float p1 = exp2f(fmaf(__uint_as_float(sr[c * 32 + e + 1]), scale_log2, -m_use));
+          const float p2 = exp2f(fmaf(__uint_as_float(sr[c * 32 + e + 2]), scale_log2, -m_use));
+          const float p3 = exp2f(fmaf(__uint_as_float(sr[c * 32 + e + 3]), scale_log2, -m_use));
+          rs0 += p0; rs1 += p1; rs2 += p2; rs3 += p3;
           pk[e / 2] = pack_bf16(p0, p1);
+          pk[e / 2 + 1] = pack_bf16(p2, p3);
         }
-        // all four chunks of S have been read by this thread before any P column it aliases is needed?  P chunk c
-        // occupies columns [16c, 16c+16) which alias S columns of chunk c/2 <= c, already consumed.
         tmem_st_32x16(tm_s[t] + lane_off + c * 16, pk);
       }
+      const float rs = (rs0 + rs1) + (rs2 + rs3);
       l_run = l_run * alpha + rs;
       m_run = m_use;
       // O correction (needs the previous P V of this tile to be complete)
@@ -313,7 +316,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __rest
 // the query heads of a KV group, i.e. over CTAs) use the same path.  A finalize kernel rounds that image to bf16.
 // =====================================================================================================================
 
-constexpr int kBwdThreads = 192;  // warps 0-3 compute (one key row per thread), warp 4 TMA, warp 5 MMA
+constexpr int kBwdThreads = 320;  // warps 0-7 compute (two warpgroups, 64 query columns each), warp 8 TMA, warp 9 MMA
 
 template <int D>
 struct BwdSmem {
@@ -323,7 +326,7 @@ struct BwdSmem {
   static constexpr int kVOff = kTile;
   static constexpr int kQdOOff = 2 * kTile;                       // per stage: Q tile, dO tile
   static constexpr int kDsOff = kQdOOff + kStages * 2 * kTile;    // dS^T as an MN-major operand: 2 x [128 x 128 B]
-  static constexpr int kStgOff = kDsOff + 32768;                  // fp32 staging: 2 x [128 rows x 128 B]
+  static constexpr int kStgOff = kDsOff + 32768;                  // fp32 staging: one [128 rows x 128 B] per warpgroup
   static constexpr int kVecOff = kStgOff + 32768;                 // per stage: lse2[128], delta[128] fp32
   static constexpr int kBarOff = kVecOff + kStages * 1024;
   static constexpr int kTotal = kBarOff + 512 + 1024;
@@ -400,14 +403,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
     mbar_init(kv_full, 1);
     for (int s = 0; s < QS; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 128);
+    mbar_init(dq_drained, 256);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -420,7 +423,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
   const uint32_t tm_dv = (D == 64) ? tmem_base + 384 : tmem_base + 384;
   constexpr bool kDqAliasesS = (D != 64);
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
       tma_prefetch_desc(&tmap_qkv);
@@ -449,7 +452,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
       constexpr uint32_t idesc_st = make_idesc_bf16(128, 128, false, false);   // S^T, dP^T: both operands K-major
@@ -488,10 +491,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         // dV += P^T dO ; dK += dS^T Q   (K dimension = 128 queries, 8 steps of 16)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(tm_dv, tm_s + kk * 8, make_smem_desc(do_addr + kk * 2048, 16384, 1024), idesc_dkv, (st | kk) != 0);
+          umma_bf16_ts(tm_dv, tm_s + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), make_smem_desc(do_addr + kk * 2048, 16384, 1024),
+                       idesc_dkv, (st | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(tm_dk, tm_dp + kk * 8, make_smem_desc(q_addr + kk * 2048, 16384, 1024), idesc_dkv, (st | kk) != 0);
+          umma_bf16_ts(tm_dk, tm_dp + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), make_smem_desc(q_addr + kk * 2048, 16384, 1024),
+                       idesc_dkv, (st | kk) != 0);
         // dQ = dS K : M = queries, N = D, K dimension = 128 keys
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
@@ -518,77 +523,83 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
     }
     __syncwarp();
   } else {
-    // ---------------- compute warps: thread r owns key row r ----------------
-    const int r = warp * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // ---------------- compute warps ----------------
+    // Thread (qd, lane) owns key row r = 32*qd + lane; warpgroup h = warp / 4 owns query columns [64h, 64h+64).
+    const int qd = warp % 4, h = warp / 4;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     const int key = n * 128 + r;
-    unsigned char* ds_row0 = smem + L::kDsOff + r * 128;          // chunk 0 (queries 0..63); chunk 1 is +16384
-    unsigned char* stg = smem + L::kStgOff;
-    const bool issuer = (threadIdx.x == 0);
+    unsigned char* ds_row = smem + L::kDsOff + h * 16384 + r * 128;   // dS^T operand chunk h (queries 64h..64h+63)
+    unsigned char* stg = smem + L::kStgOff + h * 16384;
+    const bool issuer = (threadIdx.x == h * 128);
+    const int bar_id = 1 + h;
     uint32_t ph_sdp = 0, ph_dq = 0;
     int stage = 0;
     uint32_t qphase = 0;
     bool ok = true;
-    int sbuf = 0;
-    // staged TMA reduce-add of a [128 x D] fp32 tensor-memory tile into the fp32 dQKV image
+    // TMA reduce-add of this warpgroup's half of a [128 x D] fp32 tensor-memory tile into the fp32 dQKV image
     auto drain_tile = [&](uint32_t tm_src, int col, int row) {
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
+        const int cc = h * (D / 64) + c;     // 32-column chunk index handled by this warpgroup
         uint32_t v[32];
-        tmem_ld_32x32(tm_src + lane_off + c * 32, v);
+        tmem_ld_32x32(tm_src + lane_off + cc * 32, v);
         tmem_wait_ld();
-        if (issuer) tma_wait_group_read<1>();
-        named_barrier_sync(1, 128);
-        unsigned char* rowp = stg + sbuf * 16384 + r * 128;
+        if (issuer) tma_wait_group_read<0>();  // the previous store has finished reading the staging buffer
+        named_barrier_sync(bar_id, 128);
+        unsigned char* rowp = stg + r * 128;
 #pragma unroll
         for (int p8 = 0; p8 < 8; ++p8)
           *reinterpret_cast<uint4*>(rowp + ((p8 ^ (r & 7)) * 16)) = make_uint4(v[p8 * 4], v[p8 * 4 + 1], v[p8 * 4 + 2], v[p8 * 4 + 3]);
         fence_proxy_async();
-        named_barrier_sync(1, 128);
+        named_barrier_sync(bar_id, 128);
         if (issuer) {
-          tma_reduce_add_2d(&tmap_dqkv, stg + sbuf * 16384, col + c * 32, row);
+          tma_reduce_add_2d(&tmap_dqkv, stg, col + cc * 32, row);
           tma_commit_group();
         }
-        sbuf ^= 1;
       }
     };
     for (int st = 0; st < steps && ok; ++st) {
       const int m = n + st;
       // q_full is also what delivers lse2 / delta of this query block
       if (!mbar_wait(&q_full[stage], qphase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
-      const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024);
+      const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024) + 64 * h;
       if (!mbar_wait(sdp_full, ph_sdp, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
       ph_sdp ^= 1;
       tc_fence_after();
       const bool diag = (m == n);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32], pk[16], dk[16];
-        tmem_ld_32x32(tm_s + lane_off + c * 32, sv);
-        tmem_ld_32x32(tm_dp + lane_off + c * 32, dv);
-        tmem_wait_ld();
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(tm_s + lane_off + 64 * h, sv);
+      tmem_ld_32x32(tm_s + lane_off + 64 * h + 32, sv + 32);
+      tmem_ld_32x32(tm_dp + lane_off + 64 * h, dv);
+      tmem_ld_32x32(tm_dp + lane_off + 64 * h + 32, dv + 32);
+      tmem_wait_ld();
+      const int q_first = m * 128 + 64 * h;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16], dk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           const int qc = c * 32 + e;
-          float p0 = exp2f(__uint_as_float(sv[e]) * scale_log2 - vec[qc]);
-          float p1 = exp2f(__uint_as_float(sv[e + 1]) * scale_log2 - vec[qc + 1]);
+          float p0 = exp2f(fmaf(__uint_as_float(sv[qc]), scale_log2, -vec[qc]));
+          float p1 = exp2f(fmaf(__uint_as_float(sv[qc + 1]), scale_log2, -vec[qc + 1]));
           if (diag) {
-            if (key > m * 128 + qc) p0 = 0.f;
-            if (key > m * 128 + qc + 1) p1 = 0.f;
+            if (key > q_first + qc) p0 = 0.f;
+            if (key > q_first + qc + 1) p1 = 0.f;
           }
-          float d0 = p0 * (__uint_as_float(dv[e]) - vec[128 + qc]) * scale;
-          float d1 = p1 * (__uint_as_float(dv[e + 1]) - vec[128 + qc + 1]) * scale;
+          const float d0 = p0 * (__uint_as_float(dv[qc]) - vec[128 + qc]) * scale;
+          const float d1 = p1 * (__uint_as_float(dv[qc + 1]) - vec[128 + qc + 1]) * scale;
           pk[e / 2] = pack_bf16(p0, p1);
           dk[e / 2] = pack_bf16(d0, d1);
         }
-        tmem_st_32x16(tm_s + lane_off + c * 16, pk);     // P^T  (aliases S^T columns already consumed)
-        tmem_st_32x16(tm_dp + lane_off + c * 16, dk);    // dS^T (aliases dP^T columns already consumed)
-        // dS^T row r, queries [32c, 32c+32) -> smem MN-major operand: chunk = c/2, 16-byte pieces 4*(c%2) .. +3
-        unsigned char* rowp = ds_row0 + (c / 2) * 16384;
+        // P^T / dS^T of queries [64h+32c, +32) go to packed columns [64h+16c, +16): inside this warpgroup's own
+        // S^T / dP^T column range, all of which this thread has already read
+        tmem_st_32x16(tm_s + lane_off + 64 * h + c * 16, pk);
+        tmem_st_32x16(tm_dp + lane_off + 64 * h + c * 16, dk);
 #pragma unroll
         for (int p4 = 0; p4 < 4; ++p4) {
-          const int piece = (c % 2) * 4 + p4;
-          *reinterpret_cast<uint4*>(rowp + ((piece ^ (r & 7)) * 16)) = make_uint4(dk[p4 * 4], dk[p4 * 4 + 1], dk[p4 * 4 + 2], dk[p4 * 4 + 3]);
+          const int piece = c * 4 + p4;
+          *reinterpret_cast<uint4*>(ds_row + ((piece ^ (r & 7)) * 16)) = make_uint4(dk[p4 * 4], dk[p4 * 4 + 1], dk[p4 * 4 + 2], dk[p4 * 4 + 3]);
         }
       }
       tmem_wait_st();
@@ -619,15 +630,309 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
     while (clock64() - t0 < 2000000LL) { __nanosleep(200); }
     __syncthreads();
   }
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-// fp32 image -> bf16 packed dQKV
-__global__ void dqkv_finalize_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n8) {
-  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it < n8; it += (size_t)gridDim.x * blockDim.x) {
-    float f[8];
-    load8(src + it * 8, f);
-    store8(dst + it * 8, f);
+// ---------------------------------------------------------------------------------------------------------------------
+// head_dim 64 backward, software-pipelined.  Same math and data flow as flash_bwd_kernel, but the 128-query block of a step
+// is handled as two 64-query halves with their own barriers, so the long serial chain of a step (commit -> tensor-memory
+// load -> exp / dS math -> tensor-memory store -> fence -> barrier -> next MMA) of one half runs while the tensor core
+// works on the other half and on the next step:
+//     MMA order:  ... | dV_A dK_A (i) | S_A dP_A (i+1) | dV_B dK_B (i) | dQ (i) | S_B dP_B (i+1) | dV_A dK_A (i+1) | ...
+// Warpgroup h computes half h.  dS^T lives in a double-buffered shared-memory operand and dQ in a double-buffered
+// tensor-memory tile (512 columns: S^T 128, dP^T 128, dK 64, dV 64, dQ 2 x 64), so neither stalls the next step.
+// ---------------------------------------------------------------------------------------------------------------------
+struct Bwd64Smem {
+  static constexpr int kTile = 128 * 64 * 2;
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kTile;
+  static constexpr int kQdOOff = 2 * kTile;              // 2 stages x (Q tile, dO tile)
+  static constexpr int kDsOff = kQdOOff + 4 * kTile;     // 2 buffers x 2 chunks x [128 x 128 B]
+  static constexpr int kStgOff = kDsOff + 65536;         // one [128 x 128 B] fp32 staging buffer per warpgroup
+  static constexpr int kVecOff = kStgOff + 32768;        // per stage: lse2[128], delta[128]
+  static constexpr int kBarOff = kVecOff + 2048;
+  static constexpr int kTotal = kBarOff + 512 + 1024;
+};
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                   const __grid_constant__ CUtensorMap tmap_dqkv, const float* __restrict__ lse2, const float* __restrict__ delta,
+                   int S, int n_kv, int g, float scale, float scale_log2, int* __restrict__ status) {
+  using L = Bwd64Smem;
+  constexpr int D = 64;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* kv_full = bars;             // [1]
+  uint64_t* q_full = bars + 1;          // [2]
+  uint64_t* q_empty = q_full + 2;       // [2]
+  uint64_t* sdp_full = q_empty + 2;     // [2] per half: S^T and dP^T ready
+  uint64_t* pds_full = sdp_full + 2;    // [2] per half: P^T, dS^T written (128 arrivals)
+  uint64_t* dq_full = pds_full + 2;     // [2] per dQ buffer
+  uint64_t* dq_drained = dq_full + 2;   // [2] per dQ buffer (256 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n_blk = S / 128;
+  const int n = n_blk - 1 - (int)blockIdx.x;
+  const int head = blockIdx.y;
+  const int b = blockIdx.z;
+  const int j = head / g, i = head % g;
+  const int nq = n_kv * g;
+  const int q_col = (j * (g + 2) + i) * D, k_col = (j * (g + 2) + g) * D, v_col = k_col + D;
+  const int do_col = head * D;
+  const int grow0 = b * S;
+  const int steps = n_blk - n;
+  const float* lse2_h = lse2 + ((size_t)b * nq + head) * S;
+  const float* delta_h = delta + ((size_t)b * nq + head) * S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
+      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128);
+      mbar_init(&dq_full[s], 1); mbar_init(&dq_drained[s], 256);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dk = tmem_base + 256, tm_dv = tmem_base + 320;
+  const uint32_t tm_dq0 = tmem_base + 384;  // two 64-column buffers
+
+  if (warp == 8) {
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_qkv);
+      tma_prefetch_desc(&tmap_do);
+      mbar_expect_tx(kv_full, 2 * L::kTile);
+      tma_load_2d(smem + L::kKOff, &tmap_qkv, k_col, grow0 + n * 128, kv_full);
+      tma_load_2d(smem + L::kVOff, &tmap_qkv, v_col, grow0 + n * 128, kv_full);
+      for (int st = 0; st < steps; ++st) {
+        const int stage = st & 1;
+        const uint32_t phase = (st >> 1) & 1;
+        const int m = n + st;
+        if (!mbar_wait(&q_empty[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) break;
+        unsigned char* sq = smem + L::kQdOOff + stage * 2 * L::kTile;
+        float* vec = reinterpret_cast<float*>(smem + L::kVecOff + stage * 1024);
+        mbar_expect_tx(&q_full[stage], 2 * L::kTile + 1024);
+        tma_load_2d(sq, &tmap_qkv, q_col, grow0 + m * 128, &q_full[stage]);
+        tma_load_2d(sq + L::kTile, &tmap_do, do_col, grow0 + m * 128, &q_full[stage]);
+        bulk_load_1d(vec, lse2_h + m * 128, 512, &q_full[stage]);
+        bulk_load_1d(vec + 128, delta_h + m * 128, 512, &q_full[stage]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // S^T / dP^T half: 128 keys x 64 queries
+      constexpr uint32_t idesc_dkv = make_idesc_bf16(128, D, false, true);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);
+      const uint32_t k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, status, kTimeoutSmemFull);
+      // S^T_h = K Q_h^T and dP^T_h = V dO_h^T for query half h of the tile in `stage`
+      auto issue_sdp = [&](int stage, int h) {
+        const uint32_t q_addr = smem_u32(smem + L::kQdOOff + stage * 2 * L::kTile) + h * 8192;
+        const uint32_t do_addr = q_addr + L::kTile;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ss(tm_s + 64 * h, make_smem_desc(k_addr + kk * 32, 0, 1024), make_smem_desc(q_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ss(tm_dp + 64 * h, make_smem_desc(v_addr + kk * 32, 0, 1024), make_smem_desc(do_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
+        umma_commit(&sdp_full[h]);
+      };
+      // dV += P_h^T dO_h ; dK += dS_h^T Q_h  (64 queries = 4 steps of 16)
+      auto issue_dkv = [&](int stage, int h, bool first) {
+        const uint32_t q_addr = smem_u32(smem + L::kQdOOff + stage * 2 * L::kTile);
+        const uint32_t do_addr = q_addr + L::kTile;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ts(tm_dv, tm_s + 64 * h + kk * 8, make_smem_desc(do_addr + (4 * h + kk) * 2048, 16384, 1024), idesc_dkv,
+                       !(first && kk == 0));
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ts(tm_dk, tm_dp + 64 * h + kk * 8, make_smem_desc(q_addr + (4 * h + kk) * 2048, 16384, 1024), idesc_dkv,
+                       !(first && kk == 0));
+      };
+      if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, status, kTimeoutSmemFull);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0, 0);
+        issue_sdp(0, 1);
+      }
+      for (int st = 0; st < steps && ok; ++st) {
+        const int stage = st & 1, nstage = stage ^ 1;
+        const uint32_t ph = st & 1;
+        const bool more = st + 1 < steps;
+        // ---- half A
+        if (!mbar_wait(&pds_full[0], ph, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+        issue_dkv(stage, 0, st == 0);
+        if (more) {
+          if (!mbar_wait(&q_full[nstage], ((st + 1) >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_sdp(nstage, 0);
+        }
+        // ---- half B
+        if (!mbar_wait(&pds_full[1], ph, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+        issue_dkv(stage, 1, false);
+        umma_commit(&q_empty[stage]);
+        // ---- dQ(st) = dS K into buffer st & 1 (free once dQ(st-2) was drained)
+        if (st >= 2) {
+          if (!mbar_wait(&dq_drained[st & 1], ((st >> 1) - 1) & 1, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
+          tc_fence_after();
+        }
+        const uint32_t ds_addr = smem_u32(smem + L::kDsOff + (st & 1) * 32768);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ss(tm_dq0 + 64 * (st & 1), make_smem_desc(ds_addr + kk * 2048, 16384, 1024),
+                       make_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_dq, kk != 0);
+        umma_commit(&dq_full[st & 1]);
+        if (more) issue_sdp(nstage, 1);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int qd = warp % 4, h = warp / 4;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const int key = n * 128 + r;
+    unsigned char* stg = smem + L::kStgOff + h * 16384;
+    const bool issuer = (threadIdx.x == h * 128);
+    const int bar_id = 1 + h;
+    bool ok = true;
+    // this warpgroup's 32 columns (h*32 ..) of a [128 x 64] fp32 tensor-memory tile -> TMA reduce-add into the dQKV image
+    auto drain_half = [&](uint32_t tm_src, int col, int row) {
+      uint32_t v[32];
+      tmem_ld_32x32(tm_src + lane_off + h * 32, v);
+      tmem_wait_ld();
+      if (issuer) tma_wait_group_read<0>();
+      named_barrier_sync(bar_id, 128);
+      unsigned char* rowp = stg + r * 128;
+#pragma unroll
+      for (int p8 = 0; p8 < 8; ++p8)
+        *reinterpret_cast<uint4*>(rowp + ((p8 ^ (r & 7)) * 16)) = make_uint4(v[p8 * 4], v[p8 * 4 + 1], v[p8 * 4 + 2], v[p8 * 4 + 3]);
+      fence_proxy_async();
+      named_barrier_sync(bar_id, 128);
+      if (issuer) {
+        tma_reduce_add_2d(&tmap_dqkv, stg, col + h * 32, row);
+        tma_commit_group();
+      }
+    };
+    for (int st = 0; st < steps && ok; ++st) {
+      const int m = n + st, stage = st & 1;
+      if (!mbar_wait(&q_full[stage], (st >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+      const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024) + 64 * h;
+      if (!mbar_wait(&sdp_full[h], st & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (m == n);
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(tm_s + lane_off + 64 * h, sv);
+      tmem_ld_32x32(tm_s + lane_off + 64 * h + 32, sv + 32);
+      tmem_ld_32x32(tm_dp + lane_off + 64 * h, dv);
+      tmem_ld_32x32(tm_dp + lane_off + 64 * h + 32, dv + 32);
+      tmem_wait_ld();
+      const int q_first = m * 128 + 64 * h;
+      unsigned char* ds_row = smem + L::kDsOff + (st & 1) * 32768 + h * 16384 + r * 128;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int qc = c * 32 + e;
+          float p0 = exp2f(fmaf(__uint_as_float(sv[qc]), scale_log2, -vec[qc]));
+          float p1 = exp2f(fmaf(__uint_as_float(sv[qc + 1]), scale_log2, -vec[qc + 1]));
+          if (diag) {
+            if (key > q_first + qc) p0 = 0.f;
+            if (key > q_first + qc + 1) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dv[qc]) - vec[128 + qc]) * scale;
+          const float d1 = p1 * (__uint_as_float(dv[qc + 1]) - vec[128 + qc + 1]) * scale;
+          pk[e / 2] = pack_bf16(p0, p1);
+          dk[e / 2] = pack_bf16(d0, d1);
+        }
+        tmem_st_32x16(tm_s + lane_off + 64 * h + c * 16, pk);
+        tmem_st_32x16(tm_dp + lane_off + 64 * h + c * 16, dk);
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) {
+          const int piece = c * 4 + p4;
+          *reinterpret_cast<uint4*>(ds_row + ((piece ^ (r & 7)) * 16)) = make_uint4(dk[p4 * 4], dk[p4 * 4 + 1], dk[p4 * 4 + 2], dk[p4 * 4 + 3]);
+        }
+      }
+      tmem_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&pds_full[h]);
+      // drain dQ of the PREVIOUS step (finished long ago) while the tensor core works on this one
+      if (st > 0) {
+        const int pb = (st - 1) & 1;
+        if (!mbar_wait(&dq_full[pb], ((st - 1) >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+        drain_half(tm_dq0 + 64 * pb, q_col, grow0 + (m - 1) * 128);
+        tc_fence_before();
+        mbar_arrive(&dq_drained[pb]);
+      }
+    }
+    if (ok) {
+      const int lb = (steps - 1) & 1;
+      if (mbar_wait(&dq_full[lb], ((steps - 1) >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) {
+        tc_fence_after();
+        drain_half(tm_dq0 + 64 * lb, q_col, grow0 + (n + steps - 1) * 128);
+        drain_half(tm_dk, k_col, grow0 + n * 128);   // the last dQ commit also covers the final dK / dV accumulation
+        drain_half(tm_dv, v_col, grow0 + n * 128);
+      }
+    }
+    if (issuer) tma_wait_group<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { __nanosleep(200); }
+    __syncthreads();
+  }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// fp32 image -> bf16 packed dQKV.  With a RoPE table the inverse rotation (the RoPE backward) of the q and k head
+// slots is applied on the way, so the gradient needs no separate RoPE pass.
+__global__ void dqkv_finalize_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, const float* __restrict__ table,
+                                     int M, int S, int n_kv, int g, int d) {
+  const int half = d / 2, vph = half / 8;
+  const int slots = n_kv * (g + 2);
+  const size_t total = (size_t)M * slots * vph;
+  const size_t row_stride = (size_t)slots * d;
+  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
+    const int vec = it % vph;
+    const size_t t = it / vph;
+    const int sl = t % slots;
+    const int row = t / slots;
+    const size_t off = (size_t)row * row_stride + (size_t)sl * d + vec * 8;
+    float x1[8], x2[8];
+    load8(src + off, x1);
+    load8(src + off + half, x2);
+    if (table != nullptr && (sl % (g + 2)) <= g) {
+      const float* tb = table + (size_t)(row % S) * d + vec * 8;
+      float c[8], sn[8];
+      load8(tb, c);
+      load8(tb + half, sn);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = x1[i], b = x2[i];
+        x1[i] = a * c[i] + b * sn[i];
+        x2[i] = b * c[i] - a * sn[i];
+      }
+    }
+    store8(dst + off, x1);
+    store8(dst + off + half, x2);
   }
 }
 
@@ -668,7 +973,7 @@ size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d) {
 }
 
 int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const float* lse, void* dqkv, void* scratch_f32,
-                  int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream) {
+                  const float* rope_table, int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream) {
   if (S % 128 || (d != 64 && d != 128)) return -2;
   const int nq = n_kv * g;
   const uint64_t rs = (uint64_t)n_kv * (g + 2) * d;
@@ -695,9 +1000,9 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
   dim3 grid(S / 128, nq, B);
   if (d == 64) {
     static bool set = false;
-    if (!set) { cudaFuncSetAttribute(flash_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::kTotal); set = true; }
-    flash_bwd_kernel<64><<<grid, kBwdThreads, BwdSmem<64>::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
-                                                                            scale * 1.4426950408889634f, status);
+    if (!set) { cudaFuncSetAttribute(flash_bwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::kTotal); set = true; }
+    flash_bwd64_kernel<<<grid, kBwdThreads, Bwd64Smem::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
+                                                                        scale * 1.4426950408889634f, status);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kTotal); set = true; }
@@ -705,10 +1010,10 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
                                                                               scale * 1.4426950408889634f, status);
   }
   if (cudaGetLastError() != cudaSuccess) return -21;
-  size_t n8 = n_img / 8;
-  int blocks = (int)((n8 + 255) / 256);
+  size_t items = (size_t)B * S * n_kv * (g + 2) * (d / 16);
+  int blocks = (int)((items + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  dqkv_finalize_kernel<<<blocks, 256, 0, stream>>>(img, (__nv_bfloat16*)dqkv, n8);
+  dqkv_finalize_kernel<<<blocks, 256, 0, stream>>>(img, (__nv_bfloat16*)dqkv, rope_table, B * S, S, n_kv, g, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

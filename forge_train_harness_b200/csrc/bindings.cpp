@@ -240,8 +240,8 @@ std::vector<at::Tensor> flash_fwd(const at::Tensor& qkv, int64_t S, int64_t n_kv
   return {out, lse};
 }
 
-at::Tensor flash_bwd(const at::Tensor& dout, const at::Tensor& qkv, const at::Tensor& out, const at::Tensor& lse, int64_t S,
-                     int64_t n_kv, int64_t g, int64_t d) {
+at::Tensor flash_bwd(const at::Tensor& dout, const at::Tensor& qkv, const at::Tensor& out, const at::Tensor& lse,
+                     const c10::optional<at::Tensor>& rope_table, int64_t S, int64_t n_kv, int64_t g, int64_t d) {
   need_bf16(dout, "dout");
   need_bf16(qkv, "qkv");
   need_bf16(out, "out");
@@ -250,8 +250,14 @@ at::Tensor flash_bwd(const at::Tensor& dout, const at::Tensor& qkv, const at::Te
   at::Tensor dqkv = at::empty_like(qkv);
   const size_t bytes = fth_flash_bwd_scratch_bytes((int)B, (int)S, (int)n_kv, (int)g, (int)d);
   at::Tensor scratch = at::empty({(int64_t)(bytes / 4)}, qkv.options().dtype(at::kFloat));
+  const float* tab = nullptr;
+  if (rope_table.has_value()) {
+    need_f32(*rope_table, "rope_table");
+    TORCH_CHECK(rope_table->size(0) >= S && rope_table->size(1) == d, "rope table shape mismatch");
+    tab = rope_table->data_ptr<float>();
+  }
   check(fth_flash_bwd(dout.data_ptr(), qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), dqkv.data_ptr(),
-                      scratch.data_ptr(), (int)B, (int)S, (int)n_kv, (int)g, (int)d, status_ptr(), cur_stream()), "flash_bwd", 3);
+                      scratch.data_ptr(), tab, (int)B, (int)S, (int)n_kv, (int)g, (int)d, status_ptr(), cur_stream()), "flash_bwd", 3);
   return dqkv;
 }
 

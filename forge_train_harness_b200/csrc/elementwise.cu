@@ -170,13 +170,21 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(
   }
 }
 
-// main_grad[c] += sum_b partial[b][c]
+// main_grad[c] += sum_b partial[b][c].  Block = 32 columns x 32 row-slices; the slices are combined in shared memory.
 __global__ void colsum_add_kernel(const float* __restrict__ partial, float* __restrict__ out, int nb, int H) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+  __shared__ float red[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float t = 0.f;
-  for (int b = 0; b < nb; ++b) t += partial[(size_t)b * H + c];
-  out[c] += t;
+  if (c < H)
+    for (int b = threadIdx.y; b < nb; b += 32) t += partial[(size_t)b * H + c];
+  red[threadIdx.y][threadIdx.x] = t;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < H) {
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) a += red[i][threadIdx.x];
+    out[c] += a;
+  }
 }
 
 // In-place rotate-half RoPE on the q and k heads of the packed kv-group-major QKV activation.
@@ -297,7 +305,7 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, con
 }
 
 // ---- fused cross-entropy ------------------------------------------------------------------------
-constexpr int kCeThreads = 512;
+constexpr int kCeThreads = 1024;
 
 __device__ __forceinline__ void block_max_sum(float& mx, float& sm, float* red) {
   // combine per-thread (max, sum-of-exp relative to max) pairs over the block
@@ -335,17 +343,29 @@ __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(
     float lse;
     if (mode != 2) {
       float mx = -INFINITY, sm = 0.f;
-      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        bf16x8 p = grow[v];
-        if (kSmemRow) rowbuf[v] = p;
-        float f[8];
-        unpack8(p, f);
-        float m8 = f[0];
+      // four independent 16-byte loads in flight per thread
+      for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
+        bf16x8 p[4];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) m8 = fmaxf(m8, f[i]);
-        if (m8 > mx) { sm *= __expf(mx - m8); mx = m8; }
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * blockDim.x;
+          if (v < nvec) p[u] = grow[v];
+        }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sm += __expf(f[i] - mx);
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * blockDim.x;
+          if (v < nvec) {
+            if (kSmemRow) rowbuf[v] = p[u];
+            float f[8];
+            unpack8(p[u], f);
+            float m8 = f[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) m8 = fmaxf(m8, f[i]);
+            if (m8 > mx) { sm *= __expf(mx - m8); mx = m8; }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sm += __expf(f[i] - mx);
+          }
+        }
       }
       block_max_sum(mx, sm, red);
       float tgt = has ? __bfloat162float(logits[(size_t)row * V + lab]) : 0.f;
@@ -537,7 +557,7 @@ int fth_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   int grid = fth_rmsnorm_bwd_blocks(M, H);
   FTH_ROW_DISPATCH(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
                    (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, M, H, out_scale);
-  colsum_add_kernel<<<(H + 127) / 128, 128, 0, stream>>>(dw_partial, dw_main_grad, grid, H);
+  colsum_add_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(dw_partial, dw_main_grad, grid, H);
   return 0;
 }
 

@@ -48,7 +48,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, int M, int N, int K, float alpha, int accumulate,
-                 int group_m, int* __restrict__ status) {
+                 int group_m, int k_splits, int* __restrict__ status) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -61,8 +61,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + BK - 1) / BK;
+  // split-K (accumulating fp32 epilogue only): work item = (k split, tile); every split reduce-adds into C
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total_tiles = mn_tiles * k_splits;
+  const int k_blocks_all = (K + BK - 1) / BK;
+  const int k_per_split = (k_blocks_all + k_splits - 1) / k_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -88,7 +91,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // tile -> (m_blk, n_blk): groups of `group_m` row blocks, m fastest inside a group, so that
   // concurrently running CTAs share a few B tiles and a few A tiles out of L2.
-  auto tile_coords = [&](int t, int& mb, int& nb) {
+  auto tile_coords = [&](int t_all, int& mb, int& nb) {
+    const int t = t_all % mn_tiles;
     int per_group = group_m * n_tiles;
     int gidx = t / per_group, r = t % per_group;
     int m_first = gidx * group_m;
@@ -108,7 +112,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int mb, nb;
         tile_coords(t, mb, nb);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb0 = (t / mn_tiles) * k_per_split;
+        const int kb1 = min(kb0 + k_per_split, k_blocks_all);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) { ok = false; break; }
           unsigned char* sa = smem + stage * S::kStageBytes;
           unsigned char* sb = sa + S::kABytes;
@@ -143,7 +149,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb0 = (t / mn_tiles) * k_per_split;
+        const int kb1 = min(kb0 + k_per_split, k_blocks_all);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
@@ -152,7 +160,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t adesc = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024) : make_smem_desc(sa + kk * 32, 0, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024) : make_smem_desc(sb + kk * 32, 0, 1024);
-            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -307,7 +315,18 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   int tiles = m_tiles * n_tiles;
   int grid = tiles < max_ctas ? tiles : max_ctas;
   int group_m = m_tiles < 16 ? m_tiles : 16;
-  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, tc, M, N, K, alpha, accumulate, group_m, status);
+  // split-K when the output has too few tiles to fill the GPU and the epilogue accumulates anyway
+  int k_splits = 1;
+  if (OUT_F32 && accumulate) {
+    const int k_blocks = (K + BK - 1) / BK;
+    k_splits = max_ctas / tiles;                 // floor: keep everything in one wave
+    if (k_splits > k_blocks / 8) k_splits = k_blocks / 8;
+    if (k_splits < 1) k_splits = 1;
+    // every split must own at least one k block
+    while (k_splits > 1 && ((k_blocks + k_splits - 1) / k_splits) * (k_splits - 1) >= k_blocks) --k_splits;
+  }
+  grid = tiles * k_splits < max_ctas ? tiles * k_splits : max_ctas;
+  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, tc, M, N, K, alpha, accumulate, group_m, k_splits, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -327,6 +346,7 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (epi == kEpiBf16 ? (ldc % 8) : (ldc % 4)) return -2;
   if (max_ctas <= 0) max_ctas = sm_count();
+  if (bn == 0 && epi == kEpiF32Accum && N > 128) bn = 256;  // split-K fills the GPU; wide tiles reuse A best
   if (bn == 0) {
     // fewer, fatter tiles unless that leaves the last wave mostly empty
     long long t256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);

@@ -1,0 +1,163 @@
+"""Tensor-hash capture layer: blake2b-128 records of activations, gradients and losses for the alignment gates.
+
+Record format and key families follow the reference's contract (evals/harness_hook/_dump.py:89-123,
+evals/harness_hook/recipes/README.md:10-40, 64-80; emitter on the candidate side train_loop.py:95-114, 2563-2669):
+
+    {"hash": <blake2b-128 hex of the raw bytes>, "shape": [...], "dtype": "torch.bfloat16"}
+
+    step_<N>.rank<r>.mb<m>.fwd.<fqn>#<call>          level 2   module outputs
+    step_<N>.rank<r>.mb<m>.bwd.<fqn>#<call>          level 2   gradient w.r.t. the module output
+    step_<N>.rank<r>.mb<m>.loss.per_token.preallreduce   level 1   [MBS, S] fp32 NLL
+    step_<N>.rank<r>.loss.scalar.{pre,post}allreduce     level 1
+    step_<N>.rank<r>.grad.<fqn>.{pre,post}allreduce      level 1   fp32 main-grad per parameter
+
+``mb<m>.`` prefixes only fwd / bwd / per-token keys.  Level 0 makes every method a no-op.  Dumps are one JSON file
+per rank, ``<output>.rank<r>``, written atomically.  Hashing is blake2b on the HOST (the gates compare digests of raw
+bytes, so a device-side hash of another kind would not be comparable); tensors are staged device -> pinned host on a
+dedicated copy stream through a fixed ring so capture never allocates in the hot loop (evals/capture_offload.py:147-369).
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+
+import torch
+
+CHUNK = 8_000_000  # elements per blake2b update, as the reference streams
+
+
+def hash_tensor(t: torch.Tensor) -> dict:
+    h = hashlib.blake2b(digest_size=16)
+    shape, dtype = list(t.shape), str(t.dtype)
+    if t.numel():
+        flat = t.detach().reshape(-1)
+        for chunk in flat.split(CHUNK):
+            c = chunk.cpu().contiguous()
+            h.update((c if c.dtype == torch.uint8 else c.view(torch.uint8)).numpy())
+    return {"hash": h.hexdigest(), "shape": shape, "dtype": dtype}
+
+
+class StagingRing:
+    """Fixed pinned-memory ring + copy stream: ``stage(t)`` returns a CPU view valid until the slot is reused."""
+
+    def __init__(self, nbytes: int = 256 << 20, slots: int = 4, device=None):
+        self.cuda = torch.cuda.is_available() and device is not None and torch.device(device).type == "cuda"
+        self.slots = slots
+        self.bufs = [torch.empty(nbytes, dtype=torch.uint8, pin_memory=self.cuda) for _ in range(slots)] if self.cuda else []
+        self.events = [None] * slots
+        self.turn = 0
+        self.stream = torch.cuda.Stream() if self.cuda else None
+
+    def stage(self, t: torch.Tensor) -> torch.Tensor:
+        if not self.cuda or t.device.type != "cuda":
+            return t.detach().cpu()
+        nb = t.numel() * t.element_size()
+        k = self.turn
+        self.turn = (self.turn + 1) % self.slots
+        if nb > self.bufs[k].numel():
+            return t.detach().cpu()
+        if self.events[k] is not None:
+            self.events[k].synchronize()
+        dst = self.bufs[k][:nb].view(t.dtype).view(t.shape)
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            dst.copy_(t.detach(), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        t.record_stream(self.stream)
+        self.events[k] = ev
+        ev.synchronize()
+        return dst
+
+
+class CaptureSession:
+    def __init__(self, output_file: str | None, level: int = 1, rank: int = 0, fqn_alias=None, device=None):
+        self.out, self.level, self.rank = output_file, int(level), rank
+        self.records: dict[str, dict] = {}
+        self.step, self.mb = 0, 0
+        self.calls: dict[tuple, int] = {}
+        self.alias = fqn_alias or (lambda n: n)
+        self.ring = StagingRing(device=device) if self.level > 0 else None
+
+    # -- positioning ---------------------------------------------------------
+    def begin_step(self, step: int):
+        self.step, self.mb = step, 0
+        self.calls.clear()
+
+    def begin_microbatch(self, mb: int):
+        self.mb = mb
+        self.calls.clear()
+
+    def _put(self, key: str, t: torch.Tensor):
+        self.records[key] = hash_tensor(self.ring.stage(t) if self.ring else t)
+
+    # -- capture points ---------------------------------------------------------
+    def module_hook(self, kind: str, fqn: str, t: torch.Tensor):
+        if self.level < 2:
+            return
+        k = (kind, fqn)
+        idx = self.calls.get(k, 0)
+        self.calls[k] = idx + 1
+        self._put(f"step_{self.step}.rank{self.rank}.mb{self.mb}.{kind}.{self.alias(fqn)}#{idx}", t)
+
+    def per_token_loss(self, nll: torch.Tensor, micro_batch: int):
+        if self.level < 1:
+            return
+        self._put(f"step_{self.step}.rank{self.rank}.mb{self.mb}.loss.per_token.preallreduce",
+                  nll.float().view(micro_batch, -1))
+
+    def loss_scalar(self, which: str, stats: torch.Tensor):
+        if self.level < 1:
+            return
+        self._put(f"step_{self.step}.rank{self.rank}.loss.scalar.{which}allreduce", stats[:2].double())
+
+    def grads(self, which: str, store, scale=None):
+        if self.level < 1:
+            return
+        for name, g in store.grads.items():
+            t = g if scale is None else g * scale
+            self._put(f"step_{self.step}.rank{self.rank}.grad.{self.alias(name)}.{which}allreduce", t)
+
+    # -- output -----------------------------------------------------------------
+    def dump(self):
+        if self.level < 1 or not self.out:
+            return
+        path = f"{self.out}.rank{self.rank}"
+        tmp = path + ".tmp"
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(tmp, "w") as f:
+            json.dump(self.records, f)
+            f.flush()
+            os.fsync(f.fileno())
+        os.replace(tmp, path)
+
+
+def load_merged(output_file: str) -> dict:
+    """Union of every ``<output>.rank<r>`` file (harness/capture_artifacts.py:63-138)."""
+    import glob
+    out: dict = {}
+    files = sorted(glob.glob(output_file + ".rank*"))
+    if os.path.isfile(output_file):
+        files.append(output_file)
+    for fn in files:
+        if fn.endswith(".tmp"):
+            continue
+        with open(fn) as f:
+            out.update(json.load(f))
+    return out
+
+
+def diff_captures(baseline: dict, candidate: dict, *, prefix: str = "", require_baseline_complete: bool = False) -> dict:
+    """Intersect-and-diff of two hash dicts (evals/_capture_diff.py:73-248).
+
+    Zero overlap is a FAIL; with ``require_baseline_complete`` every baseline key must exist in the candidate."""
+    bk = {k for k in baseline if prefix in k}
+    ck = {k for k in candidate if prefix in k}
+    common = sorted(bk & ck)
+    mism = [k for k in common if baseline[k]["hash"] != candidate[k]["hash"]
+            or baseline[k].get("shape") != candidate[k].get("shape")]
+    missing = sorted(bk - ck)
+    ok = bool(common) and not mism and not (require_baseline_complete and missing)
+    return {"passed": ok, "overlap": len(common), "mismatched": mism, "missing_in_candidate": missing,
+            "extra_in_candidate": sorted(ck - bk)}

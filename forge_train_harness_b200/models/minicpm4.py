@@ -142,8 +142,8 @@ class ModelChunk:
         da = tp.row_output_bwd(g_h)
         ops.linear_wgrad(da, c.att, st.g(prefix + "wo.weight"), ds)
         d_att = ops.linear_dgrad(da, st.p(prefix + "wo.weight"), ds)
-        d_qkv = ops.attention_bwd(d_att, c.qkv, c.att, c.lse, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
-        ops.rope_bwd_(d_qkv, self.rope, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
+        d_qkv = ops.attention_rope_bwd(d_att, c.qkv, c.att, c.lse, self.rope, seq_len, geo.n_kv_local, geo.g_local,
+                                       geo.head_dim)
         if cfg.qk_norm:
             d_qkv = ops.qk_norm_bwd(d_qkv, c.qkv_pre, c.qk_rstd, st.p(prefix + "q_norm.weight"),
                                     st.p(prefix + "k_norm.weight"), st.g(prefix + "q_norm.weight"),

@@ -19,7 +19,7 @@ from .torch_ops import TorchOps, rope_table
 OP_NAMES = [
     "embedding_fwd", "embedding_bwd", "rmsnorm_fwd", "residual_rmsnorm_fwd", "residual_add", "rmsnorm_bwd",
     "linear_fwd", "linear_dgrad", "linear_wgrad", "rope_fwd_", "rope_bwd_", "qk_norm_fwd", "qk_norm_bwd",
-    "attention_fwd", "attention_bwd", "swiglu_fwd", "swiglu_bwd", "cross_entropy_fwd_bwd", "adamw_segments", "sumsq",
+    "attention_fwd", "attention_bwd", "attention_rope_bwd", "swiglu_fwd", "swiglu_bwd", "cross_entropy_fwd_bwd", "adamw_segments", "sumsq",
 ]
 
 

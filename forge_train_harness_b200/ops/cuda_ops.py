@@ -114,7 +114,15 @@ class Sm100Ops:
         if not Sm100Ops.attention_supported(seq_len, d):
             from .torch_ops import TorchOps
             return TorchOps.attention_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d)
-        return _C.flash_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d)
+        return _C.flash_bwd(dout, qkv, out, lse, None, seq_len, n_kv, g, d)
+
+    @staticmethod
+    def attention_rope_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d):
+        """Attention backward with the RoPE backward folded into the gradient's bf16 write-out."""
+        if not Sm100Ops.attention_supported(seq_len, d):
+            from .torch_ops import TorchOps
+            return TorchOps.attention_rope_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d)
+        return _C.flash_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d)
 
     # ---- SwiGLU ---------------------------------------------------------------
     @staticmethod

@@ -198,6 +198,11 @@ class TorchOps:
         dv5[:, :, :, g + 1, :] = dv.permute(0, 2, 1, 3).to(qkv.dtype)
         return dqkv
 
+    @staticmethod
+    def attention_rope_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d):
+        dqkv = TorchOps.attention_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d)
+        return TorchOps.rope_bwd_(dqkv, table, seq_len, n_kv, g, d)
+
     # ---- SwiGLU on packed [gate | up] ------------------------------------
     @staticmethod
     def swiglu_fwd(gate_up):

@@ -1,0 +1,66 @@
+"""Run ONE sm_100a op a few times on a small, fixed case — the program that profiler captures are taken of.
+
+    python -m forge_train_harness_b200.utils.profile_case --op flash_bwd [--iters 3]
+
+Cases (a few hundred MB on the device at most, GEMM operands larger than the 126 MB L2):
+  gemm_fwd / gemm_dgrad / gemm_wgrad   the FC1 shape of the 0.5B model at 16384 tokens (M 16384, N 8192, K 1024)
+  flash_fwd / flash_bwd                 1 x 4096 tokens, 16 query / 2 KV heads of 64
+  rmsnorm_fwd / rmsnorm_bwd / swiglu_fwd / swiglu_bwd / rope / cross_entropy    the 0.5B shapes at 16384 (CE: 4096) tokens
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True)
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args(argv)
+    from ..ops.cuda_ops import Sm100Ops as ops, _C, check_status
+    from ..ops.torch_ops import rope_table
+    dev = "cuda"
+    r = lambda *s: torch.randn(*s, device=dev, dtype=torch.float32).mul_(0.5).to(torch.bfloat16)
+    M, H, F, V, S, d, nkv, g = 16384, 1024, 4096, 73448, 4096, 64, 2, 8
+    if a.op.startswith("gemm"):
+        x, w, dy = r(M, H), r(2 * F, H), r(M, 2 * F)
+        mg = torch.zeros(2 * F, H, device=dev)
+        fn = {"gemm_fwd": lambda: _C.gemm(x, False, w, False, None, 1.0, 0, 0, 0),
+              "gemm_dgrad": lambda: _C.gemm(dy, False, w, True, None, 1.0, 0, 0, 0),
+              "gemm_wgrad": lambda: _C.gemm(dy, True, x, True, mg, 1.0, 1, 0, 0)}[a.op]
+    elif a.op in ("flash_fwd", "flash_bwd"):
+        qkv = r(S, nkv * (g + 2) * d)
+        out, lse = ops.attention_fwd(qkv, S, nkv, g, d)
+        do = r(S, nkv * g * d)
+        fn = (lambda: ops.attention_fwd(qkv, S, nkv, g, d)) if a.op == "flash_fwd" else \
+             (lambda: ops.attention_bwd(do, qkv, out, lse, S, nkv, g, d))
+    elif a.op in ("rmsnorm_fwd", "rmsnorm_bwd"):
+        x, res, w = r(M, H), r(M, H), r(H)
+        _, rstd = ops.rmsnorm_fwd(x, w, 1e-6)
+        gw = torch.zeros(H, device=dev)
+        fn = (lambda: ops.residual_rmsnorm_fwd(x, res, 0.3, w, 1e-6)) if a.op == "rmsnorm_fwd" else \
+             (lambda: ops.rmsnorm_bwd(res, x, w, rstd, gw, res))
+    elif a.op in ("swiglu_fwd", "swiglu_bwd"):
+        gu, di = r(M, 2 * F), r(M, F)
+        fn = (lambda: ops.swiglu_fwd(gu)) if a.op == "swiglu_fwd" else (lambda: ops.swiglu_bwd(di, gu))
+    elif a.op == "rope":
+        qkv, tab = r(M, nkv * (g + 2) * d), rope_table(S, d, 10000.0, dev)
+        fn = lambda: ops.rope_fwd_(qkv, tab, S, nkv, g, d)
+    elif a.op == "cross_entropy":
+        lg = r(4096, V)
+        lab = torch.randint(0, V, (4096,), device=dev, dtype=torch.int32)
+        mk = torch.ones(4096, device=dev)
+        fn = lambda: ops.cross_entropy_fwd_bwd(lg, lab, mk)
+    else:
+        raise SystemExit(f"unknown op {a.op}")
+    for _ in range(a.iters):
+        fn()
+    torch.cuda.synchronize()
+    check_status()
+    print(f"{a.op}: ok")
+
+
+if __name__ == "__main__":
+    main()

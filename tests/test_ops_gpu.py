@@ -166,6 +166,9 @@ def test_flash_bwd(ops, B, S, nkv, g, d):
     close(v[:, :, :g], v0[:, :, :g], 3e-2, 3e-2)       # dQ
     close(v[:, :, g], v0[:, :, g], 3e-2, 3e-2)         # dK
     close(v[:, :, g + 1], v0[:, :, g + 1], 3e-2, 3e-2)  # dV
+    tab = rope_table(S, d, 10000.0, "cuda")
+    fused = ops.attention_rope_bwd(dout, qkv, out, lse, tab, S, nkv, g, d)
+    close(fused, T.rope_bwd_(dqkv0.clone(), tab, S, nkv, g, d), 3e-2, 3e-2)
 
 
 def test_gemm_repeated_calls_and_views(ops):
