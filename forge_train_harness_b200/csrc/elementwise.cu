@@ -665,3 +665,61 @@ int fth_sumsq(const float* x, size_t n, double* partial, float* out, cudaStream_
 }
 
 }  // extern "C"
+
+// =====================================================================================================================
+// RMSNorm backward without any allocation (declared in noalloc.h).
+//
+// Same kernels as fth_rmsnorm_bwd above, but the per-block partial sums of the weight gradient live in a file-scope
+// device array instead of a caller-provided buffer, so a caller that cannot allocate device memory can still run it.
+// =====================================================================================================================
+namespace fth {
+constexpr int kNoAllocMaxH = 4096;       // widest row supported by this entry point
+constexpr int kNoAllocMaxBlocks = 296;   // partial rows (= thread blocks) it will launch at most
+constexpr int kNoAllocMaxDevices = 64;
+// 296 x 4096 fp32 = 4.625 MiB, resident on every GPU that loads this library until the process exits.
+static __device__ __align__(256) float g_rmsnorm_bwd_partials[kNoAllocMaxBlocks * kNoAllocMaxH];
+// Device address of the array above, per device.  The array's NAME is only a host-side handle in host code; the
+// address a kernel can use comes from cudaGetSymbolAddress, queried once per device with that device current.
+static float* g_rmsnorm_bwd_partials_addr[kNoAllocMaxDevices] = {nullptr};
+
+static int noalloc_fail(char* err, size_t err_len, int code, const char* msg) {
+  if (err != nullptr && err_len > 0) {
+    size_t i = 0;
+    for (; msg[i] != '\0' && i + 1 < err_len; ++i) err[i] = msg[i];
+    err[i] = '\0';
+  }
+  return code;
+}
+}  // namespace fth
+
+extern "C" int fth_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                       void* dx, float* dw_main_grad, int M, int H, float out_scale, cudaStream_t stream,
+                                       char* err, size_t err_len) {
+  using namespace fth;
+  if (M <= 0 || H <= 0) return noalloc_fail(err, err_len, -1, "fth_rmsnorm_bwd_noalloc: M and H must be positive");
+  if (H > kNoAllocMaxH)
+    return noalloc_fail(err, err_len, -2, "fth_rmsnorm_bwd_noalloc: H exceeds the built-in scratch (max 4096 columns); use fth_rmsnorm_bwd with your own buffer");
+  int tpr, vpt;
+  if (row_cfg(H, tpr, vpt)) return noalloc_fail(err, err_len, -3, "fth_rmsnorm_bwd_noalloc: H must be a multiple of 8");
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices)
+    return noalloc_fail(err, err_len, -4, "fth_rmsnorm_bwd_noalloc: no current CUDA device (or device ordinal >= 64)");
+  if (g_rmsnorm_bwd_partials_addr[dev] == nullptr) {
+    // one-time set-up for this device (this is why the first call should not happen inside a stream capture)
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_rmsnorm_bwd_partials) != cudaSuccess || p == nullptr)
+      return noalloc_fail(err, err_len, -5, "fth_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed for the scratch array");
+    g_rmsnorm_bwd_partials_addr[dev] = p;
+  }
+  float* partial = g_rmsnorm_bwd_partials_addr[dev];
+  const int rpb = kRowThreads / tpr;
+  int grid = (M + rpb - 1) / rpb;
+  if (grid > kNoAllocMaxBlocks) grid = kNoAllocMaxBlocks;
+  // Every launched block writes its whole partial row (zeros if it had no rows), and the column sum reads exactly
+  // `grid` rows, so nothing left in the array by an earlier call is ever read: no clearing is needed.
+  FTH_ROW_DISPATCH(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
+                   (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, partial, M, H, out_scale);
+  colsum_add_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(partial, dw_main_grad, grid, H);
+  if (cudaGetLastError() != cudaSuccess) return noalloc_fail(err, err_len, -6, "fth_rmsnorm_bwd_noalloc: kernel launch failed");
+  return 0;
+}
