@@ -40,6 +40,15 @@ size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d);
 int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const float* lse, void* dqkv, void* scratch_f32,
                   const float* rope_table, int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream);
 
+int fth_peer_barrier(void* const* pads, int rank, int world, unsigned epoch, int lane_slot, int* status, double limit_s,
+                     cudaStream_t stream);
+int fth_dp_reduce_scatter_blocks(void);
+int fth_dp_reduce_scatter(void* const* grads, const void* mc_grads, long long start, long long count, int world, int rank,
+                          double* partial, float* sumsq_accum, cudaStream_t stream);
+int fth_adamw_push(float* master, float* m, float* v, const float* grad, void* const* params, void* mc_param, int world,
+                   const void* seg_table, int n_segs, float lr, float beta1, float beta2, float eps, float weight_decay,
+                   float bc1, float rsqrt_bc2, const float* grad_scale, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

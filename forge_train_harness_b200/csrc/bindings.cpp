@@ -261,6 +261,41 @@ at::Tensor flash_bwd(const at::Tensor& dout, const at::Tensor& qkv, const at::Te
   return dqkv;
 }
 
+// ---- peer-memory collectives (pointers come from torch symmetric memory: handle.buffer_ptrs / multicast_ptr) ----------
+void peer_barrier(const std::vector<int64_t>& pads, int64_t rank, int64_t epoch, int64_t lane_slot, double limit_s) {
+  std::vector<void*> p(pads.size());
+  for (size_t i = 0; i < pads.size(); ++i) p[i] = reinterpret_cast<void*>(pads[i]);
+  check(fth_peer_barrier(p.data(), (int)rank, (int)pads.size(), (unsigned)epoch, (int)lane_slot, status_ptr(), limit_s, cur_stream()),
+        "peer_barrier");
+}
+
+void dp_reduce_scatter(const std::vector<int64_t>& grads, int64_t mc_grads, int64_t start, int64_t count, int64_t rank,
+                       at::Tensor& sumsq_accum) {
+  need_f32(sumsq_accum, "sumsq_accum");
+  std::vector<void*> p(grads.size());
+  for (size_t i = 0; i < grads.size(); ++i) p[i] = reinterpret_cast<void*>(grads[i]);
+  at::Tensor partial = at::empty({fth_dp_reduce_scatter_blocks()}, sumsq_accum.options().dtype(at::kDouble));
+  check(fth_dp_reduce_scatter(p.data(), reinterpret_cast<const void*>(mc_grads), start, count, (int)grads.size(), (int)rank,
+                              partial.data_ptr<double>(), sumsq_accum.data_ptr<float>(), cur_stream()), "dp_reduce_scatter", 2);
+}
+
+void adamw_push(at::Tensor& master, at::Tensor& m, at::Tensor& v, const at::Tensor& grad, const std::vector<int64_t>& params,
+                int64_t mc_param, const at::Tensor& table, int64_t n_segs, double lr, double beta1, double beta2, double eps,
+                double wd, int64_t step, const at::Tensor& grad_scale) {
+  need_f32(master, "master");
+  need_f32(m, "m");
+  need_f32(v, "v");
+  need_f32(grad, "grad");
+  need_f32(grad_scale, "grad_scale");
+  std::vector<void*> p(params.size());
+  for (size_t i = 0; i < params.size(); ++i) p[i] = reinterpret_cast<void*>(params[i]);
+  const double bc1 = 1.0 - std::pow(beta1, (double)step), bc2 = 1.0 - std::pow(beta2, (double)step);
+  check(fth_adamw_push(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr<float>(), p.data(),
+                       reinterpret_cast<void*>(mc_param), (int)params.size(), table.data_ptr(), (int)n_segs, (float)lr, (float)beta1,
+                       (float)beta2, (float)eps, (float)wd, (float)bc1, (float)(1.0 / std::sqrt(bc2)), grad_scale.data_ptr<float>(),
+                       cur_stream()), "adamw_push");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -280,6 +315,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("dp_reduce_scatter", &dp_reduce_scatter);
+  m.def("adamw_push", &adamw_push);
   m.def("read_status", &read_status);
   m.def("launch_count", &launch_count);
 }

@@ -107,6 +107,15 @@ class ParamStore:
             self.params[s.name] = self.flat_param[o:o + n].view(self.shapes[s.name])
             self.grads[s.name] = self.flat_grad[o:o + n].view(self.shapes[s.name])
 
+    def rebind(self, flat_param: torch.Tensor, flat_grad: torch.Tensor) -> None:
+        """Move the flat buffers (e.g. into symmetric memory); every parameter / gradient view is rebuilt."""
+        assert flat_param.numel() == self.numel and flat_grad.numel() == self.numel
+        self.flat_param, self.flat_grad = flat_param, flat_grad
+        for s in self.specs:
+            o, n = self.offsets[s.name]
+            self.params[s.name] = self.flat_param[o:o + n].view(self.shapes[s.name])
+            self.grads[s.name] = self.flat_grad[o:o + n].view(self.shapes[s.name])
+
     # -- access --------------------------------------------------------------
     def p(self, name: str) -> torch.Tensor:
         return self.params[name]

@@ -1,0 +1,79 @@
+"""Fused data-parallel gradient / parameter path (distributed optimizer over NVLink peer memory).
+
+Replaces ``reduce_scatter -> norm -> AdamW -> bf16 cast -> all_gather`` (three passes over NCCL plus three over local
+memory) with two kernels over symmetric memory:
+
+1. ``dp_reduce_scatter``: every rank PULLS its 1/dp slice of each gradient bucket from all peers with plain loads (or one
+   ``multimem.ld_reduce`` through the switch), sums in fixed rank order in fp32, writes the slice in place and produces
+   the sum of squares for the global-norm clip in the same pass.
+2. ``adamw_push``: AdamW on the owned master / moment shard; the rounded bf16 parameter is PUSHED into every rank's
+   parameter buffer by the same thread that computed it (or one ``multimem.st``), so the parameter all-gather is not a
+   separate collective at all and the next forward's first GEMM simply finds its weights in place.
+
+Ordering between ranks is three flag barriers per step (gradients complete -> pull; pulls done -> buffers reusable;
+pushes done -> parameters readable), each a bounded device-side wait.  With gradient accumulation the collectives run once
+per step after the last micro-batch; they are not interleaved with the backward (at 16 micro-batches per step the whole
+exchange is < 0.5 % of the step).  Roofline: bytes over NVLink per rank = (dp-1)/dp * 4P (pull) + (dp-1)/dp * 2P/… (push);
+see ``profiles/``.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from .symm import PeerBarrier, symm_empty
+
+
+class FusedDP:
+    def __init__(self, store, topo):
+        from ..ops.cuda_ops import Sm100Ops
+        g = topo.dp_group
+        self.store, self.topo = store, topo
+        self.grad = symm_empty(store.numel, torch.float32, store.device, g)
+        self.param = symm_empty(store.numel, store.dtype, store.device, g)
+        self.grad.tensor.zero_()
+        self.param.tensor.copy_(store.flat_param)
+        store.rebind(self.param.tensor, self.grad.tensor)
+        self.barrier = PeerBarrier(store.device, g)
+        self.sumsq = torch.zeros((), dtype=torch.float32, device=store.device)
+        self._ops = Sm100Ops
+        self._table = None
+
+    def reduce_scatter_sumsq(self, opt) -> torch.Tensor:
+        from ..ops.cuda_ops import _C
+        self.barrier(0)  # every rank's gradients are complete
+        self.sumsq.zero_()
+        for (r0, r1, _) in opt.my_ranges:
+            _C.dp_reduce_scatter(self.grad.ptrs, self.grad.mc_ptr, r0, r1 - r0, self.grad.rank, self.sumsq)
+        self.barrier(1)  # every pull is done: gradient buffers may be overwritten again
+        sq = self.sumsq.clone()
+        for (r0, r1, _) in opt.my_ranges:  # gradients that are replicas of another model-parallel rank's count once
+            for (d0, d1) in opt.dup_ranges:
+                lo, hi = max(d0, r0), min(d1, r1)
+                if hi > lo:
+                    sq = sq - opt.ops.sumsq(self.store.flat_grad[lo:hi])
+        return sq
+
+    def adam_allgather(self, opt, lr: float, scale: torch.Tensor) -> None:
+        from ..ops.cuda_ops import _C
+        oc = opt.oc
+        if self._table is None:
+            self._table = self._ops.build_adam_table(opt.segs, self.store.device)
+        buf, n = self._table
+        _C.adamw_push(opt.master, opt.m, opt.v, self.store.flat_grad, self.param.ptrs, self.param.mc_ptr, buf, n, float(lr),
+                      oc.adam_beta1, oc.adam_beta2, oc.adam_eps, oc.weight_decay, opt.step_count,
+                      scale.reshape(1).to(torch.float32))
+        self.barrier(2)  # every push has landed: parameters are readable everywhere
+
+
+def try_create(store, topo):
+    """Returns a ``FusedDP`` or None (then the NCCL path runs).  Needs bf16 parameters, dp <= 8, and symmetric memory."""
+    if store.dtype != torch.bfloat16 or topo.dp > 8:
+        return None
+    try:
+        return FusedDP(store, topo)
+    except Exception as e:  # noqa: BLE001
+        if topo.rank == 0:
+            print(f"[debug] fused DP path unavailable ({type(e).__name__}: {e}); using NCCL collectives", file=sys.stderr, flush=True)
+        return None

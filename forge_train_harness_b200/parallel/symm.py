@@ -1,0 +1,45 @@
+"""Symmetric memory over NVLink: buffers every rank of a group maps at the same offsets.
+
+Allocation and the handle exchange use ``torch.distributed._symmetric_memory`` (CUDA VMM allocations exported to the peers
+of an NCCL group, optionally also bound to an NVSwitch multicast object).  Everything that touches the memory afterwards is
+this package's own kernels (``csrc/comm_sm100.cu``): plain peer loads / stores, or ``multimem`` on the multicast mapping.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+
+class SymmBuffer:
+    def __init__(self, tensor, handle):
+        self.tensor, self.handle = tensor, handle
+        self.ptrs = [int(p) for p in handle.buffer_ptrs]
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+        self.mc_ptr = mc if os.environ.get("FORGE_MULTIMEM", "0") == "1" else 0
+        self.rank, self.world = handle.rank, handle.world_size
+
+
+def symm_empty(numel: int, dtype, device, group) -> SymmBuffer:
+    import torch.distributed._symmetric_memory as sm
+    t = sm.empty(numel, dtype=dtype, device=device)
+    h = sm.rendezvous(t, group)
+    return SymmBuffer(t, h)
+
+
+class PeerBarrier:
+    """Device-side flag barrier over a group (bounded wait; a timeout lands in the kernel status word)."""
+
+    def __init__(self, device, group, lanes: int = 4, limit_s: float = 2.0):
+        self.buf = symm_empty(8 * lanes, torch.int32, device, group)
+        self.buf.tensor.zero_()
+        torch.cuda.synchronize()
+        import torch.distributed as dist
+        dist.barrier(group=group)  # every pad is zero before the first epoch is written
+        self.epoch = [0] * lanes
+        self.limit_s = limit_s
+
+    def __call__(self, lane: int = 0):
+        from ..ops.cuda_ops import _C
+        self.epoch[lane] += 1
+        _C.peer_barrier(self.buf.ptrs, self.buf.rank, self.epoch[lane], lane, self.limit_s)

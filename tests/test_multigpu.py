@@ -1,0 +1,49 @@
+"""Multi-GPU parity on real devices: fused peer-memory DP path vs NCCL path vs one GPU; TP+SP and PP on NCCL."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run(mode, nproc, env=None):
+    e = dict(os.environ)
+    e.update(env or {})
+    e.setdefault("NCCL_NVLS_ENABLE", "0")
+    cmd = [sys.executable, "-m", "forge_train_harness_b200.runtime.launcher", "--nproc", str(nproc), "--",
+           sys.executable, os.path.join(ROOT, "tests", "_mgpu_worker.py"), mode]
+    p = subprocess.run(cmd, cwd=ROOT, env=e, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    line = [ln for ln in p.stdout.splitlines() if ln.startswith("RESULT ")][-1]
+    return json.loads(line[7:])
+
+
+def close(a, b, tol):
+    for (l0, g0), (l1, g1) in zip(a["steps"], b["steps"]):
+        assert abs(l0 - l1) / abs(l0) < tol, (a, b)
+        assert abs(g0 - g1) / abs(g0) < 10 * tol, (a, b)
+
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+@needs2
+def test_fused_dp_matches_nccl_and_single_gpu():
+    single = run("single", 1)
+    nccl = run("dp_zero", 2, {"FORGE_FUSED_DP": "0"})
+    fused = run("dp_zero", 2, {"FORGE_FUSED_DP": "1"})
+    assert fused["fused"] and not nccl["fused"]
+    close(single, nccl, 2e-2)
+    close(nccl, fused, 5e-3)
+
+
+@needs2
+def test_tp2_sp_and_pp2_match_single_gpu():
+    single = run("single", 1)
+    close(single, run("tp_sp", 2), 2e-2)
+    close(single, run("pp", 2), 2e-2)
