@@ -1,0 +1,194 @@
+"""Capture layer, verdicts, wire format, config schema, schedules, data sources (CPU)."""
+import dataclasses
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import forge_train_harness_b200 as fth
+from forge_train_harness_b200.config import schema
+from forge_train_harness_b200.data import sources
+from forge_train_harness_b200.gates import capture as cap
+from forge_train_harness_b200.gates import verdicts as V
+from forge_train_harness_b200.optim.schedule import compute_lr, wsd_lr
+from forge_train_harness_b200.parallel.pipeline import build_schedule
+from forge_train_harness_b200.utils import wire
+from tests.test_parallel_cpu import base_cfg
+
+
+# ---- wire ---------------------------------------------------------------------------------------------
+def test_wire_roundtrip_and_trailing_fields():
+    line = wire.format_loss_line(7, 3.14159265, 0.5, 1.25, 42.0, tokens_per_sec_per_gpu=1234.5)
+    r = wire.parse_loss_line(line)
+    assert (r.step, r.tag) == (7, "LOSS") and abs(r.loss - 3.14159265) < 1e-9 and r.mfu == 42.0
+    assert r.extra["tokens_per_sec_per_gpu"].startswith("1234.5")
+    assert wire.parse_loss_line("[LOSS_RES] step=3 global_loss=1.0e+00 grad_norm=2.0e+00").tag == "LOSS_RES"
+    with pytest.raises(ValueError):
+        wire.parse_loss_line("[LOSS] step=1 global_loss=nan grad_norm=1.0")
+    assert wire.parse_loss_line("[LOSS] step=1 global_loss=nan grad_norm=1.0", strict=False) is not None
+    ph = wire.parse_phase_line(wire.format_phase_line("decay", 20, 1e-3, 0.0, 0, 40, 20, False, "synthetic"))
+    assert ph["name"] == "decay" and ph["start_step"] == "20" and ph["init_weights_only"] == "0"
+    recs = wire.parse_loss_lines(" iteration 5/ 10 | lm loss: 2.5E+00 | grad norm: 1.5 |", megatron_fallback=True)
+    assert recs[0].step == 5 and recs[0].loss == 2.5
+
+
+# ---- config --------------------------------------------------------------------------------------------
+def test_schema_aliases_products_and_rejection(tmp_path):
+    doc = {"model": {"scale_emb": 10, "dim_model_base": 128, "scale_depth": 2.0, "hidden_size": 256},
+           "cli": {"num_steps": 5, "micro_batch_size": 3, "lr": 0.5, "tensor_parallel_size": 1, "world_size": 2, "gate_window": [1, 2]},
+           "env": {"NCCL_ALGO": "Tree"}}
+    c = schema.from_dict(doc)
+    assert c.model.mup_emb_scale == 10 and c.model.mup_base_hidden_size == 128 and c.model.width_mult == 2.0
+    assert c.train.num_steps == 5 and c.train.micro_batch_size == 3 and c.optim.lr == 0.5
+    with pytest.raises(KeyError):
+        schema.from_dict({"model": {"no_such_key": 1}})
+    with pytest.raises(KeyError):
+        schema.from_dict({"nonsense": {}})
+    for name in ("tiny", "minicpm4_0.5b", "minicpm4_8b", "minicpm5_1b", "qwen3_0.6b"):
+        assert schema.preset(name).qkv_dim > 0
+    # FLOPs per token of the two benchmark shapes (training, x3)
+    assert abs(schema.preset("minicpm4_0.5b").flops_per_token(False) / 3.207e9 - 1) < 1e-3
+    assert abs(schema.preset("minicpm4_8b").flops_per_token(False) / 50.53e9 - 1) < 1e-3
+
+
+def test_lr_schedules():
+    assert wsd_lr(5, 1.0, 0.1, 10, 100, 20) == 0.5
+    assert wsd_lr(50, 1.0, 0.1, 10, 100, 20) == 1.0
+    assert abs(wsd_lr(90, 1.0, 0.1, 10, 100, 20) - (0.1 + (2 * 0.5 ** 0.5 - 1) * 0.9)) < 1e-12
+    assert wsd_lr(100, 1.0, 0.1, 10, 100, 20) == pytest.approx(0.1)
+    assert wsd_lr(101, 1.0, 0.1, 10, 100, 20) == 0.1
+    oc = fth.OptimConfig(lr=1.0, min_lr=0.0, lr_warmup_iters=10, lr_decay_iters=110, lr_schedule="cosine")
+    assert compute_lr(5, oc) == 0.5 and abs(compute_lr(60, oc) - 0.5) < 1e-12 and compute_lr(200, oc) == 0.0
+
+
+# ---- data ----------------------------------------------------------------------------------------------
+def test_megatron_binary_roundtrip_and_cursor(tmp_path):
+    rng = np.random.RandomState(0)
+    docs = [rng.randint(0, 1000, size=n).astype(np.int32) for n in (50, 200, 333, 17)]
+    prefix = str(tmp_path / "corpus")
+    sources.write_megatron_binary(prefix, docs)
+    a = sources.MegatronBinary(prefix, seq_len=16, micro_batch=2, dp_rank=0, dp_size=2, seed=3)
+    b = sources.MegatronBinary(prefix, seq_len=16, micro_batch=2, dp_rank=1, dp_size=2, seed=3)
+    flat = np.concatenate(docs)
+    x = next(a)
+    assert x["tokens"].shape == (2, 16) and torch.equal(x["tokens"][:, 1:], x["labels"][:, :-1])
+    win = flat[: len(flat) // 17 * 17].reshape(-1, 17)
+    assert any((win[:, :-1] == x["tokens"][0].numpy()).all(1))
+    assert not torch.equal(x["tokens"], next(b)["tokens"])
+    seq = [next(a)["tokens"].clone() for _ in range(30)]  # crosses epochs
+    st = a.state_dict()
+    nxt = next(a)["tokens"]
+    c = sources.MegatronBinary(prefix, 16, 2, 0, 2, 3)
+    c.load_state_dict(st)
+    assert torch.equal(next(c)["tokens"], nxt)  # O(1) restore, no replay
+    d = sources.MegatronBinary(prefix, 16, 2, 0, 2, 3)
+    d.seek_microbatches(31)
+    assert torch.equal(next(d)["tokens"], nxt)
+
+
+def test_prefetcher_skips_all_masked_batches_and_tracks_consumer_state():
+    class Src:
+        def __init__(self):
+            self.i = 0
+
+        def state_dict(self):
+            return {"i": self.i}
+
+        def __next__(self):
+            self.i += 1
+            m = torch.zeros(1, 4) if self.i % 2 else torch.ones(1, 4)
+            return {"tokens": torch.full((1, 4), self.i), "labels": torch.zeros(1, 4, dtype=torch.long), "loss_mask": m}
+    pf = sources.Prefetcher(Src(), depth=4)
+    got = [int(pf.get()["tokens"][0, 0]) for _ in range(3)]
+    assert got == [2, 4, 6] and pf.state_dict() == {"i": 6}
+    pf.stop()
+    ids, lab, mk = torch.arange(8).view(1, 8), torch.arange(1, 9).view(1, 8), torch.ones(1, 8)
+    mi, ml, mm = sources.build_mtp_tensors(ids, lab, mk)
+    assert torch.equal(mi, lab) and ml[0, -1] == 0 and mm[0, -1] == 0 and torch.equal(ml[0, :-1], lab[0, 1:])
+
+
+# ---- pipeline schedule -----------------------------------------------------------------------------------
+@pytest.mark.parametrize("pp,vpp,n_mb", [(2, 1, 4), (4, 1, 8), (2, 2, 4), (4, 2, 8), (2, 2, 2)])
+def test_schedule_is_complete_and_causal(pp, vpp, n_mb):
+    for p in range(pp):
+        acts = build_schedule(pp, p, vpp, n_mb)
+        f = [(v, i) for k, v, i in acts if k == "F"]
+        b = [(v, i) for k, v, i in acts if k == "B"]
+        assert sorted(f) == sorted(b) == sorted((v, i) for v in range(vpp) for i in range(n_mb))
+        seen = set()
+        for k, v, i in acts:
+            if k == "F":
+                seen.add((v, i))
+            else:
+                assert (v, i) in seen  # a backward never precedes its forward
+        inflight = peak = 0
+        for k, _, _ in acts:
+            inflight += 1 if k == "F" else -1
+            peak = max(peak, inflight)
+        assert peak <= (pp - p - 1) * (2 if vpp > 1 else 1) + (vpp - 1) * pp + 1 or n_mb == pp
+
+
+# ---- capture + verdicts --------------------------------------------------------------------------------------
+def _run_with_capture(tmp_path, tag, level, perturb=False):
+    cfg = base_cfg(steps=2)
+    out = str(tmp_path / f"{tag}.json")
+    sess = cap.CaptureSession(out, level=level, rank=0)
+    tr = fth.Trainer(cfg, device="cpu", quiet=True, capture=sess)
+    if perturb:
+        tr.store.p("layers.1.wo.weight").mul_(1.0001)
+        tr.opt.sync_master_from_params()
+    for _ in range(2):
+        tr.train_step()
+    sess.dump()
+    tr.close()
+    return out
+
+
+def test_capture_key_families_and_alignment_verdict(tmp_path):
+    a = _run_with_capture(tmp_path, "ref", 2)
+    b = _run_with_capture(tmp_path, "ours", 2)
+    c = _run_with_capture(tmp_path, "bad", 2, perturb=True)
+    recs = cap.load_merged(a)
+    keys = set(recs)
+    assert "step_0.rank0.mb0.fwd.layers.0.wqkv#0" in keys and "step_1.rank0.mb1.bwd.layers.3.w2#0" in keys
+    assert "step_0.rank0.mb0.loss.per_token.preallreduce" in keys and "step_0.rank0.loss.scalar.postallreduce" in keys
+    assert "step_1.rank0.grad.tok_embeddings.weight.preallreduce" in keys
+    assert recs["step_0.rank0.mb0.loss.per_token.preallreduce"]["shape"] == [2, 32]
+    assert len(recs["step_0.rank0.grad.norm.weight.postallreduce"]["hash"]) == 32
+    assert V.align(a, b, ".fwd.")["passed"] and V.align(a, b, ".grad.", backward=True)["passed"]
+    bad = V.align(a, c, ".fwd.")
+    assert not bad["passed"] and any("layers.1.wo" in k for k in bad["mismatched"])
+    assert not cap.diff_captures({"x": {"hash": "1"}}, {"y": {"hash": "1"}})["passed"]  # zero overlap fails
+    lvl1 = cap.load_merged(_run_with_capture(tmp_path, "l1", 1))
+    assert not any(".fwd." in k for k in lvl1) and any(".grad." in k for k in lvl1)
+    assert cap.load_merged(_run_with_capture(tmp_path, "l0", 0)) == {}
+    t = torch.arange(10, dtype=torch.float32)
+    flipped = t.clone()
+    flipped.view(torch.int32)[3] ^= 1  # one mantissa bit
+    assert cap.hash_tensor(t)["hash"] != cap.hash_tensor(flipped)["hash"]
+
+
+def _recs(losses, tag="LOSS"):
+    return [wire.LossRecord(tag, i + 1, l, 1.0, 0.1, 40.0) for i, l in enumerate(losses)]
+
+
+def test_long_train_and_trajectory_verdicts():
+    ref = [5.0 - 0.01 * i for i in range(40)]
+    ok = V.long_train(_recs(ref), _recs([x * 1.004 for x in ref]), (1, 41), 0.01, mfu_floor=30.0)
+    assert ok["passed"] and ok["mean_rel_diff"] == pytest.approx(0.004) and ok["drift_warning"] is None
+    bad = V.long_train(_recs(ref), _recs([x * 1.03 for x in ref]), (1, 41), 0.01)
+    assert not bad["passed"] and "systematic bias" in bad["drift_warning"]
+    grow = V.window_loss_diff_metrics({i: 5.0 for i in range(40)}, {i: 5.0 + 0.0005 * (i + 1) for i in range(40)}, range(40))
+    assert "monotonically positive" in grow["drift_warning"]
+    assert not V.long_train(_recs(ref[:10]), _recs(ref), (1, 41))["passed"]  # missing window steps
+    assert V.trajectory(_recs(ref), _recs(ref))["passed"]
+    assert not V.trajectory(_recs(ref), _recs([ref[0] + 1e-9] + ref[1:]))["passed"]  # bitwise rule
+    assert V.trajectory(_recs(ref), _recs([ref[0] + 1e-9] + ref[1:]), rtol=1e-6)["passed"]  # tolerance rule
+    text = "\n".join(wire.format_loss_line(r.step, r.loss, 1.0, 0.1, 1.0, "LOSS_REF") for r in _recs(ref)) + "\n" + \
+           "\n".join(wire.format_loss_line(r.step, r.loss, 1.0, 0.1, 1.0, "LOSS_RES") for r in _recs(ref)[10:])
+    assert V.resume(text, (11, 41))["passed"]
+    assert V.resume_startup("[RESUME_STARTUP] seconds=7.16", 18)["passed"] and not V.resume_startup("x", 18)["passed"]
+    assert V.classify_failure("", timed_out=True) == "timeout" and V.classify_failure("NCCL error: unhandled") == "network"
+    assert V.classify_failure("CUDA out of memory") == "training_failure"
