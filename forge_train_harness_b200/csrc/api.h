@@ -49,6 +49,11 @@ int fth_adamw_push(float* master, float* m, float* v, const float* grad, void* c
                    const void* seg_table, int n_segs, float lr, float beta1, float beta2, float eps, float weight_decay,
                    float bc1, float rsqrt_bc2, const float* grad_scale, cudaStream_t stream);
 
+int fth_gemm_rs(const void* a, long long lda, const void* b, long long ldb, int b_mn, void* const* out_shards, long long ldo,
+                int M, int N, int K, int tp, int rank, float alpha, int* status, cudaStream_t stream);
+int fth_ag_gemm(void* const* gather, long long ldx, const void* b, long long ldb, int b_mn, void* out, long long ldo, int M, int N,
+                int K, int tp, int rank, int n_copy_ctas, int* flags, int epoch, float alpha, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -296,6 +296,32 @@ void adamw_push(at::Tensor& master, at::Tensor& m, at::Tensor& v, const at::Tens
                        cur_stream()), "adamw_push");
 }
 
+// a [M, K_local] x b -> reduce-scatter into the owners' [M/tp, N] shards (pointers into symmetric memory, zeroed by the owners).
+void gemm_rs(const at::Tensor& a, const at::Tensor& b, bool b_mn, const std::vector<int64_t>& out_shards, int64_t N, int64_t rank,
+             double alpha) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && a.dim() == 2 && a.stride(1) == 1, "a: 2-D bf16");
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "b: 2-D bf16");
+  std::vector<void*> p(out_shards.size());
+  for (size_t i = 0; i < p.size(); ++i) p[i] = reinterpret_cast<void*>(out_shards[i]);
+  check(fth_gemm_rs(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), b_mn ? 1 : 0, p.data(), N, (int)a.size(0), (int)N,
+                    (int)a.size(1), (int)p.size(), (int)rank, (float)alpha, status_ptr(), cur_stream()), "gemm_rs");
+}
+
+// gather buffers [M, K] (symmetric; own shard already written) x b -> out [M, N]; this rank's buffer ends up fully gathered.
+at::Tensor ag_gemm(const std::vector<int64_t>& gather, int64_t M, int64_t K, const at::Tensor& b, bool b_mn, int64_t rank,
+                   int64_t n_copy_ctas, at::Tensor& flags, int64_t epoch, double alpha) {
+  TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "b: 2-D bf16");
+  need_i32(flags, "flags");
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  std::vector<void*> p(gather.size());
+  for (size_t i = 0; i < p.size(); ++i) p[i] = reinterpret_cast<void*>(gather[i]);
+  at::Tensor out = at::empty({M, N}, b.options());
+  check(fth_ag_gemm(p.data(), K, b.data_ptr(), b.stride(0), b_mn ? 1 : 0, out.data_ptr(), N, (int)M, (int)N, (int)K, (int)p.size(),
+                    (int)rank, (int)n_copy_ctas, flags.data_ptr<int>(), (int)epoch, (float)alpha, status_ptr(), cur_stream()),
+        "ag_gemm");
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -315,6 +341,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
+  m.def("gemm_rs", &gemm_rs);
+  m.def("ag_gemm", &ag_gemm);
   m.def("peer_barrier", &peer_barrier);
   m.def("dp_reduce_scatter", &dp_reduce_scatter);
   m.def("adamw_push", &adamw_push);

@@ -65,6 +65,11 @@ class Trainer:
             torch.use_deterministic_algorithms(True, warn_only=True)
         self.ops = ops or get_ops(self.device)
         self.tpc = TPComm(topo.tp_group, topo.tp, topo.tp_rank, par.sequence_parallel)
+        if self.tpc.sp and self.device.type == "cuda" and par.fused_comm and self.dtype == torch.bfloat16 \
+                and os.environ.get("FORGE_FUSED_TP", "1") == "1":
+            from .parallel import fused_tp
+            self.tpc.fused = fused_tp.try_create(topo.tp_group, topo.tp, topo.tp_rank, t.micro_batch_size * m.seq_length,
+                                                 m.hidden_size, self.device)
         chunks = pipeline_chunks(m, topo.pp, par.virtual_pipeline_stages, topo.pp_rank)
         self.store = ParamStore(m, chunks, tp=topo.tp, tp_rank=topo.tp_rank, dp=topo.dp, dtype=self.dtype,
                                 device=self.device, bucket_elems=par.ddp_bucket_elems, pp=topo.pp)

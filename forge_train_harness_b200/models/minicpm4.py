@@ -99,8 +99,7 @@ class ModelChunk:
             x, n1, c.rstd1 = ops.residual_rmsnorm_fwd(x, pending, ds, w_an, cfg.norm_epsilon)
         c.x = x
         self._cap("fwd", prefix + "attention_norm", n1)
-        c.n1f = tp.col_input_fwd(n1)
-        qkv = ops.linear_fwd(c.n1f, st.p(prefix + "wqkv.weight"))
+        qkv, c.n1f = tp.col_linear_fwd(ops, n1, st.p(prefix + "wqkv.weight"))
         self._cap("fwd", prefix + "wqkv", qkv)
         if cfg.qk_norm:
             c.qkv_pre = qkv
@@ -109,17 +108,14 @@ class ModelChunk:
         ops.rope_fwd_(qkv, self.rope, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
         c.qkv = qkv
         c.att, c.lse = ops.attention_fwd(qkv, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
-        a = ops.linear_fwd(c.att, st.p(prefix + "wo.weight"))
-        a = tp.row_output_fwd(a)
+        a = tp.row_linear_fwd(ops, c.att, st.p(prefix + "wo.weight"))
         self._cap("fwd", prefix + "wo", a)
         c.h, n2, c.rstd2 = ops.residual_rmsnorm_fwd(x, a, ds, st.p(prefix + "ffn_norm.weight"), cfg.norm_epsilon)
         self._cap("fwd", prefix + "ffn_norm", n2)
-        c.n2f = tp.col_input_fwd(n2)
-        c.gu = ops.linear_fwd(c.n2f, st.p(prefix + "wfc1.weight"))
+        c.gu, c.n2f = tp.col_linear_fwd(ops, n2, st.p(prefix + "wfc1.weight"))
         self._cap("fwd", prefix + "wfc1", c.gu)
         c.inter = ops.swiglu_fwd(c.gu)
-        m = ops.linear_fwd(c.inter, st.p(prefix + "w2.weight"))
-        c.m = tp.row_output_fwd(m)
+        c.m = tp.row_linear_fwd(ops, c.inter, st.p(prefix + "w2.weight"))
         self._cap("fwd", prefix + "w2", c.m)
         if self.recompute:
             c.inter = None
@@ -129,19 +125,17 @@ class ModelChunk:
         """``g_next`` = dL/d(h + m*ds).  Returns dL/dx (without the previous layer's pending scale)."""
         ops, st, tp, geo, cfg = self.ops, self.store, self.tp, self.geo, self.cfg
         self._cap("bwd", prefix + "w2", g_next)
-        dm = tp.row_output_bwd(g_next)
         inter = c.inter if c.inter is not None else ops.swiglu_fwd(c.gu)
+        d_inter, dm = tp.row_linear_dgrad(ops, g_next, st.p(prefix + "w2.weight"), ds)
         ops.linear_wgrad(dm, inter, st.g(prefix + "w2.weight"), ds)
-        d_inter = ops.linear_dgrad(dm, st.p(prefix + "w2.weight"), ds)
         d_gu = ops.swiglu_bwd(d_inter, c.gu)
         ops.linear_wgrad(d_gu, c.n2f, st.g(prefix + "wfc1.weight"))
-        d_n2 = tp.col_input_bwd(ops.linear_dgrad(d_gu, st.p(prefix + "wfc1.weight")))
+        d_n2 = tp.col_linear_dgrad(ops, d_gu, st.p(prefix + "wfc1.weight"))
         g_h = ops.rmsnorm_bwd(d_n2, c.h, st.p(prefix + "ffn_norm.weight"), c.rstd2,
                               st.g(prefix + "ffn_norm.weight"), g_next)
         self._cap("bwd", prefix + "wo", g_h)
-        da = tp.row_output_bwd(g_h)
+        d_att, da = tp.row_linear_dgrad(ops, g_h, st.p(prefix + "wo.weight"), ds)
         ops.linear_wgrad(da, c.att, st.g(prefix + "wo.weight"), ds)
-        d_att = ops.linear_dgrad(da, st.p(prefix + "wo.weight"), ds)
         d_qkv = ops.attention_rope_bwd(d_att, c.qkv, c.att, c.lse, self.rope, seq_len, geo.n_kv_local, geo.g_local,
                                        geo.head_dim)
         if cfg.qk_norm:
@@ -150,7 +144,7 @@ class ModelChunk:
                                     st.g(prefix + "k_norm.weight"), geo.n_kv_local, geo.g_local, geo.head_dim)
         self._cap("bwd", prefix + "wqkv", d_qkv)
         ops.linear_wgrad(d_qkv, c.n1f, st.g(prefix + "wqkv.weight"))
-        d_n1 = tp.col_input_bwd(ops.linear_dgrad(d_qkv, st.p(prefix + "wqkv.weight")))
+        d_n1 = tp.col_linear_dgrad(ops, d_qkv, st.p(prefix + "wqkv.weight"))
         g_x = ops.rmsnorm_bwd(d_n1, c.x, st.p(prefix + "attention_norm.weight"), c.rstd1,
                               st.g(prefix + "attention_norm.weight"), g_h)
         return g_x

@@ -22,6 +22,38 @@ class TPComm:
     def __init__(self, group=None, size: int = 1, rank: int = 0, sequence_parallel: bool = False):
         self.group, self.size, self.rank = group, size, rank
         self.sp = bool(sequence_parallel and size > 1)
+        self.fused = None  # a parallel.fused_tp.FusedTP when the one-kernel paths are available
+
+    # -- linear + collective pairs (the places the fused kernels plug in) -----------------------
+    def _fusable(self, x, w):
+        f = self.fused
+        return f is not None and self.sp and x.dtype == torch.bfloat16 and x.is_cuda
+
+    def col_linear_fwd(self, ops, x, w, alpha=1.0):
+        """Column-parallel forward: ``(y, x_full)`` with ``y = gather(x) @ w^T``."""
+        if self._fusable(x, w) and self.fused.supports(x.shape[0] * self.size, x.shape[1]):
+            return self.fused.ag_gemm(x, w, False, alpha)
+        xf = self.col_input_fwd(x)
+        return ops.linear_fwd(xf, w, alpha), xf
+
+    def row_linear_fwd(self, ops, x, w, alpha=1.0):
+        """Row-parallel forward: ``reduce_scatter(x @ w^T)`` (all-reduce without sequence parallelism)."""
+        if self._fusable(x, w) and self.fused.supports(x.shape[0], w.shape[0]):
+            return self.fused.gemm_rs(x, w, False, alpha)
+        return self.row_output_fwd(ops.linear_fwd(x, w, alpha))
+
+    def row_linear_dgrad(self, ops, dy, w, alpha=1.0):
+        """Backward of a row-parallel linear w.r.t. its input: ``(dx, dy_full)`` with ``dx = gather(dy) @ w``."""
+        if self._fusable(dy, w) and self.fused.supports(dy.shape[0] * self.size, dy.shape[1]):
+            return self.fused.ag_gemm(dy, w, True, alpha)
+        dyf = self.row_output_bwd(dy)
+        return ops.linear_dgrad(dyf, w, alpha), dyf
+
+    def col_linear_dgrad(self, ops, dy, w, alpha=1.0):
+        """Backward of a column-parallel linear w.r.t. its input: ``reduce_scatter(dy @ w)``."""
+        if self._fusable(dy, w) and self.fused.supports(dy.shape[0], w.shape[1]):
+            return self.fused.gemm_rs(dy, w, True, alpha)
+        return self.col_input_bwd(ops.linear_dgrad(dy, w, alpha))
 
     # -- primitives ------------------------------------------------------------
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:

@@ -34,7 +34,7 @@ def main():
     torch.cuda.synchronize()
     from forge_train_harness_b200.ops.cuda_ops import check_status
     check_status()
-    fused = tr.opt.fused is not None
+    fused = (tr.opt.fused is not None) or (tr.tpc.fused is not None)
     tr.close()
     if tr.rank == 0:
         print("RESULT " + json.dumps({"mode": mode, "fused": fused, "steps": out}), flush=True)

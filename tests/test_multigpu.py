@@ -43,7 +43,11 @@ def test_fused_dp_matches_nccl_and_single_gpu():
 
 
 @needs2
-def test_tp2_sp_and_pp2_match_single_gpu():
+def test_tp2_sp_fused_and_nccl_and_pp2_match_single_gpu():
     single = run("single", 1)
-    close(single, run("tp_sp", 2), 2e-2)
+    nccl = run("tp_sp", 2, {"FORGE_FUSED_TP": "0"})
+    fused = run("tp_sp", 2, {"FORGE_FUSED_TP": "1"})
+    assert fused["fused"] and not nccl["fused"]
+    close(single, nccl, 2e-2)
+    close(single, fused, 2e-2)
     close(single, run("pp", 2), 2e-2)
