@@ -98,43 +98,53 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (is_copy_cta) {
     // ---------------- all-gather copy CTA: one thread drives bulk copies peer -> shared -> local ----------------
+    // The CTA's blocks are one flat stream of 32 KiB pieces through a ring of shared-memory slots: loads run up to
+    // kCopySlots - 2 pieces ahead of the stores (also across block boundaries); a block's flag is published when its
+    // last store has completed.
     if (threadIdx.x == 0) {
       const long long blk_bytes = (long long)CBM * ca.row_bytes;
-      uint32_t ph[kCopySlots];
-      for (int s = 0; s < kCopySlots; ++s) ph[s] = 0;
-      bool ok = true;
-      int idx = 0;  // running index over remote blocks, dealt round-robin to the copy CTAs
-      for (int dq = 1; dq < ca.tp && ok; ++dq) {
-        const int q = (ca.rank + dq) % ca.tp;
-        for (int bi = 0; bi < tiles_per_rank && ok; ++bi, ++idx) {
-          if (idx % n_copy != (int)blockIdx.x) continue;
-          const int mb = q * tiles_per_rank + bi;
-          const char* src = reinterpret_cast<const char*>(ca.peer_x[q]) + (long long)mb * blk_bytes;
-          char* dst = reinterpret_cast<char*>(ca.local_x) + (long long)mb * blk_bytes;
-          for (long long off = 0; off < blk_bytes && ok; off += (long long)kCopySlots * kCopyPiece) {
-            tma_wait_group_read<0>();  // every slot's previous store has read its shared memory
-            int issued = 0;
-            for (int s = 0; s < kCopySlots; ++s) {
-              const long long o = off + (long long)s * kCopyPiece;
-              if (o >= blk_bytes) break;
-              const uint32_t bytes = (uint32_t)min((long long)kCopyPiece, blk_bytes - o);
-              mbar_expect_tx(&copy_bar[s], bytes);
-              bulk_g2s(smem + s * kCopyPiece, src + o, bytes, &copy_bar[s]);
-              ++issued;
-            }
-            for (int s = 0; s < issued; ++s) {
-              const long long o = off + (long long)s * kCopyPiece;
-              const uint32_t bytes = (uint32_t)min((long long)kCopyPiece, blk_bytes - o);
-              if (!mbar_wait(&copy_bar[s], ph[s], abort_flag, status, kTimeoutPeerFlag)) { ok = false; break; }
-              ph[s] ^= 1;
-              bulk_s2g(dst + o, smem + s * kCopyPiece, bytes);
-              tma_commit_group();
-            }
-          }
-          tma_wait_group<0>();  // the block is in local memory
+      const int ppb = (int)((blk_bytes + kCopyPiece - 1) / kCopyPiece);   // pieces per block
+      const int n_remote = (ca.tp - 1) * tiles_per_rank;
+      int n_mine = 0;
+      for (int i = (int)blockIdx.x; i < n_remote; i += n_copy) ++n_mine;
+      const int total = n_mine * ppb;
+      // piece j -> (remote block index i, offset)
+      auto locate = [&](int j, const char*& src, char*& dst, uint32_t& bytes, int& mb, bool& last) {
+        const int i = (int)blockIdx.x + (j / ppb) * n_copy;
+        const int q = (ca.rank + 1 + i / tiles_per_rank) % ca.tp;
+        mb = q * tiles_per_rank + i % tiles_per_rank;
+        const long long o = (long long)(j % ppb) * kCopyPiece;
+        bytes = (uint32_t)min((long long)kCopyPiece, blk_bytes - o);
+        src = reinterpret_cast<const char*>(ca.peer_x[q]) + (long long)mb * blk_bytes + o;
+        dst = reinterpret_cast<char*>(ca.local_x) + (long long)mb * blk_bytes + o;
+        last = (j % ppb) == ppb - 1;
+      };
+      auto issue_load = [&](int j) {
+        const char* src; char* dst; uint32_t bytes; int mb; bool last;
+        locate(j, src, dst, bytes, mb, last);
+        const int sl = j % kCopySlots;
+        mbar_expect_tx(&copy_bar[sl], bytes);
+        bulk_g2s(smem + sl * kCopyPiece, src, bytes, &copy_bar[sl]);
+      };
+      int loaded = 0;
+      for (; loaded < total && loaded < kCopySlots; ++loaded) issue_load(loaded);
+      for (int j = 0; j < total; ++j) {
+        const char* src; char* dst; uint32_t bytes; int mb; bool last;
+        locate(j, src, dst, bytes, mb, last);
+        const int sl = j % kCopySlots;
+        if (!mbar_wait(&copy_bar[sl], (uint32_t)((j / kCopySlots) & 1), abort_flag, status, kTimeoutPeerFlag)) break;
+        bulk_s2g(dst, smem + sl * kCopyPiece, bytes);
+        tma_commit_group();
+        if (last) {
+          tma_wait_group<0>();          // every store of this block has completed
           fence_proxy_async_all();
           __threadfence();
           st_release_gpu(ca.flags + mb, ca.epoch);
+        }
+        if (j >= 1 && loaded < total) {
+          tma_wait_group_read<1>();     // store j-1 has read its slot: reuse it for the next load
+          issue_load(loaded);           // loaded == j - 1 + kCopySlots, same slot as piece j - 1
+          ++loaded;
         }
       }
       tma_wait_group<0>();
@@ -369,7 +379,12 @@ int fth_ag_gemm(void* const* gather, long long ldx, const void* b, long long ldb
   }
   CommArgs ca = {};
   ca.mode = 2; ca.tp = tp; ca.rank = rank; ca.rows_per_rank = M / tp;
-  ca.n_copy_ctas = tp > 1 ? (n_copy_ctas > 0 ? n_copy_ctas : 8) : 0;
+  {
+    const int n_remote = (tp - 1) * (M / tp / CBM);
+    int want = n_copy_ctas > 0 ? n_copy_ctas : 16;
+    if (want > n_remote) want = n_remote;
+    ca.n_copy_ctas = tp > 1 ? want : 0;
+  }
   if (tp == 1) ca.mode = 0;
   ca.epoch = epoch; ca.flags = flags;
   for (int q = 0; q < 8; ++q) ca.peer_x[q] = gather[q < tp ? q : 0];

@@ -21,7 +21,7 @@ from .symm import PeerBarrier, symm_empty
 
 
 class FusedTP:
-    def __init__(self, group, tp: int, rank: int, M: int, H: int, device, n_copy_ctas: int = 8):
+    def __init__(self, group, tp: int, rank: int, M: int, H: int, device, n_copy_ctas: int = 0):
         self.tp, self.rank, self.M, self.H, self.Ms = tp, rank, M, H, M // tp
         self.gather = [symm_empty(M * H, torch.bfloat16, device, group) for _ in range(2)]
         self.shard = [symm_empty(self.Ms * H, torch.bfloat16, device, group) for _ in range(2)]

@@ -1,0 +1,59 @@
+"""Whole-engine runs on one GPU: sm_100a ops vs the plain-PyTorch ops on the same device, CUDA-graph replay, MTP, q/k-norm."""
+import dataclasses
+
+import pytest
+import torch
+
+import forge_train_harness_b200 as fth
+
+pytestmark = pytest.mark.gpu
+
+
+def cfg_for(kind, graph=False, steps=3):
+    m = dataclasses.replace(fth.preset("tiny"), num_layers=2, seq_length=256, padded_vocab_size=4096, hidden_size=256,
+                            ffn_hidden_size=512, num_attention_heads=4, num_query_groups=2, head_dim=64)
+    if kind == "mtp":
+        m = dataclasses.replace(m, tie_embeddings=False, mtp_num_layers=1, mtp_loss_weight=0.3)
+    if kind == "qwen":
+        m = dataclasses.replace(m, qk_norm=True, use_mup=False, head_dim=128, num_attention_heads=2, num_query_groups=1)
+    return fth.RunConfig(model=m, optim=fth.OptimConfig(lr=2e-3, lr_schedule="constant"),
+                         train=fth.TrainConfig(num_steps=steps, micro_batch_size=2, grad_accum_steps=2, seed=11, dtype="bf16",
+                                               cuda_graph=graph),
+                         data=fth.DataConfig(prefetch_size=0))
+
+
+def run(cfg, ops=None):
+    tr = fth.Trainer(cfg, device="cuda:0", ops=ops, quiet=True)
+    out = []
+    for _ in range(cfg.train.num_steps):
+        r = tr.train_step()
+        out.append((float(r["loss"]), float(r["grad_norm"])))
+    used_graph = tr._graph is not None
+    tr.close()
+    torch.cuda.synchronize()
+    from forge_train_harness_b200.ops.cuda_ops import check_status
+    check_status()
+    return out, used_graph
+
+
+def baseline_ops():
+    from forge_train_harness_b200.ops import RoutedOps, TorchOps
+    return RoutedOps({"baseline": TorchOps}, "baseline")
+
+
+@pytest.mark.parametrize("kind", ["plain", "mtp", "qwen"])
+def test_sm100_ops_match_pytorch_ops(kind):
+    cfg = cfg_for(kind)
+    ref, _ = run(cfg, baseline_ops())
+    got, _ = run(cfg)
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) / abs(l0) < 1e-2, (ref, got)
+        assert abs(g0 - g1) / abs(g0) < 1e-1, (ref, got)
+
+
+def test_cuda_graph_replay_matches_eager():
+    eager, g0 = run(cfg_for("plain", graph=False, steps=4))
+    graph, g1 = run(cfg_for("plain", graph=True, steps=4))
+    assert g1 and not g0
+    for (l0, n0), (l1, n1) in zip(eager, graph):
+        assert abs(l0 - l1) / abs(l0) < 2e-3 and abs(n0 - n1) / abs(n0) < 2e-2, (eager, graph)
