@@ -303,7 +303,7 @@ constexpr int kFwd2Threads = 576;  // warps 0-15 softmax (2 tiles x 2 column hal
 template <int D>
 __global__ void __launch_bounds__(kFwd2Threads, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out,
-                 int S, int n_kv, int g, float scale_log2, int* __restrict__ status) {
+                 int S, int n_kv, int g, float scale_log2, int* __restrict__ status, long long* __restrict__ dbg) {
   using L = FwdSmem<D>;
   constexpr int KS = L::kStages;
   extern __shared__ unsigned char smem_raw[];
@@ -455,8 +455,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
     float m_run = -INFINITY, l_run = 0.f;
     uint32_t ph_s = 0, ph_o = 0, ph_x = 0;
     bool ok = true;
+    const bool rec = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 0 || warp == 8) && lane == 0;
+    long long* drow = dbg + (warp / 8) * 8 * 64;
+#define FTH_TS(i) do { if (rec && kb < 64) drow[(i) * 64 + kb] = clock64(); } while (0)
     for (int kb = 0; kb < nb && ok; ++kb) {
+      FTH_TS(0);
       if (!mbar_wait(&s_full[t], ph_s, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      FTH_TS(1);
       ph_s ^= 1;
       tc_fence_after();
       const bool diag = (kb * 128 + 127 > q0 + t * 128);
@@ -465,6 +470,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       tmem_ld_32x32(tm_s[t] + lane_off + s_col, sr);
       tmem_ld_32x32(tm_s[t] + lane_off + s_col + 32, sr + 32);
       tmem_wait_ld();
+      FTH_TS(2);
       if (diag) {
 #pragma unroll
         for (int e = 0; e < 64; ++e)
@@ -484,6 +490,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       mbar_arrive(&xbar[t]);
       if (!mbar_wait(&xbar[t], ph_x, abort_flag, status, kTimeoutGeneric)) { ok = false; break; }
       ph_x ^= 1;
+      FTH_TS(3);
       mx = fmaxf(mx, slot[(hh ^ 1) * 128 + r]) * scale_log2;
       float m_new = fmaxf(m_run, mx);
       float m_use = (m_new - m_run > kRescaleThreshold) ? m_new : m_run;
@@ -509,6 +516,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       }
       l_run = l_run * alpha + ((rs0 + rs1) + (rs2 + rs3));
       m_run = m_use;
+      FTH_TS(4);
       if (kb > 0) {
         if (!mbar_wait(&o_done[t], ph_o, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
         ph_o ^= 1;
@@ -525,10 +533,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
           }
         }
       }
+      FTH_TS(5);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
+      FTH_TS(6);
     }
+#undef FTH_TS
     if (nb > 0 && ok) {
       if (mbar_wait(&o_done[t], ph_o, abort_flag, status, kTimeoutTmemEmpty)) {
         tc_fence_after();
@@ -1218,6 +1229,10 @@ using namespace fth;
 extern "C" {
 
 // qkv: [B*S, n_kv*(g+2)*d] bf16 packed; out: [B*S, n_kv*g*d] bf16; lse: [B, n_kv*g, S] fp32.  S % 128 == 0, d in {64,128}.
+static long long* g_fwd_dbg = nullptr;
+// Optional timeline buffer (2 x 8 x 64 clock64 stamps of CTA (0,0,0)'s softmax phases); nullptr disables.
+void fth_flash_fwd_set_debug(long long* buf) { g_fwd_dbg = buf; }
+
 int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv, int g, int d, int* status,
                   cudaStream_t stream) {
   if (S % 128 || (d != 64 && d != 128)) return -2;
@@ -1230,11 +1245,11 @@ int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv
   if (d == 64) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(flash_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::kTotal); set = true; }
-    flash_fwd2_kernel<64><<<grid, kFwd2Threads, FwdSmem<64>::kTotal, stream>>>(tm, (__nv_bfloat16*)out, lse, S, n_kv, g, scale_log2, status);
+    flash_fwd2_kernel<64><<<grid, kFwd2Threads, FwdSmem<64>::kTotal, stream>>>(tm, (__nv_bfloat16*)out, lse, S, n_kv, g, scale_log2, status, g_fwd_dbg);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(flash_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kTotal); set = true; }
-    flash_fwd2_kernel<128><<<grid, kFwd2Threads, FwdSmem<128>::kTotal, stream>>>(tm, (__nv_bfloat16*)out, lse, S, n_kv, g, scale_log2, status);
+    flash_fwd2_kernel<128><<<grid, kFwd2Threads, FwdSmem<128>::kTotal, stream>>>(tm, (__nv_bfloat16*)out, lse, S, n_kv, g, scale_log2, status, g_fwd_dbg);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -148,7 +148,7 @@ class Trainer:
         if self.capture is not None:
             self.capture.per_token_loss(out["nll"], self.cfg.train.micro_batch_size)
         stats = self._mb_stats(out, batch)
-        ch.backward(batch, cache)
+        ch.run_backward(batch, cache)
         return stats
 
     def _try_capture_graph(self, batch: dict):
@@ -230,7 +230,7 @@ class Trainer:
                     self.links.send_act(out)
             else:
                 g_out = None if ch.spec.has_head else self.links.recv_grad(shape, self.dtype, self.device)
-                g_in = ch.backward(batches[i], caches.pop((v, i)), g_out)
+                g_in = ch.run_backward(batches[i], caches.pop((v, i)), g_out)
                 if g_in is not None:
                     self.links.send_grad(g_in)
         self.links.drain()

@@ -48,6 +48,7 @@ def main(argv=None):
     ap.add_argument("--threshold", type=float, default=0.01)
     ap.add_argument("--out", default="gates_out")
     ap.add_argument("--timeout", type=float, default=1500.0)
+    ap.add_argument("--split-logs", default="", help="also write <dir>/ref/ref.log and <dir>/ours/ours.log (dispatcher layout)")
     a = ap.parse_args(argv)
     m = preset(a.model)
     if a.layers:
@@ -115,6 +116,11 @@ def main(argv=None):
     o = subprocess.run(ours_cmd, cwd=ROOT, capture_output=True, text=True, timeout=a.timeout)
     open(os.path.join(out, "ours.log"), "w").write(o.stdout + "\n--- stderr ---\n" + o.stderr[-20000:])
     our_recs = wire.parse_loss_lines(o.stdout, strict=False)
+    if a.split_logs:
+        for side, text in (("ref", r.stdout), ("ours", o.stdout)):
+            os.makedirs(os.path.join(a.split_logs, side), exist_ok=True)
+            if side == "ref" or not os.path.isfile(os.path.join(a.split_logs, side, "ours.log")):
+                open(os.path.join(a.split_logs, side, f"{side}.log"), "w").write(text)
     # ---- (3) verdict ---------------------------------------------------------------------------------------------
     res = {"model": m.name, "layers": m.num_layers, "nproc": a.nproc, "global_batch": gbs, "steps": a.steps,
            "ref_rc": r.returncode, "ours_rc": o.returncode, "ref_steps": len(ref_recs), "ours_steps": len(our_recs)}

@@ -1,0 +1,102 @@
+"""Harness command line (the counterpart of ``bin/harness`` -> harness/cli.py:70-213).
+
+    python -m forge_train_harness_b200.harness run <suite> [--registry configs/eval/dense_training.toml] [--timeout S] [--arg k=v]
+    python -m forge_train_harness_b200.harness guard | anti-proxy | unit | info | doctor | echo-config <toml> | render <gate.toml> ...
+
+Local suites (``guard``, ``anti-proxy``, ``unit``) run in-process / as a pytest child; gate suites go request -> dispatcher ->
+result JSON between the result markers.  Timeout precedence: ``--timeout`` > ``HARNESS_RUN_TIMEOUT_S`` > the registry value.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+
+from ..config import schema
+from . import dispatcher, guards, render
+from . import run_schema as RS
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _timeout(cli_value, registry_value):
+    if cli_value:
+        return float(cli_value)
+    env = os.environ.get("HARNESS_RUN_TIMEOUT_S")
+    return float(env) if env else float(registry_value)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="harness")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    r = sub.add_parser("run")
+    r.add_argument("suite")
+    r.add_argument("--registry", default=os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    r.add_argument("--timeout", type=float, default=0.0)
+    r.add_argument("--arg", action="append", default=[])
+    r.add_argument("--artifacts", default=os.path.join(ROOT, ".artifacts", "runs"))
+    for name in ("guard", "anti-proxy", "unit", "info", "doctor"):
+        sub.add_parser(name)
+    e = sub.add_parser("echo-config")
+    e.add_argument("path")
+    rn = sub.add_parser("render")
+    rn.add_argument("gate")
+    rn.add_argument("--model", required=True)
+    rn.add_argument("--optim", required=True)
+    rn.add_argument("--registry", default=os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    a = ap.parse_args(argv)
+
+    if a.cmd == "guard":
+        res = guards.framework_guard()
+        print(json.dumps(res))
+        return 0 if res["passed"] else 1
+    if a.cmd == "anti-proxy":
+        res = guards.anti_proxy_guard()
+        print(json.dumps(res))
+        return 0 if res["passed"] else 1
+    if a.cmd == "unit":
+        return subprocess.call([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests"), "-q", "-m", "not gpu"])
+    if a.cmd == "info":
+        print(json.dumps({"result_markers": [RS.RESULT_BEGIN, RS.RESULT_END], "runner_metrics": RS.RUNNER_METRICS,
+                          "schema_version": RS.RUN_SCHEMA_VERSION}, indent=1))
+        return 0
+    if a.cmd == "doctor":
+        import torch
+        info = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available(),
+                "extension_built": os.path.isfile(os.path.join(ROOT, "forge_train_harness_b200", "_C.so")),
+                "reference_installed": os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "training_engine_tensor"))}
+        if torch.cuda.is_available():
+            info["gpus"] = [torch.cuda.get_device_name(i) for i in range(torch.cuda.device_count())]
+        print(json.dumps(info, indent=1))
+        return 0
+    if a.cmd == "echo-config":
+        import dataclasses
+        cfg = schema.load(a.path)
+        print(json.dumps({k: dataclasses.asdict(getattr(cfg, k)) for k in ("model", "optim", "parallel", "train", "data", "ckpt")}, indent=1))
+        return 0
+    if a.cmd == "render":
+        reg = render.load_toml(a.registry)
+        prods = render.render_gate(render.load_toml(a.gate), render.load_toml(a.model)["model"], render.load_toml(a.optim)["optim"],
+                                   reg.get("env", {}), reg.get("defaults", {}).get("seed", 1234))
+        for side in ("ref", "ours"):
+            print(f"# ---- {side} product ----\n" + render.dumps_product(prods[side]))
+        return 0
+    # run <suite>
+    reg = render.load_toml(a.registry)
+    gate = reg.get("evals", {}).get(a.suite, {})
+    args = dict(kv.split("=", 1) for kv in a.arg)
+    args["timeout_s"] = _timeout(a.timeout, gate.get("timeout_s", 600))
+    req = RS.make_run_request(a.suite, args, gate.get("gpu_count", 1))
+    art = os.path.join(a.artifacts, req["run_id"])
+    os.makedirs(art, exist_ok=True)
+    with open(os.path.join(art, "request.json"), "w") as f:
+        json.dump(req, f, indent=1)
+    res = dispatcher.run_suite(req, reg, ROOT, art, cache_dir=os.path.join(ROOT, ".artifacts", "ref_cache"))
+    RS.emit_result(res, sys.stdout)
+    return 0 if res["status"] == "passed" else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

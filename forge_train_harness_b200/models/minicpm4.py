@@ -206,7 +206,7 @@ class ModelChunk:
             out["mtp_nll"] = self._mtp_fwd(batch, cache, S)
         return out, cache
 
-    def backward(self, batch: dict, cache: ChunkCache, g_out: torch.Tensor | None = None):
+    def run_backward(self, batch: dict, cache: ChunkCache, g_out: torch.Tensor | None = None):
         """Accumulates weight gradients; returns dL/dx_in (None on an embedding chunk)."""
         S = batch["seq_len"]
         if self.spec.has_head:

@@ -1,0 +1,111 @@
+"""Harness control plane on CPU: schema, renderer, guards, MFU bar, dispatcher with fake side scripts, real CPU gates."""
+import json
+import os
+import sys
+
+import pytest
+
+from forge_train_harness_b200.harness import dispatcher, guards, mfu, render
+from forge_train_harness_b200.harness import run_schema as RS
+from forge_train_harness_b200.harness.cli import main as cli_main
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_run_schema_roundtrip_and_validation():
+    req = RS.make_run_request("long-train", {"x": 1})
+    RS.validate_run_request(req)
+    bad = dict(req, artifact_relpath="../escape")
+    with pytest.raises(ValueError):
+        RS.validate_run_request(bad)
+    res = RS.make_run_result("long-train", True, "ok", {"mean_rel_diff": 0.0, "max_rel_diff": 0.0, "threshold": 0.01})
+    RS.validate_run_result(res, "long_train")
+    with pytest.raises(ValueError):
+        RS.validate_run_result(RS.make_run_result("x", True, "ok", {}), "long_train")
+    import io
+    buf = io.StringIO()
+    RS.emit_result(res, buf)
+    assert RS.extract_result("noise\n" + buf.getvalue() + "more") == res and RS.extract_result("nothing") is None
+
+
+def test_render_layers_overrides_unset_and_transport_split():
+    gate = render.load_toml(os.path.join(ROOT, "configs", "eval", "gate_config", "long-train.toml"))
+    reg = render.load_toml(os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    model = {"num_layers": 24, "hidden_size": 1024}
+    optim = {"lr": 3e-4, "lr_warmup_iters": 2000}
+    p = render.render_gate(gate, model, optim, reg["env"], 1234)
+    assert p["ref"]["cli"]["micro_batch_size"] == 2 and p["ours"]["cli"]["micro_batch_size"] == 4  # side override wins
+    assert p["ref"]["cli"]["grad_accum_steps"] == 20 and p["ours"]["cli"]["grad_accum_steps"] == 10
+    assert p["ours"]["cli"]["lr_warmup_iters"] == 0 and p["ours"]["cli"]["seed"] == 1234
+    assert "NCCL_NVLS_ENABLE" in p["ref"]["env"] and "NCCL_NVLS_ENABLE" not in p["ours"]["env"]  # "@unset" tombstone
+    assert p["ours"]["env"]["NUM_PROCS"] == 2 and p["ours"]["env"]["DETERMINISTIC"] is False
+    assert not any(k.startswith("review_") or k.startswith("mfu_elastic") for k in p["ours"]["cli"])  # review-only keys stripped
+    text = render.dumps_product(p["ours"])
+    import tomllib
+    assert tomllib.loads(text)["cli"]["gate_window"] == [101, 201]
+    env = render.product_env({"cli": {"a": True, "w": [1, 2], "r": "<runtime>", "p": "<auto-port>"}, "env": {"X": "y"}}, lambda: 4242)
+    assert env == ["export A='1'", "export W='1 2'", "export P='4242'", "export X='y'"]
+
+
+def test_guards_pass_on_engine_and_catch_violations(tmp_path):
+    assert guards.framework_guard()["passed"] and guards.anti_proxy_guard()["passed"]
+    (tmp_path / "models").mkdir()
+    (tmp_path / "models" / "bad.py").write_text('"""torch.optim in a docstring is fine"""\nimport torch\n# loss.backward( in a comment is fine\n'
+                                                "opt = torch.optim.AdamW([])\nx.sum().backward()\nimport training_engine_tensor\n")
+    v = {w for _, w in guards.framework_guard(str(tmp_path))["violations"]}
+    assert v == {"torch.optim", ".backward("}
+    assert not guards.anti_proxy_guard(str(tmp_path))["passed"]
+
+
+def test_mfu_history_and_elastic_bar(tmp_path):
+    h = str(tmp_path / "mfu_history.jsonl")
+    for suite, v, ok in [("long-train", 37.0, True), ("long-train-smoke", 50.0, True), ("long-train", 38.4, True),
+                         ("long-train", 45.0, False), ("long-train", 38.6, True), ("long-train", 38.5, None)]:
+        mfu.record(h, suite, v, ok)
+    s = mfu.qualifying(mfu.load(h))
+    assert s == [37.0, 38.4, 38.6, 38.5]  # smoke runs and failed-loss runs never count
+    assert mfu.evaluate(s, 38.0) == (True, "STRICT_PASS")
+    assert mfu.evaluate(s, 40.0) == (True, "ELASTIC_PASS")          # plateau within 2 pp of the bar, spread <= 0.5
+    assert mfu.evaluate(s[:2], 40.0) == (False, "IN_BAND_INSUFFICIENT_HISTORY")
+    assert mfu.evaluate([36.0, 38.4, 39.9], 40.0) == (False, "IN_BAND_UNSTABLE")
+    assert mfu.evaluate(s, 45.0) == (False, "BELOW_BAND") and mfu.evaluate([], 1.0) == (False, "NO_QUALIFYING_RUNS")
+
+
+def _fake(lines, rc=0, sleep=0.0):
+    body = "import sys,time\n" + "".join(f"print({ln!r})\n" for ln in lines) + f"time.sleep({sleep})\nsys.exit({rc})\n"
+    return [sys.executable, "-c", body]
+
+
+def _loss(step, v, tag="LOSS"):
+    return f"[{tag}] step={step} global_loss={v:.9e} grad_norm=1.000000000e+00 time_s=0.1 mfu_e2e_standard=40.0"
+
+
+def test_dispatcher_three_steps_cache_and_failure_classes(tmp_path):
+    ref = [_loss(i, 5.0 - 0.01 * i) for i in range(1, 31)]
+    reg = {"evals": {"lt": {"needs_ref": True, "verdict": "long_train", "gate_window": [1, 31], "loss_rel_threshold": 0.01,
+                            "ref_cmd": _fake(ref), "ours_cmd": _fake([_loss(i, (5.0 - 0.01 * i) * 1.002) for i in range(1, 31)])},
+                     "bad": {"needs_ref": True, "verdict": "long_train", "gate_window": [1, 31], "ref_cmd": _fake(ref),
+                             "ours_cmd": _fake(["RuntimeError: CUDA out of memory"], rc=1)},
+                     "slow": {"needs_ref": False, "verdict": "resume_startup", "timeout_s": 1, "ours_cmd": _fake([], sleep=30)}}}
+    cache = str(tmp_path / "cache")
+    r1 = dispatcher.run_suite(RS.make_run_request("lt"), reg, ROOT, str(tmp_path / "a"), cache)
+    assert r1["status"] == "passed" and r1["details"]["ref_cache"] == "miss" and abs(r1["metrics"]["mean_rel_diff"] - 0.002) < 1e-6
+    RS.validate_run_result(r1, "long_train")
+    r2 = dispatcher.run_suite(RS.make_run_request("lt"), reg, ROOT, str(tmp_path / "b"), cache)
+    assert r2["details"]["ref_cache"] == "hit" and os.path.isfile(tmp_path / "b" / "result.json")
+    r3 = dispatcher.run_suite(RS.make_run_request("bad"), reg, ROOT, str(tmp_path / "c"), cache)
+    assert r3["status"] == "failed" and r3["details"]["failure_class"] == "training_failure" and r3["details"]["side"] == "ours"
+    r4 = dispatcher.run_suite(RS.make_run_request("slow", {"timeout_s": 1}), reg, ROOT, str(tmp_path / "d"), None)
+    assert r4["status"] == "failed" and r4["details"]["failure_class"] == "timeout"
+    assert dispatcher.run_suite(RS.make_run_request("nope"), reg, ROOT, str(tmp_path / "e"))["status"] == "failed"
+
+
+def test_cli_runs_real_cpu_gates(tmp_path, capsys):
+    rc = cli_main(["run", "resume-gate", "--artifacts", str(tmp_path)])
+    out = capsys.readouterr().out
+    res = RS.extract_result(out)
+    assert rc == 0 and res["status"] == "passed" and res["metrics"]["max_abs_loss_diff"] == 0.0, res
+    rc = cli_main(["run", "production-train", "--artifacts", str(tmp_path)])
+    res = RS.extract_result(capsys.readouterr().out)
+    assert rc == 0 and res["metrics"]["missing"] == [], res
+    assert cli_main(["guard"]) == 0 and cli_main(["info"]) == 0
