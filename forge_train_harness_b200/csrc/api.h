@@ -37,6 +37,7 @@ int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv
                   cudaStream_t stream);
 
 void fth_flash_fwd_set_debug(long long* buf);
+void fth_flash_bwd_set_debug(long long* buf);
 size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d);
 int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const float* lse, void* dqkv, void* scratch_f32,
                   const float* rope_table, int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream);

@@ -13,6 +13,7 @@
 // Replaces flash_attn_func / _flash_attn_backward (FA2, mma.sync) at forward.py:204-235 and backward.py:473-527.
 // Q/K/V are read in place from the QKV GEMM output through one 2-D tensor map (no .contiguous() copies of K and V,
 // forward.py:83-93), and the backward writes dQ/dK/dV straight into the packed layout the QKV wgrad/dgrad consume.
+#include <type_traits>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -599,6 +600,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
 // the query heads of a KV group, i.e. over CTAs) use the same path.  A finalize kernel rounds that image to bf16.
 // =====================================================================================================================
 
+constexpr int kBwd64Threads = 448;  // head_dim-64 kernel: warps 0-7 compute, 8-11 drain, 12 TMA, 13 MMA
 constexpr int kBwdThreads = 320;  // warps 0-7 compute (two warpgroups, 64 query columns each), warp 8 TMA, warp 9 MMA
 
 template <int D>
@@ -617,7 +619,7 @@ struct BwdSmem {
 
 __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
-                                      int B, int S, int nq, int d) {
+                                      int B, int S, int nq, int d, float scale) {
   const int warps_per_block = blockDim.x / 32;
   const long long total = (long long)B * S * nq;
   const int lane = threadIdx.x % 32;
@@ -637,7 +639,7 @@ __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const
     if (lane == 0) {
       const int b = row / S, s = row % S;
       const size_t idx = ((size_t)b * nq + h) * S + s;
-      delta[idx] = acc;
+      delta[idx] = acc * scale;   // pre-scaled: dS = P * (dP*scale - delta*scale) is one FFMA + one FMUL
       lse2[idx] = lse[idx] * 1.4426950408889634f;
     }
   }
@@ -870,8 +872,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
             if (key > q_first + qc) p0 = 0.f;
             if (key > q_first + qc + 1) p1 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(dv[qc]) - vec[128 + qc]) * scale;
-          const float d1 = p1 * (__uint_as_float(dv[qc + 1]) - vec[128 + qc + 1]) * scale;
+          const float d0 = p0 * fmaf(__uint_as_float(dv[qc]), scale, -vec[128 + qc]);
+          const float d1 = p1 * fmaf(__uint_as_float(dv[qc + 1]), scale, -vec[128 + qc + 1]);
           pk[e / 2] = pack_bf16(p0, p1);
           dk[e / 2] = pack_bf16(d0, d1);
         }
@@ -937,10 +939,10 @@ struct Bwd64Smem {
   static constexpr int kTotal = kBarOff + 512 + 1024;
 };
 
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwd64Threads, 1)
 flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
                    const __grid_constant__ CUtensorMap tmap_dqkv, const float* __restrict__ lse2, const float* __restrict__ delta,
-                   int S, int n_kv, int g, float scale, float scale_log2, int* __restrict__ status) {
+                   int S, int n_kv, int g, float scale, float scale_log2, int* __restrict__ status, long long* __restrict__ dbg) {
   using L = Bwd64Smem;
   constexpr int D = 64;
   extern __shared__ unsigned char smem_raw[];
@@ -975,13 +977,13 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
       mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128);
-      mbar_init(&dq_full[s], 1); mbar_init(&dq_drained[s], 256);
+      mbar_init(&dq_full[s], 1); mbar_init(&dq_drained[s], 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 13) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -989,7 +991,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dk = tmem_base + 256, tm_dv = tmem_base + 320;
   const uint32_t tm_dq0 = tmem_base + 384;  // two 64-column buffers
 
-  if (warp == 8) {
+  if (warp == 12) {
     if (elect_one()) {
       tma_prefetch_desc(&tmap_qkv);
       tma_prefetch_desc(&tmap_do);
@@ -1011,7 +1013,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
+  } else if (warp == 13) {
     if (elect_one()) {
       constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // S^T / dP^T half: 128 keys x 64 queries
       constexpr uint32_t idesc_dkv = make_idesc_bf16(128, D, false, true);
@@ -1049,130 +1051,165 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         issue_sdp(0, 0);
         issue_sdp(0, 1);
       }
+      const bool mrec = dbg != nullptr && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
+#define FTH_MS(i) do { if (mrec && st < 64) dbg[(16 + (i)) * 64 + st] = clock64(); } while (0)
       for (int st = 0; st < steps && ok; ++st) {
         const int stage = st & 1, nstage = stage ^ 1;
         const uint32_t ph = st & 1;
         const bool more = st + 1 < steps;
         // ---- half A
+        FTH_MS(0);
         if (!mbar_wait(&pds_full[0], ph, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
+        FTH_MS(1);
         issue_dkv(stage, 0, st == 0);
         if (more) {
           if (!mbar_wait(&q_full[nstage], ((st + 1) >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
           tc_fence_after();
+          FTH_MS(2);
           issue_sdp(nstage, 0);
         }
+        FTH_MS(3);
         // ---- half B
         if (!mbar_wait(&pds_full[1], ph, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
+        FTH_MS(4);
         issue_dkv(stage, 1, false);
         umma_commit(&q_empty[stage]);
+        // the next S^T / dP^T of this half goes first: warpgroup 1 waits for it, nobody waits for dQ
+        if (more) issue_sdp(nstage, 1);
         // ---- dQ(st) = dS K into buffer st & 1 (free once dQ(st-2) was drained)
         if (st >= 2) {
           if (!mbar_wait(&dq_drained[st & 1], ((st >> 1) - 1) & 1, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
           tc_fence_after();
         }
+        FTH_MS(5);
         const uint32_t ds_addr = smem_u32(smem + L::kDsOff + (st & 1) * 32768);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16_ss(tm_dq0 + 64 * (st & 1), make_smem_desc(ds_addr + kk * 2048, 16384, 1024),
                        make_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_dq, kk != 0);
         umma_commit(&dq_full[st & 1]);
-        if (more) issue_sdp(nstage, 1);
+        FTH_MS(6);
       }
+#undef FTH_MS
     }
     __syncwarp();
-  } else {
+  } else if (warp >= 8 && warp < 12) {
+    // ---------------- drain warps: dQ of every step, then dK and dV, tensor memory -> TMA reduce-add ----------------
+    const int qd = warp - 8;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    unsigned char* stg = smem + L::kStgOff;               // two [128 x 128 B] chunks = the 64 fp32 columns of a tile
+    const bool issuer = (threadIdx.x == 256);
+    auto drain64 = [&](uint32_t tm_src, int col, int row, uint64_t* release_bar) {
+      if (issuer) tma_wait_group_read<0>();
+      named_barrier_sync(3, 128);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_src + lane_off + c * 32, v);
+        tmem_wait_ld();
+        if (c == 1 && release_bar != nullptr) { tc_fence_before(); mbar_arrive(release_bar); }   // the tile may be overwritten now
+        unsigned char* rowp = stg + c * 16384 + r * 128;
+#pragma unroll
+        for (int p8 = 0; p8 < 8; ++p8)
+          *reinterpret_cast<uint4*>(rowp + ((p8 ^ (r & 7)) * 16)) = make_uint4(v[p8 * 4], v[p8 * 4 + 1], v[p8 * 4 + 2], v[p8 * 4 + 3]);
+      }
+      fence_proxy_async();
+      named_barrier_sync(3, 128);
+      if (issuer) {
+        tma_reduce_add_2d(&tmap_dqkv, stg, col, row);
+        tma_reduce_add_2d(&tmap_dqkv, stg + 16384, col + 32, row);
+        tma_commit_group();
+      }
+    };
+    bool ok = true;
+    for (int st = 0; st < steps && ok; ++st) {
+      const int pb = st & 1;
+      if (!mbar_wait(&dq_full[pb], (st >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      drain64(tm_dq0 + 64 * pb, q_col, grow0 + (n + st) * 128, &dq_drained[pb]);
+    }
+    if (ok) {   // the last dQ commit also covers the final dK / dV accumulation
+      drain64(tm_dk, k_col, grow0 + n * 128, nullptr);
+      drain64(tm_dv, v_col, grow0 + n * 128, nullptr);
+    }
+    if (issuer) tma_wait_group<0>();
+  } else if (warp < 8) {
+    // ---------------- compute warps: warpgroup h owns query half h of every step ----------------
     const int qd = warp % 4, h = warp / 4;
     const int r = qd * 32 + lane;
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     const int key = n * 128 + r;
-    unsigned char* stg = smem + L::kStgOff + h * 16384;
-    const bool issuer = (threadIdx.x == h * 128);
-    const int bar_id = 1 + h;
     bool ok = true;
-    // this warpgroup's 32 columns (h*32 ..) of a [128 x 64] fp32 tensor-memory tile -> TMA reduce-add into the dQKV image
-    auto drain_half = [&](uint32_t tm_src, int col, int row) {
-      uint32_t v[32];
-      tmem_ld_32x32(tm_src + lane_off + h * 32, v);
-      tmem_wait_ld();
-      if (issuer) tma_wait_group_read<0>();
-      named_barrier_sync(bar_id, 128);
-      unsigned char* rowp = stg + r * 128;
-#pragma unroll
-      for (int p8 = 0; p8 < 8; ++p8)
-        *reinterpret_cast<uint4*>(rowp + ((p8 ^ (r & 7)) * 16)) = make_uint4(v[p8 * 4], v[p8 * 4 + 1], v[p8 * 4 + 2], v[p8 * 4 + 3]);
-      fence_proxy_async();
-      named_barrier_sync(bar_id, 128);
-      if (issuer) {
-        tma_reduce_add_2d(&tmap_dqkv, stg, col + h * 32, row);
-        tma_commit_group();
-      }
-    };
+    const bool rec = dbg != nullptr && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0 && qd == 0 && lane == 0;
+    long long* drow = dbg + h * 8 * 64;
+#define FTH_TS(i) do { if (rec && st < 64) drow[(i) * 64 + st] = clock64(); } while (0)
     for (int st = 0; st < steps && ok; ++st) {
       const int m = n + st, stage = st & 1;
+      FTH_TS(0);
       if (!mbar_wait(&q_full[stage], (st >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
       const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024) + 64 * h;
+      FTH_TS(6);
       if (!mbar_wait(&sdp_full[h], st & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      FTH_TS(1);
       tc_fence_after();
       const bool diag = (m == n);
-      uint32_t sv[64], dv[64];
-      tmem_ld_32x32(tm_s + lane_off + 64 * h, sv);
-      tmem_ld_32x32(tm_s + lane_off + 64 * h + 32, sv + 32);
-      tmem_ld_32x32(tm_dp + lane_off + 64 * h, dv);
-      tmem_ld_32x32(tm_dp + lane_off + 64 * h + 32, dv + 32);
-      tmem_wait_ld();
       const int q_first = m * 128 + 64 * h;
       unsigned char* ds_row = smem + L::kDsOff + (st & 1) * 32768 + h * 16384 + r * 128;
+      // Four 16-column chunks with a rolling prefetch: the tensor-memory load of chunk c+1 is in flight during the math
+      // of chunk c.  The bf16 P^T / dS^T of chunk c land on columns [8c, 8c+8) of the warpgroup's own range, all of
+      // which chunks <= c have already read.  lse2 / delta come as 128-bit broadcast loads.
+      auto math = [&](auto diag_tag) {
+        constexpr bool kDiag = decltype(diag_tag)::value;
+        uint32_t sv[2][16], dv[2][16];
+        tmem_ld_32x16(tm_s + lane_off + 64 * h, sv[0]);
+        tmem_ld_32x16(tm_dp + lane_off + 64 * h, dv[0]);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16], dk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const int qc = c * 32 + e;
-          float p0 = exp2f(fmaf(__uint_as_float(sv[qc]), scale_log2, -vec[qc]));
-          float p1 = exp2f(fmaf(__uint_as_float(sv[qc + 1]), scale_log2, -vec[qc + 1]));
-          if (diag) {
-            if (key > q_first + qc) p0 = 0.f;
-            if (key > q_first + qc + 1) p1 = 0.f;
+        for (int c = 0; c < 4; ++c) {
+          tmem_wait_ld();
+          if (c == 0) FTH_TS(2);
+          if (c < 3) {
+            tmem_ld_32x16(tm_s + lane_off + 64 * h + (c + 1) * 16, sv[(c + 1) & 1]);
+            tmem_ld_32x16(tm_dp + lane_off + 64 * h + (c + 1) * 16, dv[(c + 1) & 1]);
           }
-          const float d0 = p0 * (__uint_as_float(dv[qc]) - vec[128 + qc]) * scale;
-          const float d1 = p1 * (__uint_as_float(dv[qc + 1]) - vec[128 + qc + 1]) * scale;
-          pk[e / 2] = pack_bf16(p0, p1);
-          dk[e / 2] = pack_bf16(d0, d1);
-        }
-        tmem_st_32x16(tm_s + lane_off + 64 * h + c * 16, pk);
-        tmem_st_32x16(tm_dp + lane_off + 64 * h + c * 16, dk);
+          const float4* l4 = reinterpret_cast<const float4*>(vec + c * 16);
+          const float4* d4 = reinterpret_cast<const float4*>(vec + 128 + c * 16);
+          uint32_t pk[8], dk[8];
 #pragma unroll
-        for (int p4 = 0; p4 < 4; ++p4) {
-          const int piece = c * 4 + p4;
-          *reinterpret_cast<uint4*>(ds_row + ((piece ^ (r & 7)) * 16)) = make_uint4(dk[p4 * 4], dk[p4 * 4 + 1], dk[p4 * 4 + 2], dk[p4 * 4 + 3]);
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const float4 lv = l4[q4], dl = d4[q4];
+            const float ls[4] = {lv.x, lv.y, lv.z, lv.w}, de[4] = {dl.x, dl.y, dl.z, dl.w};
+            float p[4], d[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              p[e] = exp2f(fmaf(__uint_as_float(sv[c & 1][q4 * 4 + e]), scale_log2, -ls[e]));
+              if (kDiag) { if (key > q_first + c * 16 + q4 * 4 + e) p[e] = 0.f; }
+              d[e] = p[e] * fmaf(__uint_as_float(dv[c & 1][q4 * 4 + e]), scale, -de[e]);
+            }
+            pk[q4 * 2] = pack_bf16(p[0], p[1]); pk[q4 * 2 + 1] = pack_bf16(p[2], p[3]);
+            dk[q4 * 2] = pack_bf16(d[0], d[1]); dk[q4 * 2 + 1] = pack_bf16(d[2], d[3]);
+          }
+          tmem_st_32x8(tm_s + lane_off + 64 * h + c * 8, pk);
+          tmem_st_32x8(tm_dp + lane_off + 64 * h + c * 8, dk);
+#pragma unroll
+          for (int p2 = 0; p2 < 2; ++p2) {
+            const int piece = c * 2 + p2;
+            *reinterpret_cast<uint4*>(ds_row + ((piece ^ (r & 7)) * 16)) = make_uint4(dk[p2 * 4], dk[p2 * 4 + 1], dk[p2 * 4 + 2], dk[p2 * 4 + 3]);
+          }
         }
-      }
+      };
+      if (diag) math(std::true_type{}); else math(std::false_type{});
+      FTH_TS(3);
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&pds_full[h]);
-      // drain dQ of the PREVIOUS step (finished long ago) while the tensor core works on this one
-      if (st > 0) {
-        const int pb = (st - 1) & 1;
-        if (!mbar_wait(&dq_full[pb], ((st - 1) >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
-        tc_fence_after();
-        drain_half(tm_dq0 + 64 * pb, q_col, grow0 + (m - 1) * 128);
-        tc_fence_before();
-        mbar_arrive(&dq_drained[pb]);
-      }
+      FTH_TS(4);
+      FTH_TS(5);
     }
-    if (ok) {
-      const int lb = (steps - 1) & 1;
-      if (mbar_wait(&dq_full[lb], ((steps - 1) >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) {
-        tc_fence_after();
-        drain_half(tm_dq0 + 64 * lb, q_col, grow0 + (n + steps - 1) * 128);
-        drain_half(tm_dk, k_col, grow0 + n * 128);   // the last dQ commit also covers the final dK / dV accumulation
-        drain_half(tm_dv, v_col, grow0 + n * 128);
-      }
-    }
-    if (issuer) tma_wait_group<0>();
+#undef FTH_TS
   }
 
   tc_fence_before();
@@ -1182,7 +1219,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     while (clock64() - t0 < 2000000LL) { __nanosleep(200); }
     __syncthreads();
   }
-  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 13) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // fp32 image -> bf16 packed dQKV.  With a RoPE table the inverse rotation (the RoPE backward) of the q and k head
@@ -1255,6 +1292,9 @@ int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv
 }
 
 // Scratch: `scratch_f32` holds [B*S, qkv_dim] fp32 (zeroed here) followed by delta and lse2, each [B, nq, S] fp32.
+static long long* g_bwd_dbg = nullptr;
+void fth_flash_bwd_set_debug(long long* buf) { g_bwd_dbg = buf; }
+
 size_t fth_flash_bwd_scratch_bytes(int B, int S, int n_kv, int g, int d) {
   return ((size_t)B * S * n_kv * (g + 2) * d + 2 * (size_t)B * n_kv * g * S) * sizeof(float);
 }
@@ -1274,7 +1314,7 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
     int blocks = (int)((warps + 7) / 8);
     if (blocks > 148 * 16) blocks = 148 * 16;
     flash_bwd_prep_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, lse, delta, lse2,
-                                                     B, S, nq, d);
+                                                     B, S, nq, d, 1.f / sqrtf((float)d));
   }
   CUtensorMap tq, tdo, tdq;
   int r = make_tmap_bf16_2d(&tq, qkv, (uint64_t)B * S, rs, rs, 128, 64);
@@ -1288,8 +1328,8 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
   if (d == 64) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(flash_bwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::kTotal); set = true; }
-    flash_bwd64_kernel<<<grid, kBwdThreads, Bwd64Smem::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
-                                                                        scale * 1.4426950408889634f, status);
+    flash_bwd64_kernel<<<grid, kBwd64Threads, Bwd64Smem::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
+                                                                        scale * 1.4426950408889634f, status, g_bwd_dbg);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kTotal); set = true; }

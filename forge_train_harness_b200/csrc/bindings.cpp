@@ -342,6 +342,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_fwd_set_debug", [](int64_t p) { fth_flash_fwd_set_debug(reinterpret_cast<long long*>(p)); });
   m.def("flash_bwd", &flash_bwd);
+  m.def("flash_bwd_set_debug", [](int64_t p) { fth_flash_bwd_set_debug(reinterpret_cast<long long*>(p)); });
   m.def("gemm_rs", &gemm_rs);
   m.def("ag_gemm", &ag_gemm);
   m.def("peer_barrier", &peer_barrier);

@@ -164,6 +164,13 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* r)
       : "memory");
 }
 
+// 32 lanes x 8 columns store (registers -> tensor memory)
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // ---- descriptors ----------------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version field = 1.
 //   K-major operand  (rows of 64 bf16 = 128 B, 8-row groups 1024 B apart): lbo = 0 (unused), sbo = 1024.
@@ -188,5 +195,9 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
          | ((uint32_t)(N >> 3) << 17)       // N / 8
          | ((uint32_t)(M >> 4) << 24);      // M / 16
 }
+
+// Warpgroup-wide register re-allocation (every warp of the warpgroup executes the same instruction).
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 }  // namespace fth
