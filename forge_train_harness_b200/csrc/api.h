@@ -22,8 +22,8 @@ int fth_embedding_fwd(const int* ids, const void* w, void* out, int M, int H, in
 int fth_embedding_bwd(const void* dout, const int* ids, float* main_grad, int M, int H, int vocab_start, int vocab_local,
                       float scale, cudaStream_t stream);
 int fth_cross_entropy(void* logits, const int* labels, const float* mask, float* nll, float* st_max, float* st_sum,
-                      float* st_tgt, const float* lse_in, int M, int V, int vocab_start, float grad_scale, int mode,
-                      cudaStream_t stream);
+                      float* st_tgt, const float* lse_in, int M, int V, long long ld, int vocab_start, float grad_scale,
+                      int mode, cudaStream_t stream);
 int fth_adamw_segments(float* master, float* m, float* v, const float* grad, void* param, int param_is_bf16,
                        const void* seg_table, int n_segs, float lr, float beta1, float beta2, float eps, float weight_decay,
                        float bc1, float rsqrt_bc2, const float* grad_scale, cudaStream_t stream);

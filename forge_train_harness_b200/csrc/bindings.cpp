@@ -22,6 +22,12 @@ void check(int rc, const char* what, int kernels = 1) {
 void need_bf16(const at::Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), n, " must be a contiguous CUDA bf16 tensor");
 }
+// 2-D bf16 whose rows may be padded: unit inner stride, row stride a multiple of 8 elements (16 bytes)
+void need_bf16_rows(const at::Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && t.stride(0) % 8 == 0 &&
+                  t.stride(0) >= t.size(1) && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0,
+              n, " must be a CUDA bf16 matrix with unit inner stride and 16-byte aligned rows");
+}
 void need_f32(const at::Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), n, " must be a contiguous CUDA fp32 tensor");
 }
@@ -143,38 +149,38 @@ void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& ma
 // mode 0: returns nll; logits overwritten with the gradient.
 at::Tensor cross_entropy(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, double grad_scale,
                          int64_t vocab_start) {
-  need_bf16(logits, "logits");
+  need_bf16_rows(logits, "logits");
   need_i32(labels, "labels");
   need_f32(mask, "mask");
   const int M = logits.size(0), V = logits.size(1);
   at::Tensor nll = at::empty({M}, mask.options());
   check(fth_cross_entropy(logits.data_ptr(), labels.data_ptr<int>(), mask.data_ptr<float>(), nll.data_ptr<float>(), nullptr,
-                          nullptr, nullptr, nullptr, M, V, (int)vocab_start, (float)grad_scale, 0, cur_stream()),
+                          nullptr, nullptr, nullptr, M, V, logits.stride(0), (int)vocab_start, (float)grad_scale, 0, cur_stream()),
         "cross_entropy");
   return nll;
 }
 
 std::vector<at::Tensor> ce_stats(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, int64_t vocab_start) {
-  need_bf16(logits, "logits");
+  need_bf16_rows(logits, "logits");
   need_i32(labels, "labels");
   need_f32(mask, "mask");
   const int M = logits.size(0), V = logits.size(1);
   at::Tensor mx = at::empty({M}, mask.options()), sm = at::empty({M}, mask.options()), tg = at::empty({M}, mask.options());
   check(fth_cross_entropy(logits.data_ptr(), labels.data_ptr<int>(), mask.data_ptr<float>(), nullptr, mx.data_ptr<float>(),
-                          sm.data_ptr<float>(), tg.data_ptr<float>(), nullptr, M, V, (int)vocab_start, 1.f, 1, cur_stream()),
+                          sm.data_ptr<float>(), tg.data_ptr<float>(), nullptr, M, V, logits.stride(0), (int)vocab_start, 1.f, 1, cur_stream()),
         "ce_stats");
   return {mx, sm, tg};
 }
 
 void ce_grad(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, const at::Tensor& lse, double grad_scale,
              int64_t vocab_start) {
-  need_bf16(logits, "logits");
+  need_bf16_rows(logits, "logits");
   need_i32(labels, "labels");
   need_f32(mask, "mask");
   need_f32(lse, "lse");
   check(fth_cross_entropy(logits.data_ptr(), labels.data_ptr<int>(), mask.data_ptr<float>(), nullptr, nullptr, nullptr, nullptr,
-                          lse.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)vocab_start, (float)grad_scale,
-                          2, cur_stream()), "ce_grad");
+                          lse.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), logits.stride(0), (int)vocab_start,
+                          (float)grad_scale, 2, cur_stream()), "ce_grad");
 }
 
 void adamw_segments(at::Tensor& master, at::Tensor& m, at::Tensor& v, const at::Tensor& grad, at::Tensor& param,

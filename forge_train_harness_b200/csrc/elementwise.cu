@@ -331,13 +331,16 @@ template <bool kSmemRow>
 __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(
     __nv_bfloat16* __restrict__ logits, const int* __restrict__ labels, const float* __restrict__ mask,
     float* __restrict__ nll, float* __restrict__ st_max, float* __restrict__ st_sum, float* __restrict__ st_tgt,
-    const float* __restrict__ lse_in, int M, int V, int vocab_start, float grad_scale, int mode) {
+    const float* __restrict__ lse_in, int M, int V, long long ld, int vocab_start, float grad_scale, int mode) {
+  // rows are `ld` elements apart (ld % 8 == 0); a row's last 16-byte vector may reach past V: those elements count as
+  // -inf in the statistics and get a zero gradient
   extern __shared__ __align__(16) unsigned char ce_smem[];
   __shared__ float red[64];
   bf16x8* rowbuf = reinterpret_cast<bf16x8*>(ce_smem);
-  const int nvec = V / 8;
+  const int nvec = (V + 7) / 8;
+  const int tail = V & 7;   // valid elements of the last vector, 0 = all eight
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
-    bf16x8* grow = reinterpret_cast<bf16x8*>(logits + (size_t)row * V);
+    bf16x8* grow = reinterpret_cast<bf16x8*>(logits + (size_t)row * ld);
     const int lab = labels[row] - vocab_start;
     const bool has = lab >= 0 && lab < V;
     float lse;
@@ -358,6 +361,11 @@ __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(
             if (kSmemRow) rowbuf[v] = p[u];
             float f[8];
             unpack8(p[u], f);
+            if (tail && v == nvec - 1) {
+#pragma unroll
+              for (int i = 1; i < 8; ++i)
+                if (i >= tail) f[i] = -INFINITY;
+            }
             float m8 = f[0];
 #pragma unroll
             for (int i = 1; i < 8; ++i) m8 = fmaxf(m8, f[i]);
@@ -368,7 +376,7 @@ __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(
         }
       }
       block_max_sum(mx, sm, red);
-      float tgt = has ? __bfloat162float(logits[(size_t)row * V + lab]) : 0.f;
+      float tgt = has ? __bfloat162float(logits[(size_t)row * ld + lab]) : 0.f;
       if (mode == 1) {
         if (threadIdx.x == 0) { st_max[row] = mx; st_sum[row] = sm; st_tgt[row] = tgt; }
         continue;
@@ -388,7 +396,7 @@ __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(
       for (int i = 0; i < 8; ++i) {
         float g = __expf(f[i] - lse);
         if (has && v * 8 + i == lab) g -= 1.f;
-        f[i] = g * gs;
+        f[i] = (tail && v * 8 + i >= V) ? 0.f : g * gs;
       }
       grow[v] = pack8(f);
     }
@@ -616,10 +624,10 @@ int fth_embedding_bwd(const void* dout, const int* ids, float* main_grad, int M,
 }
 
 int fth_cross_entropy(void* logits, const int* labels, const float* mask, float* nll, float* st_max, float* st_sum,
-                      float* st_tgt, const float* lse_in, int M, int V, int vocab_start, float grad_scale, int mode,
-                      cudaStream_t stream) {
-  if (V % 8) return -1;
-  size_t row_bytes = (size_t)V * 2;
+                      float* st_tgt, const float* lse_in, int M, int V, long long ld, int vocab_start, float grad_scale,
+                      int mode, cudaStream_t stream) {
+  if (ld % 8 || ld < V) return -1;
+  size_t row_bytes = (size_t)((V + 7) / 8) * 16;
   static int max_smem = 0;
   if (max_smem == 0) {
     int dev = 0;
@@ -632,11 +640,11 @@ int fth_cross_entropy(void* logits, const int* labels, const float* mask, float*
     int per_sm = max(1, (int)(((size_t)max_smem) / (row_bytes + 1024)));
     int grid = min(M, num_sms() * min(per_sm, 4));
     cross_entropy_kernel<true><<<grid, kCeThreads, row_bytes, stream>>>(
-        (__nv_bfloat16*)logits, labels, mask, nll, st_max, st_sum, st_tgt, lse_in, M, V, vocab_start, grad_scale, mode);
+        (__nv_bfloat16*)logits, labels, mask, nll, st_max, st_sum, st_tgt, lse_in, M, V, ld, vocab_start, grad_scale, mode);
   } else {
     int grid = min(M, num_sms() * 4);
     cross_entropy_kernel<false><<<grid, kCeThreads, 0, stream>>>(
-        (__nv_bfloat16*)logits, labels, mask, nll, st_max, st_sum, st_tgt, lse_in, M, V, vocab_start, grad_scale, mode);
+        (__nv_bfloat16*)logits, labels, mask, nll, st_max, st_sum, st_tgt, lse_in, M, V, ld, vocab_start, grad_scale, mode);
   }
   return 0;
 }

@@ -75,6 +75,12 @@ class Sm100Ops:
     # ---- linear: tcgen05 GEMMs --------------------------------------------
     @staticmethod
     def linear_fwd(x, w, alpha=1.0):
+        n = w.shape[0]
+        if n % 8:
+            # a vocabulary shard such as 73448 / 4 = 18362 columns: the TMA store needs 16-byte row pitch, so the result is
+            # a view of a row-padded buffer; its consumers (fused CE, dgrad / wgrad GEMMs) take the row stride
+            buf = torch.empty((x.shape[0], (n + 7) // 8 * 8), dtype=torch.bfloat16, device=x.device)
+            return _C.gemm(x, False, w, False, buf[:, :n], float(alpha), 0, 0, 0)
         return _C.gemm(x, False, w, False, None, float(alpha), 0, 0, 0)
 
     @staticmethod

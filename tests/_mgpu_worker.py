@@ -17,8 +17,12 @@ def main():
     init_distributed()
     par = {"dp_zero": dict(use_distributed_optimizer=True, ddp_bucket_elems=300_000),
            "dp_plain": dict(use_distributed_optimizer=False),
-           "tp_sp": dict(tensor_parallel_size=int(os.environ["WORLD_SIZE"]), sequence_parallel=True),
+           "tp_sp": dict(tensor_parallel_size=int(os.environ.get("WORLD_SIZE", "1")), sequence_parallel=True),
            "pp": dict(pipeline_parallel_size=2),
+           "tp2pp2": dict(tensor_parallel_size=2, pipeline_parallel_size=2, sequence_parallel=True,
+                          use_distributed_optimizer=True),
+           "tp2pp2v2": dict(tensor_parallel_size=2, pipeline_parallel_size=2, virtual_pipeline_stages=2,
+                            sequence_parallel=True, use_distributed_optimizer=True),
            "single": {}}[mode.split(":")[0]]
     model = dataclasses.replace(fth.preset("tiny"), num_layers=4, seq_length=256, padded_vocab_size=4096, hidden_size=256,
                                 ffn_hidden_size=512, num_attention_heads=4, num_query_groups=2, head_dim=64)

@@ -51,3 +51,29 @@ def test_tp2_sp_fused_and_nccl_and_pp2_match_single_gpu():
     close(single, nccl, 2e-2)
     close(single, fused, 2e-2)
     close(single, run("pp", 2), 2e-2)
+
+
+needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+
+
+@needs4
+def test_tp4_with_replicated_kv_heads_fused_and_nccl_match_single_gpu():
+    """2 KV heads on 4 tensor-parallel ranks: each KV head lives on two ranks and its weight gradient is summed over them."""
+    single = run("single", 1)
+    nccl = run("tp_sp", 4, {"FORGE_FUSED_TP": "0"})
+    fused = run("tp_sp", 4, {"FORGE_FUSED_TP": "1"})
+    assert fused["fused"] and not nccl["fused"]
+    close(single, nccl, 2e-2)
+    close(single, fused, 2e-2)
+
+
+@needs4
+def test_tp2_pp2_and_interleaved_match_single_gpu():
+    single = run("single", 1)
+    close(single, run("tp2pp2", 4), 2e-2)
+    close(single, run("tp2pp2v2", 4), 2e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_tp2_pp2_dp2_matches_single_gpu():
+    close(run("single", 1), run("tp2pp2", 8), 2e-2)

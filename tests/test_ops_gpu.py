@@ -94,6 +94,47 @@ def test_cross_entropy(ops, M, V):
     assert err < 4e-3, err
 
 
+def test_ragged_vocab_shard_head(ops):
+    """A vocabulary shard whose width is not a multiple of 8 (73448 / 4 = 18362): row-padded logits through the head GEMM,
+    the fused cross-entropy statistics / gradient and the two backward GEMMs."""
+    M, H, V = 384, 256, 18362
+    x, w = rnd(M, H), rnd(V, H, scale=0.05)
+    labels = torch.randint(-V, 2 * V, (M,), device="cuda", dtype=torch.int32)   # some targets live on other shards
+    mask = (torch.rand(M, device="cuda") > 0.2).float()
+    logits = ops.linear_fwd(x, w, 0.5)
+    assert logits.shape == (M, V) and logits.stride(0) % 8 == 0
+    ref = 0.5 * (x.float() @ w.float().t())
+    close(logits.float(), ref, 2e-2, 2e-2)
+    from forge_train_harness_b200.ops.cuda_ops import _C
+    mx, sm, tg = _C.ce_stats(logits, labels, mask, 0)
+    lf = logits.float()
+    close(mx, lf.max(dim=1).values, 1e-6, 1e-6)
+    close(sm, torch.exp(lf - mx[:, None]).sum(dim=1), 1e-3, 1e-3)
+    has = (labels >= 0) & (labels < V)
+    tg0 = torch.where(has, lf.gather(1, labels.clamp(0, V - 1).long()[:, None])[:, 0], torch.zeros_like(mx))
+    close(tg, tg0, 1e-6, 1e-6)
+    lse = mx + torch.log(sm)
+    g0 = torch.exp(lf - lse[:, None])
+    g0[has, labels[has].long()] -= 1.0
+    g0 = g0 * (mask * 0.3)[:, None]
+    _C.ce_grad(logits, labels, mask, lse, 0.3, 0)
+    assert (logits.float() - g0).abs().max().item() < 4e-3
+    # single-rank fused path on a padded view
+    logits2 = ops.linear_fwd(x, w, 0.5)
+    lab2 = labels.clamp(0, V - 1)
+    l0 = logits2.float().clone()
+    nll0 = T.cross_entropy_fwd_bwd(l0, lab2, mask, 0.3)
+    nll = ops.cross_entropy_fwd_bwd(logits2, lab2, mask, 0.3)
+    close(nll, nll0, 1e-3, 2e-2)
+    assert (logits2.float() - l0).abs().max().item() < 4e-3
+    # backward GEMMs read the padded view through its row stride
+    dx = ops.linear_dgrad(logits2, w, 2.0)
+    close(dx.float(), 2.0 * (logits2.float() @ w.float()), 2e-2, 2e-2)
+    gw = torch.zeros(V, H, device="cuda")
+    ops.linear_wgrad(logits2, x, gw, 2.0)
+    close(gw, 2.0 * (logits2.float().t() @ x.float()), 2e-2, 2e-2)
+
+
 def test_adamw_and_sumsq(ops):
     n = 50000
     master = torch.randn(n, device="cuda")
