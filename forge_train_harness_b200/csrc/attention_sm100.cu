@@ -620,25 +620,30 @@ struct BwdSmem {
 __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
                                       int B, int S, int nq, int d, float scale) {
-  const int warps_per_block = blockDim.x / 32;
-  const long long total = (long long)B * S * nq;
-  const int lane = threadIdx.x % 32;
-  for (long long w = (long long)blockIdx.x * warps_per_block + threadIdx.x / 32; w < total; w += (long long)gridDim.x * warps_per_block) {
-    const int h = w % nq;
-    const long long row = w / nq;  // b*S + s
-    const size_t base = (size_t)row * nq * d + (size_t)h * d;
+  // d / 8 lanes per (row, head): each lane one 16-byte vector of O and of dO, so a warp covers 4 items at head_dim 64.
+  // Items run row-fastest inside a head, which makes the delta / lse2 writes and the lse reads contiguous.
+  const int lpi = d / 8, ipw = 32 / lpi;
+  const int lane = threadIdx.x % 32, sub = lane / lpi, l = lane % lpi;
+  const long long rows = (long long)B * S, total = rows * nq;
+  const long long warps = (long long)gridDim.x * (blockDim.x / 32);
+  for (long long w0 = ((long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32) * ipw; w0 < total; w0 += warps * ipw) {
+    const long long w = w0 + sub;
+    const bool ok = w < total;
+    const int h = ok ? (int)(w / rows) : 0;
+    const long long row = ok ? w % rows : 0;  // b*S + s
     float acc = 0.f;
-    for (int c = lane * 8; c < d; c += 256) {
+    if (ok) {
+      const size_t base = ((size_t)row * nq + h) * d + l * 8;
       float a[8], b8[8];
-      load8(o + base + c, a);
-      load8(d_o + base + c, b8);
+      load8(o + base, a);
+      load8(d_o + base, b8);
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc += a[e] * b8[e];
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      const int b = row / S, s = row % S;
-      const size_t idx = ((size_t)b * nq + h) * S + s;
+    for (int off = lpi / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (ok && l == 0) {
+      const int b = (int)(row / S), sq = (int)(row % S);
+      const size_t idx = ((size_t)b * nq + h) * S + sq;
       delta[idx] = acc * scale;   // pre-scaled: dS = P * (dP*scale - delta*scale) is one FFMA + one FMUL
       lse2[idx] = lse[idx] * 1.4426950408889634f;
     }
@@ -1310,7 +1315,7 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
   float* lse2 = delta + (size_t)B * nq * S;
   cudaMemsetAsync(img, 0, n_img * sizeof(float), stream);
   {
-    long long warps = (long long)B * S * nq;
+    long long warps = ((long long)B * S * nq + (256 / d) - 1) / (256 / d);
     int blocks = (int)((warps + 7) / 8);
     if (blocks > 148 * 16) blocks = 148 * 16;
     flash_bwd_prep_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, lse, delta, lse2,

@@ -113,11 +113,13 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(
     const bool ok = row < M;
     const float rstd = ok ? rstd_in[row] : 0.f;
     float gv[VPT][8], xh[VPT][8];
+    bf16x8 dr[VPT];   // the residual-stream gradient is fetched with dy and x, not after the row reduction
     float dot = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       int c = (v * TPR + lane) * 8;
       if (ok && c < H) {
+        if (dres != nullptr) dr[v] = *reinterpret_cast<const bf16x8*>(dres + (size_t)row * H + c);
         load8(dy + (size_t)row * H + c, gv[v]);
         load8(x + (size_t)row * H + c, xh[v]);
 #pragma unroll
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(
       int c = (v * TPR + lane) * 8;
       if (ok && c < H) {
         float o[8];
-        if (dres != nullptr) load8(dres + (size_t)row * H + c, o);
+        if (dres != nullptr) unpack8(dr[v], o);
         else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = 0.f;
@@ -190,31 +192,36 @@ __global__ void colsum_add_kernel(const float* __restrict__ partial, float* __re
 // In-place rotate-half RoPE on the q and k heads of the packed kv-group-major QKV activation.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ table, int M, int S,
                             int n_kv, int g, int d, float sign) {
+  // A thread owns one 16-byte vector position of the row (head slot, vector) and walks down the rows, so the index
+  // arithmetic (divisions by g + 1 and d / 16) happens once per thread, not once per element.
   const int half = d / 2, vph = half / 8;  // vectors per half head
-  const int slots = n_kv * (g + 1);
-  const size_t total = (size_t)M * slots * vph;
+  const int ipr = n_kv * (g + 1) * vph;    // vector pairs per row
   const int row_stride = n_kv * (g + 2) * d;
-  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
-    int vec = it % vph;
-    size_t t = it / vph;
-    int sl = t % slots;
-    int row = t / slots;
-    int j = sl / (g + 1), hh = sl % (g + 1);
-    __nv_bfloat16* p = qkv + (size_t)row * row_stride + (size_t)(j * (g + 2) + hh) * d + vec * 8;
-    const float* tb = table + (size_t)(row % S) * d + vec * 8;
-    float x1[8], x2[8], c[8], s[8], o1[8], o2[8];
-    load8(p, x1);
-    load8(p + half, x2);
-    load8(tb, c);
-    load8(tb + half, s);
+  const int tpr = ipr < (int)blockDim.x ? ipr : (int)blockDim.x;
+  const int rpb = blockDim.x / tpr;
+  const int my_row = threadIdx.x / tpr;
+  if (my_row >= rpb) return;
+  for (int rem = threadIdx.x % tpr; rem < ipr; rem += tpr) {
+    const int vec = rem % vph, sl = rem / vph;
+    const int j = sl / (g + 1), hh = sl % (g + 1);
+    const int col = (j * (g + 2) + hh) * d + vec * 8;
+    for (int row = blockIdx.x * rpb + my_row; row < M; row += gridDim.x * rpb) {
+      __nv_bfloat16* p = qkv + (size_t)row * row_stride + col;
+      const float* tb = table + (size_t)(row % S) * d + vec * 8;
+      float x1[8], x2[8], c[8], sn[8], o1[8], o2[8];
+      load8(p, x1);
+      load8(p + half, x2);
+      load8(tb, c);
+      load8(tb + half, sn);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float sn = s[i] * sign;
-      o1[i] = x1[i] * c[i] - x2[i] * sn;
-      o2[i] = x2[i] * c[i] + x1[i] * sn;
+      for (int i = 0; i < 8; ++i) {
+        const float si = sn[i] * sign;
+        o1[i] = x1[i] * c[i] - x2[i] * si;
+        o2[i] = x2[i] * c[i] + x1[i] * si;
+      }
+      store8(p, o1);
+      store8(p + half, o2);
     }
-    store8(p, o1);
-    store8(p + half, o2);
   }
 }
 
@@ -508,25 +515,24 @@ static int num_sms() {
   return g_num_sms;
 }
 
-static int row_cfg(int H, int& tpr, int& vpt) {
+// Wide layout for the bandwidth-bound training shapes: as many threads per row as there are 16-byte vectors (up to 256),
+// so a thread holds one vector per array, registers stay low and every SM keeps its full 2048 threads of loads in flight.
+static int row_cfg_wide(int H, int& tpr, int& vpt) {
   int vecs = H / 8;
   tpr = 32;
-  while (tpr < 256 && vecs > tpr * 4) tpr *= 2;
+  while (tpr < 256 && vecs > tpr) tpr *= 2;
   vpt = (vecs + tpr - 1) / tpr;
   return (H % 8 == 0 && vpt <= 4) ? 0 : -1;
 }
 
-#define FTH_ROW_DISPATCH(KERNEL, ...)                                                      \
+#define FTH_ROW_DISPATCH_WIDE(KERNEL, ...)                                                 \
   do {                                                                                     \
     switch (tpr * 8 + vpt) {                                                               \
       case 32 * 8 + 1: KERNEL<32, 1><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
-      case 32 * 8 + 2: KERNEL<32, 2><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
-      case 32 * 8 + 3: KERNEL<32, 3><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
-      case 32 * 8 + 4: KERNEL<32, 4><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
-      case 64 * 8 + 3: KERNEL<64, 3><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
-      case 64 * 8 + 4: KERNEL<64, 4><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
-      case 128 * 8 + 3: KERNEL<128, 3><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
-      case 128 * 8 + 4: KERNEL<128, 4><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
+      case 64 * 8 + 1: KERNEL<64, 1><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break;   \
+      case 128 * 8 + 1: KERNEL<128, 1><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
+      case 256 * 8 + 1: KERNEL<256, 1><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
+      case 256 * 8 + 2: KERNEL<256, 2><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
       case 256 * 8 + 3: KERNEL<256, 3><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
       case 256 * 8 + 4: KERNEL<256, 4><<<grid, kRowThreads, 0, stream>>>(__VA_ARGS__); break; \
       default: return -1;                                                                  \
@@ -542,10 +548,10 @@ extern "C" {
 int fth_rmsnorm_fwd(const void* x, const void* res, float res_scale, const void* w, void* r_out, void* y,
                     float* rstd, int M, int H, float eps, float out_scale, cudaStream_t stream) {
   int tpr, vpt;
-  if (row_cfg(H, tpr, vpt)) return -1;
+  if (row_cfg_wide(H, tpr, vpt)) return -1;
   int rpb = kRowThreads / tpr;
   int grid = min((M + rpb - 1) / rpb, num_sms() * 8);
-  FTH_ROW_DISPATCH(rmsnorm_fwd_kernel, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, res_scale,
+  FTH_ROW_DISPATCH_WIDE(rmsnorm_fwd_kernel, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, res_scale,
                    (const __nv_bfloat16*)w, (__nv_bfloat16*)r_out, (__nv_bfloat16*)y, rstd, M, H, eps, out_scale);
   return 0;
 }
@@ -553,17 +559,17 @@ int fth_rmsnorm_fwd(const void* x, const void* res, float res_scale, const void*
 // Number of partial rows (= blocks) the backward kernel writes for M rows of width H.
 int fth_rmsnorm_bwd_blocks(int M, int H) {
   int tpr, vpt;
-  if (row_cfg(H, tpr, vpt)) return -1;
+  if (row_cfg_wide(H, tpr, vpt)) return -1;
   int rpb = kRowThreads / tpr;
-  return min((M + rpb - 1) / rpb, num_sms() * 4);
+  return min((M + rpb - 1) / rpb, num_sms() * 8);
 }
 
 int fth_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                     float* dw_partial, float* dw_main_grad, int M, int H, float out_scale, cudaStream_t stream) {
   int tpr, vpt;
-  if (row_cfg(H, tpr, vpt)) return -1;
+  if (row_cfg_wide(H, tpr, vpt)) return -1;
   int grid = fth_rmsnorm_bwd_blocks(M, H);
-  FTH_ROW_DISPATCH(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
+  FTH_ROW_DISPATCH_WIDE(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
                    (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, M, H, out_scale);
   colsum_add_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(dw_partial, dw_main_grad, grid, H);
   return 0;
@@ -571,8 +577,9 @@ int fth_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
 
 int fth_rope(void* qkv, const float* table, int M, int S, int n_kv, int g, int d, float sign, cudaStream_t stream) {
   if (d % 16) return -1;
-  size_t total = (size_t)M * n_kv * (g + 1) * (d / 16);
-  int grid = (int)min((total + 255) / 256, (size_t)num_sms() * 16);
+  const int ipr = n_kv * (g + 1) * (d / 16);
+  const int rpb = 256 / (ipr < 256 ? ipr : 256);
+  int grid = min((M + rpb - 1) / rpb, num_sms() * 8);
   rope_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, table, M, S, n_kv, g, d, sign);
   return 0;
 }
@@ -708,7 +715,7 @@ extern "C" int fth_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   if (H > kNoAllocMaxH)
     return noalloc_fail(err, err_len, -2, "fth_rmsnorm_bwd_noalloc: H exceeds the built-in scratch (max 4096 columns); use fth_rmsnorm_bwd with your own buffer");
   int tpr, vpt;
-  if (row_cfg(H, tpr, vpt)) return noalloc_fail(err, err_len, -3, "fth_rmsnorm_bwd_noalloc: H must be a multiple of 8");
+  if (row_cfg_wide(H, tpr, vpt)) return noalloc_fail(err, err_len, -3, "fth_rmsnorm_bwd_noalloc: H must be a multiple of 8");
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices)
     return noalloc_fail(err, err_len, -4, "fth_rmsnorm_bwd_noalloc: no current CUDA device (or device ordinal >= 64)");
@@ -725,7 +732,7 @@ extern "C" int fth_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   if (grid > kNoAllocMaxBlocks) grid = kNoAllocMaxBlocks;
   // Every launched block writes its whole partial row (zeros if it had no rows), and the column sum reads exactly
   // `grid` rows, so nothing left in the array by an earlier call is ever read: no clearing is needed.
-  FTH_ROW_DISPATCH(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
+  FTH_ROW_DISPATCH_WIDE(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
                    (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, partial, M, H, out_scale);
   colsum_add_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(partial, dw_main_grad, grid, H);
   if (cudaGetLastError() != cudaSuccess) return noalloc_fail(err, err_len, -6, "fth_rmsnorm_bwd_noalloc: kernel launch failed");

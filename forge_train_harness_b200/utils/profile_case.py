@@ -6,6 +6,8 @@ Cases (a few hundred MB on the device at most, GEMM operands larger than the 126
   gemm_fwd / gemm_dgrad / gemm_wgrad   the FC1 shape of the 0.5B model at 16384 tokens (M 16384, N 8192, K 1024)
   flash_fwd / flash_bwd                 1 x 4096 tokens, 16 query / 2 KV heads of 64
   rmsnorm_fwd / rmsnorm_bwd / swiglu_fwd / swiglu_bwd / rope / cross_entropy    the 0.5B shapes at 16384 (CE: 4096) tokens
+  microbatch                            engine steps of the 0.5B shape cut to 2 layers: one micro-batch of 4 x 4096 tokens per
+                                        step, no CUDA graph, so that a launch list shows every kernel of a layer and of the head
 """
 from __future__ import annotations
 
@@ -53,6 +55,16 @@ def main(argv=None):
         lab = torch.randint(0, V, (4096,), device=dev, dtype=torch.int32)
         mk = torch.ones(4096, device=dev)
         fn = lambda: ops.cross_entropy_fwd_bwd(lg, lab, mk)
+    elif a.op == "microbatch":
+        import dataclasses
+        from .. import OptimConfig, RunConfig, TrainConfig, DataConfig, Trainer, preset
+        cfg = RunConfig(model=dataclasses.replace(preset("minicpm4_0.5b"), num_layers=2),
+                        optim=OptimConfig(lr=1e-3, lr_schedule="constant"),
+                        train=TrainConfig(num_steps=a.iters, micro_batch_size=4, global_batch_size=4, seed=1, dtype="bf16",
+                                          cuda_graph=False),
+                        data=DataConfig(prefetch_size=0))
+        tr = Trainer(cfg, quiet=True)
+        fn = tr.train_step
     else:
         raise SystemExit(f"unknown op {a.op}")
     for _ in range(a.iters):
