@@ -56,6 +56,12 @@ int fth_gemm_rs(const void* a, long long lda, const void* b, long long ldb, int 
 int fth_ag_gemm(void* const* gather, long long ldx, const void* b, long long ldb, int b_mn, void* out, long long ldo, int M, int N,
                 int K, int tp, int rank, int n_copy_ctas, int* flags, int epoch, float alpha, int* status, cudaStream_t stream);
 
+// MXFP8 (e4m3 payload + e8m0 scale per 32 elements of the contraction dimension); see mxfp8_sm100.cu.
+size_t fth_mxfp8_sf_bytes(int rows, int K);
+int fth_mxfp8_quant(const void* x, long long ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t stream);
+int fth_gemm_mxfp8(const void* a, const void* sfa, const void* b, const void* sfb, void* c, long long ldc, int M, int N, int K,
+                   float alpha, int epi, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

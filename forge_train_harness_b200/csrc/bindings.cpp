@@ -234,6 +234,46 @@ at::Tensor gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, 
   return out;
 }
 
+// MXFP8 quantisation of a 2-D bf16 matrix.  colwise = false: payload [R, C], scale blocks along C.  colwise = true: payload
+// of the TRANSPOSE [C, R], scale blocks along R.  Returns {payload uint8, scale chunks uint8}.
+std::vector<at::Tensor> mxfp8_quant(const at::Tensor& x, bool colwise) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 8 == 0 &&
+                  (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "mxfp8_quant: bf16 CUDA matrix with 16-byte aligned rows");
+  const int64_t R = x.size(0), C = x.size(1);
+  const int64_t rows = colwise ? C : R, K = colwise ? R : C;
+  TORCH_CHECK(K % 32 == 0, "mxfp8_quant: the quantised dimension must be a multiple of 32, got ", K);
+  at::Tensor q = at::empty({rows, K}, x.options().dtype(at::kByte));
+  const int64_t sfb = (int64_t)fth_mxfp8_sf_bytes((int)rows, (int)K);
+  // whole chunks are read by the GEMM: bytes no block writes must not be the e8m0 NaN pattern
+  at::Tensor sf = ((K / 32) % 4 == 0 && rows % 128 == 0) ? at::empty({sfb}, q.options()) : at::zeros({sfb}, q.options());
+  check(fth_mxfp8_quant(x.data_ptr(), x.stride(0), q.data_ptr(), sf.data_ptr(), (int)R, (int)C, colwise ? 1 : 0, cur_stream()),
+        "mxfp8_quant");
+  return {q, sf};
+}
+
+// C = alpha * A B^T on MXFP8 operands (payload [M|N, K] uint8 + scale chunks).  epi as in gemm().
+at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb,
+                      c10::optional<at::Tensor> c, double alpha, int64_t epi) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kByte && b.scalar_type() == at::kByte && a.is_contiguous() &&
+                  b.is_contiguous() && a.dim() == 2 && b.dim() == 2, "gemm_mxfp8: contiguous uint8 payloads");
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(b.size(1) == K, "gemm_mxfp8: reduction dims differ");
+  TORCH_CHECK(sfa.numel() >= (int64_t)fth_mxfp8_sf_bytes((int)M, (int)K) && sfb.numel() >= (int64_t)fth_mxfp8_sf_bytes((int)N, (int)K),
+              "gemm_mxfp8: scale arrays too small");
+  at::Tensor out;
+  if (c.has_value()) {
+    out = *c;
+    TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "bad output");
+    TORCH_CHECK(out.scalar_type() == (epi == 0 ? at::kBFloat16 : at::kFloat), "output dtype does not match epilogue");
+  } else {
+    TORCH_CHECK(epi != 1, "accumulating epilogue needs an output tensor");
+    out = at::empty({M, N}, a.options().dtype(epi == 0 ? at::kBFloat16 : at::kFloat));
+  }
+  check(fth_gemm_mxfp8(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), out.data_ptr(), out.stride(0), (int)M, (int)N,
+                       (int)K, (float)alpha, (int)epi, status_ptr(), cur_stream()), "gemm_mxfp8");
+  return out;
+}
+
 // Causal GQA attention on the packed QKV activation.  Returns {out [M, n_kv*g*d] bf16, lse [B, n_kv*g, S] fp32}.
 std::vector<at::Tensor> flash_fwd(const at::Tensor& qkv, int64_t S, int64_t n_kv, int64_t g, int64_t d) {
   need_bf16(qkv, "qkv");
@@ -345,6 +385,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_segments", &adamw_segments);
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
+  m.def("mxfp8_quant", &mxfp8_quant);
+  m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_fwd_set_debug", [](int64_t p) { fth_flash_fwd_set_debug(reinterpret_cast<long long*>(p)); });
   m.def("flash_bwd", &flash_bwd);

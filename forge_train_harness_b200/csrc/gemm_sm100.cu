@@ -289,6 +289,10 @@ int make_tmap_f32_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t 
                      uint32_t box_cols) {
   return make_tmap_2d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, rows, cols, ld, box_rows, box_cols);
 }
+int make_tmap_u8_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                    uint32_t box_cols) {
+  return make_tmap_2d(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ptr, rows, cols, ld, box_rows, box_cols);
+}
 
 static int sm_count() {
   static int n = 0;

@@ -221,3 +221,49 @@ def test_gemm_repeated_calls_and_views(ops):
         y = ops.linear_fwd(x, w)
         close(y, x.float() @ w.float().t(), 1e-2, 0.1)
         w.mul_(0.9)
+
+
+# ---- MXFP8 ----------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("R,C", [(128, 128), (256, 1024), (200, 160), (4096, 4096)])
+@pytest.mark.parametrize("colwise", [False, True])
+def test_mxfp8_quant_matches_format_statement(ops, R, C, colwise):
+    from forge_train_harness_b200.ops import mxfp8 as mx
+    if colwise and R % 32:
+        R = (R + 31) // 32 * 32
+    x = rnd(R, C, scale=2.0)
+    x[3, :] = 0
+    q, sf = mx.quantize(x, colwise)
+    q0, sf0 = mx.quantize_ref(x, colwise)
+    assert q.shape == q0.shape and torch.equal(sf.cpu(), sf0.cpu())
+    assert torch.equal(q.cpu(), q0.cpu())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (200, 264, 160), (1024, 4096, 4096), (130, 96, 32)])
+def test_mxfp8_gemm_matches_dequantised_matmul(ops, M, N, K):
+    from forge_train_harness_b200.ops import mxfp8 as mx
+    a, b = rnd(M, K), rnd(N, K, scale=0.3)
+    aq, asf = mx.quantize(a)
+    bq, bsf = mx.quantize(b)
+    ref = mx.dequantize_ref(aq, asf) @ mx.dequantize_ref(bq, bsf).t()
+    y = mx.gemm(aq, asf, bq, bsf, None, 0.5, 0)
+    close(y.float(), 0.5 * ref, 1e-2, 1e-2)
+    y32 = mx.gemm(aq, asf, bq, bsf, None, 1.0, 2)
+    close(y32, ref, 1e-4, 1e-3)
+    acc = torch.ones(M, N, device="cuda")
+    mx.gemm(aq, asf, bq, bsf, acc, 2.0, 1)
+    close(acc, 1.0 + 2.0 * ref, 1e-4, 1e-3)
+
+
+def test_mxfp8_linear_products_close_to_bf16(ops):
+    from forge_train_harness_b200.ops import mxfp8 as mx
+    M, N, K = 512, 768, 1024
+    x, w, dy = rnd(M, K, scale=0.5), rnd(N, K, scale=0.05), rnd(M, N)
+    lin = mx.Mxfp8Linear()
+    ref = x.float() @ w.float().t()
+    assert (lin.fwd(x, w).float() - ref).abs().max() <= 0.05 * ref.abs().max()
+    refd = dy.float() @ w.float()
+    assert (lin.dgrad(dy, w).float() - refd).abs().max() <= 0.05 * refd.abs().max()
+    g = torch.zeros(N, K, device="cuda")
+    lin.wgrad(dy, x, g)
+    refw = dy.float().t() @ x.float()
+    assert (g - refw).abs().max() <= 0.05 * refw.abs().max()
