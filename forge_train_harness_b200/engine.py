@@ -64,8 +64,13 @@ class Trainer:
             os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
             torch.use_deterministic_algorithms(True, warn_only=True)
         self.ops = ops or get_ops(self.device)
+        if par.fp8 == "mxfp8" and self.dtype == torch.bfloat16:
+            # block-scaled fp8 for every linear product whose dimensions are multiples of 32 (the ragged vocabulary
+            # products stay bf16); the one-kernel TP paths are bf16 kernels, so this option uses the library collectives
+            from .ops.mxfp8 import Mxfp8Ops
+            self.ops = Mxfp8Ops(self.ops)
         self.tpc = TPComm(topo.tp_group, topo.tp, topo.tp_rank, par.sequence_parallel)
-        if self.tpc.sp and self.device.type == "cuda" and par.fused_comm and self.dtype == torch.bfloat16 \
+        if self.tpc.sp and self.device.type == "cuda" and par.fused_comm and self.dtype == torch.bfloat16 and par.fp8 == "off" \
                 and os.environ.get("FORGE_FUSED_TP", "1") == "1":
             from .parallel import fused_tp
             self.tpc.fused = fused_tp.try_create(topo.tp_group, topo.tp, topo.tp_rank, t.micro_batch_size * m.seq_length,
@@ -269,12 +274,19 @@ class Trainer:
             self.capture.grads("pre", self.store)
         lr = compute_lr(step_abs, self.cfg.optim)
         norm = self.opt.step(lr, inv_tokens)
+        self.weights_changed()
         if self.capture is not None:
             self.capture.grads("post", self.store, scale=inv_tokens)
             self.capture.loss_scalar("post", stats)
         self.step = step_abs
         self.last = {"loss": loss, "grad_norm": norm, "tokens": stats[1], "lr": lr}
         return self.last
+
+    def weights_changed(self):
+        """Tell op tables that keep derived copies of the weights (the MXFP8 quantised ones) that the bf16 parameters moved."""
+        hook = getattr(self.ops, "after_optimizer_step", None)
+        if hook is not None:
+            hook()
 
     # ------------------------------------------------------------------
     def data_state(self) -> dict:
@@ -322,6 +334,7 @@ def run_training_loop(cfg: RunConfig, *, trainer: Trainer | None = None, loss_ta
     rank0 = tr.rank == 0
     if t.resume_from:
         ckpt.load(tr, t.resume_from, weights_only=t.init_weights_only)
+        tr.weights_changed()
         if rank0:
             print(wire.format_resume_startup(time.time() - t0_wall), file=out, flush=True)
     if rank0:

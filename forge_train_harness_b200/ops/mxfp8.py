@@ -9,8 +9,9 @@ and backward.py:79,90,389,394); this is the block-scaled option of the 8B tensor
 * thin wrappers over the extension (``quantize`` / ``gemm``);
 * ``Mxfp8Linear``: the three products of a linear layer.  Scale blocks always run along the contraction dimension, so
   the forward uses row-quantised ``x`` and ``w``, the data gradient row-quantised ``dy`` and column-quantised ``w``, the
-  weight gradient column-quantised ``dy`` and ``x``.  Weight copies are cached per parameter and refreshed when the
-  optimizer has stepped (the parameter's ``_version`` or an explicit step counter changes).
+  weight gradient column-quantised ``dy`` and ``x``.  Weight copies are cached per parameter in fixed buffers and
+  re-quantised in place after every optimizer step;
+* ``Mxfp8Ops``: an op table that routes the three linear products through ``Mxfp8Linear`` (``parallel.fp8 = "mxfp8"``).
 
 Scale storage: for every 128 rows x 4 scale blocks one 512-byte chunk, byte ``(r % 32) * 16 + (r // 32 % 4) * 4 + kb % 4``,
 chunks ordered ``[ceil(rows / 128)][ceil(K / 128)]`` — the layout one ``tcgen05.cp.32x128b.warpx4`` moves into tensor memory.
@@ -86,28 +87,38 @@ def gemm(a, sfa, b, sfb, out=None, alpha: float = 1.0, epi: int = 0):
 
 
 class Mxfp8Linear:
-    """Forward / dgrad / wgrad of ``y = alpha * x @ w.T`` in MXFP8 with cached weight copies."""
+    """Forward / dgrad / wgrad of ``y = alpha * x @ w.T`` in MXFP8 with cached weight copies.
+
+    A weight is quantised on first use and the copies live in fixed buffers (a captured CUDA graph may hold their
+    addresses); ``refresh()`` re-quantises every cached weight into the same buffers and is called by the engine after
+    each optimizer step and after a checkpoint load.
+    """
 
     def __init__(self):
-        self._w = {}     # key -> (stamp, row-quantised (q, sf), col-quantised (q, sf) or None)
-        self.stamp = 0   # bumped by the engine after every optimizer step
-
-    def invalidate(self):
-        self.stamp += 1
+        self._w = {}     # (data_ptr, shape) -> [weight view, row-quantised (q, sf), col-quantised (q, sf) or None]
 
     def _weight(self, w, need_col):
         key = (w.data_ptr(), tuple(w.shape))
         ent = self._w.get(key)
-        if ent is None or ent[0] != self.stamp:
-            ent = [self.stamp, quantize(w, False), None]
+        if ent is None:
+            ent = [w, quantize(w, False), None]
             self._w[key] = ent
         if need_col and ent[2] is None:
             ent[2] = quantize(w, True)
         return ent
 
+    def refresh(self):
+        for ent in self._w.values():
+            w = ent[0]
+            for slot, colwise in ((1, False), (2, True)):
+                if ent[slot] is not None:
+                    q, sf = quantize(w, colwise)
+                    ent[slot][0].copy_(q)
+                    ent[slot][1].copy_(sf)
+
     @staticmethod
-    def supported(m_rows: int, n: int, k: int) -> bool:
-        return m_rows % 32 == 0 and n % 32 == 0 and k % 32 == 0
+    def supported(*dims) -> bool:
+        return all(d % 32 == 0 for d in dims)
 
     def fwd(self, x, w, alpha=1.0):
         xq, xs = quantize(x, False)
@@ -123,3 +134,45 @@ class Mxfp8Linear:
         dq, dsf = quantize(dy, True)               # [N, M]: contraction over the tokens
         xq, xs = quantize(x, True)                 # [K, M]
         return gemm(dq, dsf, xq, xs, main_grad, alpha, 1)
+
+
+class Mxfp8Ops:
+    """An op table whose three linear products run in MXFP8 wherever every dimension is a multiple of 32; everything else
+    (and the ragged vocabulary head / embedding products) stays on the wrapped table."""
+
+    def __init__(self, base):
+        from . import OP_NAMES
+        for n in OP_NAMES:
+            if n not in ("linear_fwd", "linear_dgrad", "linear_wgrad"):
+                setattr(self, n, getattr(base, n))
+        self.base = base
+        self.lin = Mxfp8Linear()
+        self.name = getattr(base, "name", "ops") + "+mxfp8"
+        self.versions = dict(getattr(base, "versions", {}), linear_fwd="mxfp8", linear_dgrad="mxfp8", linear_wgrad="mxfp8")
+        self.mx_calls = 0
+
+    @staticmethod
+    def _plain(t):
+        return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.dtype == torch.bfloat16
+
+    def linear_fwd(self, x, w, alpha=1.0):
+        if self._plain(x) and self._plain(w) and Mxfp8Linear.supported(x.shape[0], x.shape[1], w.shape[0]):
+            self.mx_calls += 1
+            return self.lin.fwd(x, w, alpha)
+        return self.base.linear_fwd(x, w, alpha)
+
+    def linear_dgrad(self, dy, w, alpha=1.0):
+        if self._plain(dy) and self._plain(w) and Mxfp8Linear.supported(dy.shape[0], dy.shape[1], w.shape[1]):
+            self.mx_calls += 1
+            return self.lin.dgrad(dy, w, alpha)
+        return self.base.linear_dgrad(dy, w, alpha)
+
+    def linear_wgrad(self, dy, x, main_grad, alpha=1.0):
+        if self._plain(dy) and self._plain(x) and main_grad.dtype == torch.float32 and \
+                Mxfp8Linear.supported(dy.shape[0], dy.shape[1], x.shape[1]):
+            self.mx_calls += 1
+            return self.lin.wgrad(dy, x, main_grad, alpha)
+        return self.base.linear_wgrad(dy, x, main_grad, alpha)
+
+    def after_optimizer_step(self):
+        self.lin.refresh()

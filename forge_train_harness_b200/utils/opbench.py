@@ -82,6 +82,18 @@ def main(argv=None):
         rec(f"cublas_dgrad_{name}", timeit(lambda: dy @ w, flush=flush), fl)
         rec(f"cublas_wgrad_{name}", timeit(lambda: dy.t() @ x, flush=flush), fl)
         del x, w, dy, mg
+    if want("mxfp8"):
+        from ..ops import mxfp8 as mx
+        for name, N, K in gemms[:4]:
+            x, w = r(M, K), r(N, K)
+            fl = 2.0 * M * N * K
+            rec(f"mxfp8_quant_row_{name}_x", timeit(lambda: mx.quantize(x, False), flush=flush), bytes_=3.0 * M * K)
+            rec(f"mxfp8_quant_col_{name}_x", timeit(lambda: mx.quantize(x, True), flush=flush), bytes_=3.0 * M * K)
+            xq, xs = mx.quantize(x, False)
+            wq, ws = mx.quantize(w, False)
+            rec(f"mxfp8_gemm_fwd_{name}", timeit(lambda: mx.gemm(xq, xs, wq, ws, None, 1.0, 0), flush=flush), fl)
+            rec(f"bf16_gemm_fwd_{name}", timeit(lambda: _C.gemm(x, False, w, False, None, 1.0, 0, 0, 0), flush=flush), fl)
+            del x, w, xq, xs, wq, ws
     if want("norm"):
         x, res, w = r(M, H), r(M, H), r(H)
         rec("rmsnorm_fwd", timeit(lambda: ops.rmsnorm_fwd(x, w, 1e-6), flush=flush), bytes_=2.0 * M * H * 2)

@@ -57,3 +57,15 @@ def test_cuda_graph_replay_matches_eager():
     assert g1 and not g0
     for (l0, n0), (l1, n1) in zip(eager, graph):
         assert abs(l0 - l1) / abs(l0) < 2e-3 and abs(n0 - n1) / abs(n0) < 2e-2, (eager, graph)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_mxfp8_linears_train_close_to_bf16(graph):
+    """`parallel.fp8 = "mxfp8"`: block-scaled tcgen05 GEMMs for the layer linears, eager and under CUDA-graph replay."""
+    cfg = cfg_for("plain", graph=graph, steps=5)
+    ref, _ = run(cfg)
+    got, used = run(cfg.replace(parallel={"fp8": "mxfp8"}))
+    assert used == graph
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) / abs(l0) < 2e-2, (ref, got)
+        assert abs(g0 - g1) / abs(g0) < 2e-1, (ref, got)

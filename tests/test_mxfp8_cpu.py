@@ -54,10 +54,35 @@ def test_linear_products_close_to_exact():
     lin.wgrad(dy, x, g, 2.0)
     refw = 1.0 + 2.0 * dy.float().t() @ x.float()
     assert (g - refw).abs().max() <= 0.06 * refw.abs().max()
-    # weight copies are cached until the optimizer steps
-    k0 = dict(lin._w)
+    # weight copies are cached in fixed buffers and refreshed in place after an optimizer step
+    k0 = {k: (v[1][0], v[1][0].clone()) for k, v in lin._w.items()}
     lin.fwd(x, w)
-    assert all(lin._w[k] is k0[k] for k in k0)
-    lin.invalidate()
-    lin.fwd(x, w)
-    assert any(lin._w[k] is not k0[k] for k in k0)
+    assert all(lin._w[k][1][0] is k0[k][0] for k in k0)
+    w.mul_(2.0)
+    lin.refresh()
+    assert all(lin._w[k][1][0] is k0[k][0] for k in k0)
+    y2 = lin.fwd(x, w, 0.5)
+    assert (y2.float() - 2 * ref).abs().max() <= 0.06 * 2 * ref.abs().max()
+
+
+def test_engine_trains_with_mxfp8_linears_on_cpu():
+    """`parallel.fp8 = "mxfp8"` routes the layer GEMMs through the MXFP8 products (format statement on CPU) and keeps training."""
+    import math
+
+    import forge_train_harness_b200 as fth
+    cfg = fth.RunConfig(model=fth.preset("tiny"), optim=fth.OptimConfig(lr=3e-3, lr_schedule="constant"),
+                        parallel=fth.ParallelConfig(fp8="mxfp8"),
+                        train=fth.TrainConfig(num_steps=5, micro_batch_size=2, grad_accum_steps=1, seed=0, dtype="bf16", cuda_graph=False),
+                        data=fth.DataConfig(prefetch_size=0))
+    cfg = cfg.replace(model={"seq_length": 64, "padded_vocab_size": 264})
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    assert tr.ops.name.endswith("+mxfp8")
+    losses = [float(tr.train_step()["loss"]) for _ in range(5)]
+    assert tr.ops.mx_calls >= 5 * 2 * 4 * 3 - 8   # 4 linears x 3 products per layer and step (first layer's input grad aside)
+    assert all(math.isfinite(v) for v in losses) and losses[-1] < losses[0]
+    # same run in bf16: the fp8 trajectory stays close
+    tr2 = fth.Trainer(cfg.replace(parallel={"fp8": "off"}), device="cpu", quiet=True)
+    ref = [float(tr2.train_step()["loss"]) for _ in range(5)]
+    assert max(abs(a - b) / abs(b) for a, b in zip(losses, ref)) < 0.02
+    tr.close()
+    tr2.close()
