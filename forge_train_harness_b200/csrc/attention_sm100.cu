@@ -38,6 +38,8 @@ struct FwdSmem {
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  // one conversion instruction; doing the rounding with an integer add and a byte permute instead measured slower
+  // (forward exp phase 1914 -> 2450 cycles per block): the integer pipe is half rate and the phase is issue bound
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
@@ -320,6 +322,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xch = reinterpret_cast<float*>(smem + L::kBarOff + 512);  // [2 parities][2 tiles][2 halves][128 rows]
   uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L::kBarOff + 384);  // [2] per-tile exchange barrier, 256 arrivals
+  uint64_t* s_free = xbar + 2;          // [2] per tile: S has been read out of tensor memory (256 arrivals)
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n_pairs = (S + 255) / 256;
@@ -338,7 +341,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 256); mbar_init(&o_done[t], 1); mbar_init(&xbar[t], 256); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 256); mbar_init(&o_done[t], 1); mbar_init(&xbar[t], 256); mbar_init(&s_free[t], 256); }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -349,8 +352,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // tensor-memory columns: S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,256+D)  O_B [384,384+D)
+  // At head_dim 64 the 512 columns hold S (2 x 128), a separate bf16 P (2 x 64) and O (2 x 64): with P out of place the
+  // next S = Q K^T of a tile is issued as soon as its softmax warps have read the current S, and is ready by the time
+  // they finish the exp phase.  At head_dim 128 O needs 2 x 128 columns and P overwrites S in place.
+  constexpr bool kSepP = (D == 64);
   const uint32_t tm_s[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tm_o[2] = {tmem_base + 256, tmem_base + 384};
+  const uint32_t tm_p[2] = {kSepP ? tmem_base + 256 : tmem_base, kSepP ? tmem_base + 320 : tmem_base + 128};
+  const uint32_t tm_o[2] = {kSepP ? tmem_base + 384 : tmem_base + 256, kSepP ? tmem_base + 448 : tmem_base + 384};
 
   if (warp == 16) {
     // ---------------- TMA producer ----------------
@@ -394,7 +402,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       auto issue_pv = [&](int t, uint32_t v_addr, bool first) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(tm_o[t], tm_s[t] + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), make_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_o,
+          umma_bf16_ts(tm_o[t], kSepP ? tm_p[t] + kk * 8 : tm_s[t] + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8),
+                       make_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_o,
                        (first && kk == 0) ? 0u : 1u);
         umma_commit(&o_done[t]);
       };
@@ -419,6 +428,27 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
         if (nstage == KS) { nstage = 0; nphase ^= 1; }
         const uint32_t k_next = smem_u32(smem + L::kKVOff + nstage * 2 * L::kTile);
         bool next_ready = false;
+        if constexpr (kSepP) {
+          // next S of both tiles first (their current S has been read early in the softmax of block kb) ...
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (kb + 1 >= nb_t[t]) continue;
+            if (!mbar_wait(&s_free[t], kb & 1, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
+            if (!next_ready) {
+              if (!mbar_wait(&kv_full[nstage], nphase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+              next_ready = true;
+            }
+            tc_fence_after();
+            issue_s(t, k_next);
+          }
+          // ... then P V of block kb as each tile's P arrives
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (kb >= nb_t[t]) continue;
+            if (!mbar_wait(&p_full[t], p_phase[t], abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+            p_phase[t] ^= 1;
+            tc_fence_after();
+            issue_pv(t, v_cur, kb == 0);
+          }
+        } else
         for (int t = 0; t < 2 && ok; ++t) {
           if (kb >= nb_t[t]) continue;
           if (!mbar_wait(&p_full[t], p_phase[t], abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
@@ -471,6 +501,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       tmem_ld_32x32(tm_s[t] + lane_off + s_col, sr);
       tmem_ld_32x32(tm_s[t] + lane_off + s_col + 32, sr + 32);
       tmem_wait_ld();
+      if constexpr (kSepP) { tc_fence_before(); mbar_arrive(&s_free[t]); }
       FTH_TS(2);
       if (diag) {
 #pragma unroll
@@ -498,6 +529,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       if (m_run == -INFINITY) m_use = m_new;
       const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
       const bool need_fix = (m_use != m_run) && kb > 0;
+      if constexpr (kSepP) {
+        if (kb > 0) {   // P V of the previous block has read P and finished with O
+          if (!mbar_wait(&o_done[t], ph_o, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
+          ph_o ^= 1;
+          tc_fence_after();
+        }
+      }
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -513,15 +551,17 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
           pk[e / 2 + 1] = pack_bf16(p2, p3);
         }
         // P of keys [64hh+32c, +32) -> packed columns [64hh+16c, +16): inside this half's own S columns (already read)
-        tmem_st_32x16(tm_s[t] + lane_off + s_col + c * 16, pk);
+        tmem_st_32x16(kSepP ? tm_p[t] + lane_off + 32 * hh + c * 16 : tm_s[t] + lane_off + s_col + c * 16, pk);
       }
       l_run = l_run * alpha + ((rs0 + rs1) + (rs2 + rs3));
       m_run = m_use;
       FTH_TS(4);
       if (kb > 0) {
-        if (!mbar_wait(&o_done[t], ph_o, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
-        ph_o ^= 1;
-        tc_fence_after();
+        if constexpr (!kSepP) {
+          if (!mbar_wait(&o_done[t], ph_o, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
+          ph_o ^= 1;
+          tc_fence_after();
+        }
         if (__any_sync(0xffffffffu, need_fix)) {   // each half rescales its own D/2 columns of O
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
