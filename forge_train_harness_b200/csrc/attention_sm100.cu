@@ -37,6 +37,11 @@ struct FwdSmem {
   static constexpr int kTotal = kBarOff + 512 + 4096 + 1024;
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   // one conversion instruction; doing the rounding with an integer add and a byte permute instead measured slower
   // (forward exp phase 1914 -> 2450 cycles per block): the integer pipe is half rate and the phase is issue bound
@@ -321,8 +326,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xch = reinterpret_cast<float*>(smem + L::kBarOff + 512);  // [2 parities][2 tiles][2 halves][128 rows]
-  uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L::kBarOff + 384);  // [2] per-tile exchange barrier, 256 arrivals
-  uint64_t* s_free = xbar + 2;          // [2] per tile: S has been read out of tensor memory (256 arrivals)
+  uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L::kBarOff + 384);  // [2] per-tile exchange barrier, 8 arrivals (one per warp)
+  uint64_t* s_free = xbar + 2;          // [2] per tile: S has been read out of tensor memory (8 arrivals)
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n_pairs = (S + 255) / 256;
@@ -341,7 +346,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 256); mbar_init(&o_done[t], 1); mbar_init(&xbar[t], 256); mbar_init(&s_free[t], 256); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); mbar_init(&o_done[t], 1); mbar_init(&xbar[t], 8); mbar_init(&s_free[t], 8); }   // one arrival per warp
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -501,25 +506,26 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       tmem_ld_32x32(tm_s[t] + lane_off + s_col, sr);
       tmem_ld_32x32(tm_s[t] + lane_off + s_col + 32, sr + 32);
       tmem_wait_ld();
-      if constexpr (kSepP) { tc_fence_before(); mbar_arrive(&s_free[t]); }
+      if constexpr (kSepP) { tc_fence_before(); mbar_arrive_warp(&s_free[t]); }
       FTH_TS(2);
       if (diag) {
 #pragma unroll
         for (int e = 0; e < 64; ++e)
           if (kpos0 + e > qrow) sr[e] = 0xff800000u;  // -inf
       }
+      // three-input max: half the instructions of the pairwise form on the half-rate pipe this phase is bound by
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int e = 0; e < 64; e += 8) {
-        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])));
-        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])));
-        mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sr[e + 4]), __uint_as_float(sr[e + 5])));
-        mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sr[e + 6]), __uint_as_float(sr[e + 7])));
+        mx0 = fmax3(mx0, __uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(sr[e + 4]), __uint_as_float(sr[e + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(sr[e + 6]), __uint_as_float(sr[e + 7]));
       }
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       float* slot = xch + (((kb & 1) * 2 + t) * 2) * 128;
       slot[hh * 128 + r] = mx;
-      mbar_arrive(&xbar[t]);
+      mbar_arrive_warp(&xbar[t]);
       if (!mbar_wait(&xbar[t], ph_x, abort_flag, status, kTimeoutGeneric)) { ok = false; break; }
       ph_x ^= 1;
       FTH_TS(3);
@@ -577,7 +583,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
       FTH_TS(5);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[t]);
+      mbar_arrive_warp(&p_full[t]);
       FTH_TS(6);
     }
 #undef FTH_TS
@@ -586,7 +592,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __res
         tc_fence_after();
         float* slot = xch + (((nb & 1) * 2 + t) * 2) * 128;   // parity not used by the last block's max exchange
         slot[hh * 128 + r] = l_run;
-        mbar_arrive(&xbar[t]);
+        mbar_arrive_warp(&xbar[t]);
         if (mbar_wait(&xbar[t], ph_x, abort_flag, status, kTimeoutGeneric)) {
         const float l_tot = l_run + slot[(hh ^ 1) * 128 + r];
         const float inv = 1.f / l_tot;
@@ -709,9 +715,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
   uint64_t* q_full = bars + 1;         // [QS]
   uint64_t* q_empty = q_full + QS;     // [QS]
   uint64_t* sdp_full = q_empty + QS;   // S^T and dP^T ready
-  uint64_t* pds_full = sdp_full + 1;   // P^T, dS^T written (128 arrivals)
+  uint64_t* pds_full = sdp_full + 1;   // P^T, dS^T written (one arrival per compute warp)
   uint64_t* dq_full = pds_full + 1;    // dV, dK, dQ MMAs of this step finished
-  uint64_t* dq_drained = dq_full + 1;  // dQ read out of tensor memory (128 arrivals)
+  uint64_t* dq_drained = dq_full + 1;  // dQ read out of tensor memory (one arrival per warp)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -733,9 +739,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
     mbar_init(kv_full, 1);
     for (int s = 0; s < QS; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 256);
+    mbar_init(pds_full, 8);        // one arrival per compute warp
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 256);
+    mbar_init(dq_drained, 8);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -935,14 +941,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      mbar_arrive_warp(pds_full);
       // drain dQ of this step
       if (!mbar_wait(dq_full, ph_dq, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
       ph_dq ^= 1;
       tc_fence_after();
       drain_tile(tm_dq, q_col, grow0 + m * 128);
       tc_fence_before();
-      mbar_arrive(dq_drained);
+      mbar_arrive_warp(dq_drained);
       if (++stage == QS) { stage = 0; qphase ^= 1; }
     }
     if (ok) {
@@ -997,9 +1003,9 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   uint64_t* q_full = bars + 1;          // [2]
   uint64_t* q_empty = q_full + 2;       // [2]
   uint64_t* sdp_full = q_empty + 2;     // [2] per half: S^T and dP^T ready
-  uint64_t* pds_full = sdp_full + 2;    // [2] per half: P^T, dS^T written (128 arrivals)
+  uint64_t* pds_full = sdp_full + 2;    // [2] per half: P^T, dS^T written (4 arrivals, one per warp)
   uint64_t* dq_full = pds_full + 2;     // [2] per dQ buffer
-  uint64_t* dq_drained = dq_full + 2;   // [2] per dQ buffer (256 arrivals)
+  uint64_t* dq_drained = dq_full + 2;   // [2] per dQ buffer (4 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -1021,8 +1027,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128);
-      mbar_init(&dq_full[s], 1); mbar_init(&dq_drained[s], 128);
+      mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 4);     // one arrival per warp
+      mbar_init(&dq_full[s], 1); mbar_init(&dq_drained[s], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -1155,7 +1161,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         uint32_t v[32];
         tmem_ld_32x32(tm_src + lane_off + c * 32, v);
         tmem_wait_ld();
-        if (c == 1 && release_bar != nullptr) { tc_fence_before(); mbar_arrive(release_bar); }   // the tile may be overwritten now
+        if (c == 1 && release_bar != nullptr) { tc_fence_before(); mbar_arrive_warp(release_bar); }   // the tile may be overwritten now
         unsigned char* rowp = stg + c * 16384 + r * 128;
 #pragma unroll
         for (int p8 = 0; p8 < 8; ++p8)
@@ -1250,7 +1256,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(&pds_full[h]);
+      mbar_arrive_warp(&pds_full[h]);
       FTH_TS(4);
       FTH_TS(5);
     }
