@@ -985,13 +985,17 @@ struct Bwd64Smem {
   static constexpr int kQdOOff = 2 * kTile;              // 2 stages x (Q tile, dO tile)
   static constexpr int kDsOff = kQdOOff + 4 * kTile;     // 2 buffers x 2 chunks x [128 x 128 B]
   static constexpr int kStgOff = kDsOff + 65536;         // one [128 x 128 B] fp32 staging buffer per warpgroup
-  static constexpr int kVecOff = kStgOff + 32768;        // per stage: lse2[128], delta[128]
-  static constexpr int kBarOff = kVecOff + 2048;
+  // "augmentation" operands (see the kernel): a constant [128 x 16] tile of ones and, per stage, four [64 x 16] tiles
+  // (S^T half 0 / 1, dP^T half 0 / 1) holding -lse2 / scale_log2 resp. -delta split into two bf16, all K-major, no swizzle
+  static constexpr int kOnesOff = kStgOff + 32768;       // 4 KB
+  static constexpr int kAugOff = kOnesOff + 4096;        // 2 stages x 4 x 2 KB
+  static constexpr int kBarOff = kAugOff + 16384;
   static constexpr int kTotal = kBarOff + 512 + 1024;
 };
 
 __global__ void __launch_bounds__(kBwd64Threads, 1)
-flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_q64,
+                   const __grid_constant__ CUtensorMap tmap_do64,
                    const __grid_constant__ CUtensorMap tmap_dqkv, const float* __restrict__ lse2, const float* __restrict__ delta,
                    int S, int n_kv, int g, float scale, float scale_log2, int* __restrict__ status, long long* __restrict__ dbg) {
   using L = Bwd64Smem;
@@ -1000,13 +1004,14 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* kv_full = bars;             // [1]
-  uint64_t* q_full = bars + 1;          // [2]
-  uint64_t* q_empty = q_full + 2;       // [2]
-  uint64_t* sdp_full = q_empty + 2;     // [2] per half: S^T and dP^T ready
+  uint64_t* q_full = bars + 1;          // [2 stages][2 query halves]: rows 64h .. 64h+63 of the Q and dO tiles
+  uint64_t* q_empty = q_full + 4;       // [2][2]
+  uint64_t* sdp_full = q_empty + 4;     // [2] per half: S^T and dP^T ready
   uint64_t* pds_full = sdp_full + 2;    // [2] per half: P^T, dS^T written (4 arrivals, one per warp)
   uint64_t* dq_full = pds_full + 2;     // [2] per dQ buffer
   uint64_t* dq_drained = dq_full + 2;   // [2] per dQ buffer (4 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 2);
+  uint64_t* aug_full = dq_drained + 2;  // [2] per stage: augmentation tiles written (4 arrivals, one per drain warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aug_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -1026,9 +1031,11 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
+      mbar_init(&q_full[2 * s], 1); mbar_init(&q_full[2 * s + 1], 1);
+      mbar_init(&q_empty[2 * s], 1); mbar_init(&q_empty[2 * s + 1], 1);
       mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 4);     // one arrival per warp
       mbar_init(&dq_full[s], 1); mbar_init(&dq_drained[s], 4);
+      mbar_init(&aug_full[s], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -1045,22 +1052,25 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   if (warp == 12) {
     if (elect_one()) {
       tma_prefetch_desc(&tmap_qkv);
-      tma_prefetch_desc(&tmap_do);
+      tma_prefetch_desc(&tmap_q64);
+      tma_prefetch_desc(&tmap_do64);
       mbar_expect_tx(kv_full, 2 * L::kTile);
       tma_load_2d(smem + L::kKOff, &tmap_qkv, k_col, grow0 + n * 128, kv_full);
       tma_load_2d(smem + L::kVOff, &tmap_qkv, v_col, grow0 + n * 128, kv_full);
-      for (int st = 0; st < steps; ++st) {
+      // Q and dO arrive per query half: half h of a stage is free as soon as the dV / dK products of that half have
+      // read it, half a step before the whole tile would be, which keeps the loads ahead of the shortened steps
+      bool live = true;
+      for (int st = 0; st < steps && live; ++st) {
         const int stage = st & 1;
         const uint32_t phase = (st >> 1) & 1;
         const int m = n + st;
-        if (!mbar_wait(&q_empty[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) break;
         unsigned char* sq = smem + L::kQdOOff + stage * 2 * L::kTile;
-        float* vec = reinterpret_cast<float*>(smem + L::kVecOff + stage * 1024);
-        mbar_expect_tx(&q_full[stage], 2 * L::kTile + 1024);
-        tma_load_2d(sq, &tmap_qkv, q_col, grow0 + m * 128, &q_full[stage]);
-        tma_load_2d(sq + L::kTile, &tmap_do, do_col, grow0 + m * 128, &q_full[stage]);
-        bulk_load_1d(vec, lse2_h + m * 128, 512, &q_full[stage]);
-        bulk_load_1d(vec + 128, delta_h + m * 128, 512, &q_full[stage]);
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait(&q_empty[2 * stage + h], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) { live = false; break; }
+          mbar_expect_tx(&q_full[2 * stage + h], L::kTile);
+          tma_load_2d(sq + h * 8192, &tmap_q64, q_col, grow0 + m * 128 + 64 * h, &q_full[2 * stage + h]);
+          tma_load_2d(sq + L::kTile + h * 8192, &tmap_do64, do_col, grow0 + m * 128 + 64 * h, &q_full[2 * stage + h]);
+        }
       }
     }
     __syncwarp();
@@ -1081,6 +1091,12 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_bf16_ss(tm_dp + 64 * h, make_smem_desc(v_addr + kk * 32, 0, 1024), make_smem_desc(do_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
+        // fifth k-step: ones x (-lse2 / scale_log2) resp. ones x (-delta), so the accumulators already hold the exponent
+        // argument and dP - delta and no thread has to fetch per-query vectors
+        const uint32_t aug = smem_u32(smem + L::kAugOff + stage * 8192);
+        const uint64_t ones_desc = make_smem_desc_plain(smem_u32(smem + L::kOnesOff), 128, 256);
+        umma_bf16_ss(tm_s + 64 * h, ones_desc, make_smem_desc_plain(aug + h * 2048, 128, 256), idesc_st, 1u);
+        umma_bf16_ss(tm_dp + 64 * h, ones_desc, make_smem_desc_plain(aug + 4096 + h * 2048, 128, 256), idesc_st, 1u);
         umma_commit(&sdp_full[h]);
       };
       // dV += P_h^T dO_h ; dK += dS_h^T Q_h  (64 queries = 4 steps of 16)
@@ -1096,12 +1112,11 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
           umma_bf16_ts(tm_dk, tm_dp + 64 * h + kk * 8, make_smem_desc(q_addr + (4 * h + kk) * 2048, 16384, 1024), idesc_dkv,
                        !(first && kk == 0));
       };
+      if (ok) ok = mbar_wait(&aug_full[0], 0, abort_flag, status, kTimeoutSmemFull);
       if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, status, kTimeoutSmemFull);
-      if (ok) {
-        tc_fence_after();
-        issue_sdp(0, 0);
-        issue_sdp(0, 1);
-      }
+      if (ok) { tc_fence_after(); issue_sdp(0, 0); }
+      if (ok) ok = mbar_wait(&q_full[1], 0, abort_flag, status, kTimeoutSmemFull);
+      if (ok) { tc_fence_after(); issue_sdp(0, 1); }
       const bool mrec = dbg != nullptr && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
 #define FTH_MS(i) do { if (mrec && st < 64) dbg[(16 + (i)) * 64 + st] = clock64(); } while (0)
       for (int st = 0; st < steps && ok; ++st) {
@@ -1114,8 +1129,10 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         tc_fence_after();
         FTH_MS(1);
         issue_dkv(stage, 0, st == 0);
+        umma_commit(&q_empty[2 * stage]);
         if (more) {
-          if (!mbar_wait(&q_full[nstage], ((st + 1) >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          if (!mbar_wait(&q_full[2 * nstage], ((st + 1) >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          if (!mbar_wait(&aug_full[nstage], ((st + 1) >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
           tc_fence_after();
           FTH_MS(2);
           issue_sdp(nstage, 0);
@@ -1126,9 +1143,13 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         tc_fence_after();
         FTH_MS(4);
         issue_dkv(stage, 1, false);
-        umma_commit(&q_empty[stage]);
+        umma_commit(&q_empty[2 * stage + 1]);
         // the next S^T / dP^T of this half goes first: warpgroup 1 waits for it, nobody waits for dQ
-        if (more) issue_sdp(nstage, 1);
+        if (more) {
+          if (!mbar_wait(&q_full[2 * nstage + 1], ((st + 1) >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_sdp(nstage, 1);
+        }
         // ---- dQ(st) = dS K into buffer st & 1 (free once dQ(st-2) was drained)
         if (st >= 2) {
           if (!mbar_wait(&dq_drained[st & 1], ((st >> 1) - 1) & 1, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
@@ -1175,11 +1196,40 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         tma_commit_group();
       }
     };
+    // Augmentation tiles.  Thread t of the 128 owns query t of a step: -lse2 / scale_log2 and -delta (the pre-pass stores
+    // delta * scale) as bf16 hi + lo pairs in columns 0 and 1 of its row; the constant tile has ones in those two columns.
+    const float inv_scale_log2 = 1.f / scale_log2, inv_scale = 1.f / scale;
+    auto write_aug = [&](int st_for) {
+      const int m = n + st_for, hq = r >> 6, ql = r & 63;
+      const float vs = -lse2_h[m * 128 + r] * inv_scale_log2, vd = -delta_h[m * 128 + r] * inv_scale;
+      const __nv_bfloat16 s_hi = __float2bfloat16(vs), d_hi = __float2bfloat16(vd);
+      const __nv_bfloat16 s_lo = __float2bfloat16(vs - __bfloat162float(s_hi)), d_lo = __float2bfloat16(vd - __bfloat162float(d_hi));
+      unsigned char* base = smem + L::kAugOff + (st_for & 1) * 8192 + hq * 2048 + (ql >> 3) * 256 + (ql & 7) * 16;
+      *reinterpret_cast<uint32_t*>(base) = (uint32_t)__bfloat16_as_ushort(s_hi) | ((uint32_t)__bfloat16_as_ushort(s_lo) << 16);
+      *reinterpret_cast<uint32_t*>(base + 4096) = (uint32_t)__bfloat16_as_ushort(d_hi) | ((uint32_t)__bfloat16_as_ushort(d_lo) << 16);
+      fence_proxy_async();
+      mbar_arrive_warp(&aug_full[st_for & 1]);
+    };
+    {
+      // one-time: zero both stages' tiles (only columns 0 and 1 are ever rewritten) and build the ones tile
+      uint4* z = reinterpret_cast<uint4*>(smem + L::kAugOff);
+      for (int i = r; i < 16384 / 16; i += 128) z[i] = make_uint4(0u, 0u, 0u, 0u);
+      unsigned char* one_row = smem + L::kOnesOff + (r >> 3) * 256 + (r & 7) * 16;
+      *reinterpret_cast<uint4*>(one_row) = make_uint4(0x3F803F80u, 0u, 0u, 0u);          // bf16 1.0, 1.0, then zeros
+      *reinterpret_cast<uint4*>(one_row + 128) = make_uint4(0u, 0u, 0u, 0u);
+      named_barrier_sync(3, 128);   // the zero fill of other threads' rows is complete before anybody writes values
+      write_aug(0);
+      if (steps > 1) write_aug(1);
+    }
     bool ok = true;
     for (int st = 0; st < steps && ok; ++st) {
       const int pb = st & 1;
       if (!mbar_wait(&dq_full[pb], (st >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
+      // dq_full(st) also covers the S^T / dP^T products of step st + 1, so the tiles of parity st + 1 can take step st + 3
+      // (and, the first time round, those of parity 0 step 2): always more than a step ahead of the MMA warp's need
+      if (st == 0 && steps > 2) write_aug(2);
+      if (st + 3 < steps) write_aug(st + 3);
       drain64(tm_dq0 + 64 * pb, q_col, grow0 + (n + st) * 128, &dq_drained[pb]);
     }
     if (ok) {   // the last dQ commit also covers the final dK / dV accumulation
@@ -1200,8 +1250,6 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     for (int st = 0; st < steps && ok; ++st) {
       const int m = n + st, stage = st & 1;
       FTH_TS(0);
-      if (!mbar_wait(&q_full[stage], (st >> 1) & 1, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
-      const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024) + 64 * h;
       FTH_TS(6);
       if (!mbar_wait(&sdp_full[h], st & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
       FTH_TS(1);
@@ -1211,7 +1259,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       unsigned char* ds_row = smem + L::kDsOff + (st & 1) * 32768 + h * 16384 + r * 128;
       // Four 16-column chunks with a rolling prefetch: the tensor-memory load of chunk c+1 is in flight during the math
       // of chunk c.  The bf16 P^T / dS^T of chunk c land on columns [8c, 8c+8) of the warpgroup's own range, all of
-      // which chunks <= c have already read.  lse2 / delta come as 128-bit broadcast loads.
+      // which chunks <= c have already read.
       auto math = [&](auto diag_tag) {
         constexpr bool kDiag = decltype(diag_tag)::value;
         uint32_t sv[2][16], dv[2][16];
@@ -1225,19 +1273,15 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
             tmem_ld_32x16(tm_s + lane_off + 64 * h + (c + 1) * 16, sv[(c + 1) & 1]);
             tmem_ld_32x16(tm_dp + lane_off + 64 * h + (c + 1) * 16, dv[(c + 1) & 1]);
           }
-          const float4* l4 = reinterpret_cast<const float4*>(vec + c * 16);
-          const float4* d4 = reinterpret_cast<const float4*>(vec + 128 + c * 16);
           uint32_t pk[8], dk[8];
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-            const float4 lv = l4[q4], dl = d4[q4];
-            const float ls[4] = {lv.x, lv.y, lv.z, lv.w}, de[4] = {dl.x, dl.y, dl.z, dl.w};
             float p[4], d[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              p[e] = exp2f(fmaf(__uint_as_float(sv[c & 1][q4 * 4 + e]), scale_log2, -ls[e]));
+              p[e] = exp2f(__uint_as_float(sv[c & 1][q4 * 4 + e]) * scale_log2);   // the accumulator already holds S - lse
               if (kDiag) { if (key > q_first + c * 16 + q4 * 4 + e) p[e] = 0.f; }
-              d[e] = p[e] * fmaf(__uint_as_float(dv[c & 1][q4 * 4 + e]), scale, -de[e]);
+              d[e] = (p[e] * scale) * __uint_as_float(dv[c & 1][q4 * 4 + e]);       // ... and dP - delta
             }
             pk[q4 * 2] = pack_bf16(p[0], p[1]); pk[q4 * 2 + 1] = pack_bf16(p[2], p[3]);
             dk[q4 * 2] = pack_bf16(d[0], d[1]); dk[q4 * 2 + 1] = pack_bf16(d[2], d[3]);
@@ -1372,6 +1416,11 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
   if (r) return r;
   r = make_tmap_bf16_2d(&tdo, d_out, (uint64_t)B * S, (uint64_t)nq * d, (uint64_t)nq * d, 128, 64);
   if (r) return r;
+  CUtensorMap tq64, tdo64;   // 64-row boxes: the head_dim-64 kernel loads Q and dO per query half
+  r = make_tmap_bf16_2d(&tq64, qkv, (uint64_t)B * S, rs, rs, 64, 64);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tdo64, d_out, (uint64_t)B * S, (uint64_t)nq * d, (uint64_t)nq * d, 64, 64);
+  if (r) return r;
   r = make_tmap_f32_2d(&tdq, img, (uint64_t)B * S, rs, rs, 128, 32);
   if (r) return r;
   const float scale = 1.f / sqrtf((float)d);
@@ -1379,7 +1428,7 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
   if (d == 64) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(flash_bwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd64Smem::kTotal); set = true; }
-    flash_bwd64_kernel<<<grid, kBwd64Threads, Bwd64Smem::kTotal, stream>>>(tq, tdo, tdq, lse2, delta, S, n_kv, g, scale,
+    flash_bwd64_kernel<<<grid, kBwd64Threads, Bwd64Smem::kTotal, stream>>>(tq, tq64, tdo64, tdq, lse2, delta, S, n_kv, g, scale,
                                                                         scale * 1.4426950408889634f, status, g_bwd_dbg);
   } else {
     static bool set = false;

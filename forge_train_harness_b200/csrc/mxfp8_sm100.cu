@@ -141,15 +141,6 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf8(int M, int N, uint32_t a_
          | ((uint32_t)(M >> 4) << 24)
          | (a_sf_id << 29);
 }
-// Shared-memory descriptor without swizzle: 8-row x 16-byte core matrices, `sbo` bytes between 8-row groups.
-__device__ __forceinline__ uint64_t make_smem_desc_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  return d;
-}
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }

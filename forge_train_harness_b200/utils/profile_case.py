@@ -4,6 +4,8 @@
 
 Cases (a few hundred MB on the device at most, GEMM operands larger than the 126 MB L2):
   gemm_fwd / gemm_dgrad / gemm_wgrad   the FC1 shape of the 0.5B model at 16384 tokens (M 16384, N 8192, K 1024)
+  gemm_mxfp8                            the FC1 shape of the 8B model at 4096 tokens (M 4096, N 8192 = one TP-4 shard, K 4096), e4m3 + e8m0
+  mxfp8_quant_row / mxfp8_quant_col     quantisation of a 16384 x 4096 bf16 activation
   flash_fwd / flash_bwd                 1 x 4096 tokens, 16 query / 2 KV heads of 64
   rmsnorm_fwd / rmsnorm_bwd / swiglu_fwd / swiglu_bwd / rope / cross_entropy    the 0.5B shapes at 16384 (CE: 4096) tokens
   microbatch                            engine steps of the 0.5B shape cut to 2 layers: one micro-batch of 4 x 4096 tokens per
@@ -26,12 +28,22 @@ def main(argv=None):
     dev = "cuda"
     r = lambda *s: torch.randn(*s, device=dev, dtype=torch.float32).mul_(0.5).to(torch.bfloat16)
     M, H, F, V, S, d, nkv, g = 16384, 1024, 4096, 73448, 4096, 64, 2, 8
-    if a.op.startswith("gemm"):
+    if a.op in ("gemm_fwd", "gemm_dgrad", "gemm_wgrad"):
         x, w, dy = r(M, H), r(2 * F, H), r(M, 2 * F)
         mg = torch.zeros(2 * F, H, device=dev)
         fn = {"gemm_fwd": lambda: _C.gemm(x, False, w, False, None, 1.0, 0, 0, 0),
               "gemm_dgrad": lambda: _C.gemm(dy, False, w, True, None, 1.0, 0, 0, 0),
               "gemm_wgrad": lambda: _C.gemm(dy, True, x, True, mg, 1.0, 1, 0, 0)}[a.op]
+    elif a.op.startswith("gemm_mxfp8") or a.op.startswith("mxfp8_quant"):
+        from ..ops import mxfp8 as mx
+        if a.op == "gemm_mxfp8":
+            x, w = r(4096, 4096), r(8192, 4096)
+            xq, xs = mx.quantize(x)
+            wq, ws = mx.quantize(w)
+            fn = lambda: mx.gemm(xq, xs, wq, ws, None, 1.0, 0)
+        else:
+            x = r(M, 4096)
+            fn = lambda: mx.quantize(x, a.op.endswith("col"))
     elif a.op in ("flash_fwd", "flash_bwd"):
         qkv = r(S, nkv * (g + 2) * d)
         out, lse = ops.attention_fwd(qkv, S, nkv, g, d)
