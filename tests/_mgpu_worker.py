@@ -19,6 +19,9 @@ def main():
            "dp_plain": dict(use_distributed_optimizer=False),
            "tp_sp": dict(tensor_parallel_size=int(os.environ.get("WORLD_SIZE", "1")), sequence_parallel=True),
            "pp": dict(pipeline_parallel_size=2),
+           "tp2dp2": dict(tensor_parallel_size=2, sequence_parallel=True, use_distributed_optimizer=True,
+                          ddp_bucket_elems=300_000),
+           "pp2dp2": dict(pipeline_parallel_size=2, use_distributed_optimizer=True, ddp_bucket_elems=300_000),
            "tp2pp2": dict(tensor_parallel_size=2, pipeline_parallel_size=2, sequence_parallel=True,
                           use_distributed_optimizer=True),
            "tp2pp2v2": dict(tensor_parallel_size=2, pipeline_parallel_size=2, virtual_pipeline_stages=2,

@@ -74,6 +74,18 @@ def test_tp2_pp2_and_interleaved_match_single_gpu():
     close(single, run("tp2pp2v2", 4), 2e-2)
 
 
+@needs4
+def test_fused_dp_under_tp_and_under_pp_matches_single_gpu():
+    """The peer-memory DP path with two data-parallel groups side by side (TP 2 x DP 2, PP 2 x DP 2), fused and NCCL."""
+    single = run("single", 1)
+    for mode in ("tp2dp2", "pp2dp2"):
+        nccl = run(mode, 4, {"FORGE_FUSED_DP": "0", "FORGE_FUSED_TP": "0"})
+        fused = run(mode, 4)
+        assert fused["fused"]
+        close(single, nccl, 2e-2)
+        close(single, fused, 2e-2)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
 def test_tp2_pp2_dp2_matches_single_gpu():
     close(run("single", 1), run("tp2pp2", 8), 2e-2)

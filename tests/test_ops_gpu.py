@@ -267,3 +267,26 @@ def test_mxfp8_linear_products_close_to_bf16(ops):
     lin.wgrad(dy, x, g)
     refw = dy.float().t() @ x.float()
     assert (g - refw).abs().max() <= 0.05 * refw.abs().max()
+
+
+def test_bounded_peer_wait_runs_out_and_reports_status(ops):
+    """Failure detection on the device side: a flag wait whose peer never arrives gives up after its limit, the kernel
+    returns, the host reads the status code, and the context keeps working (no trap, no endless spin)."""
+    from forge_train_harness_b200.ops.cuda_ops import _C, check_status
+    _C.read_status(True)
+    pads = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    # rank 0 of a 2-rank barrier whose rank 1 does not exist: slot 1 of the own pad is never written
+    _C.peer_barrier([p.data_ptr() for p in pads], 0, 1, 0, 0.05)
+    torch.cuda.synchronize()
+    assert int(pads[1][0]) == 1 and int(pads[0][0]) == 1      # the release stores went out
+    with pytest.raises(RuntimeError, match="peer flag never set"):
+        check_status()
+    check_status()                                             # the read cleared it
+    # the same barrier completes once the missing flag is there, and ordinary kernels still run
+    pads[0][1] = 2
+    _C.peer_barrier([p.data_ptr() for p in pads], 0, 2, 0, 0.05)
+    x, w = rnd(64, 256), rnd(256)
+    y, _ = ops.rmsnorm_fwd(x, w, 1e-6)
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.isfinite(y.float()).all()
