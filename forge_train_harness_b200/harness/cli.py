@@ -37,7 +37,7 @@ def main(argv=None) -> int:
     r.add_argument("--timeout", type=float, default=0.0)
     r.add_argument("--arg", action="append", default=[])
     r.add_argument("--artifacts", default=os.path.join(ROOT, ".artifacts", "runs"))
-    for name in ("guard", "anti-proxy", "unit", "info", "doctor"):
+    for name in ("guard", "anti-proxy", "unit", "info", "doctor", "env"):
         sub.add_parser(name)
     e = sub.add_parser("echo-config")
     e.add_argument("path")
@@ -58,6 +58,9 @@ def main(argv=None) -> int:
         return 0 if res["passed"] else 1
     if a.cmd == "unit":
         return subprocess.call([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests"), "-q", "-m", "not gpu"])
+    if a.cmd == "env":
+        from . import env_check
+        return env_check.main([])
     if a.cmd == "info":
         print(json.dumps({"result_markers": [RS.RESULT_BEGIN, RS.RESULT_END], "runner_metrics": RS.RUNNER_METRICS,
                           "schema_version": RS.RUN_SCHEMA_VERSION}, indent=1))

@@ -109,3 +109,39 @@ def test_cli_runs_real_cpu_gates(tmp_path, capsys):
     res = RS.extract_result(capsys.readouterr().out)
     assert rc == 0 and res["metrics"]["missing"] == [], res
     assert cli_main(["guard"]) == 0 and cli_main(["info"]) == 0
+
+
+def test_launch_summary_groups_kernels_and_reports_delta(tmp_path):
+    from forge_train_harness_b200.utils import launch_summary as LS
+    csv_text = '''==PROF== Connected to process 1
+"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"
+"0","1","python","h","void fth::gemm_bf16_kernel<256, 4, 0, 0, 0>(CUtensorMap)","1","7","(192, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","ns","200,000"
+"1","1","python","h","fth::rope_kernel(__nv_bfloat16 *, int)","1","7","(256, 1, 1)","(1184, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","us","28.5"
+"2","1","python","h","void fth::gemm_bf16_kernel<256, 4, 0, 0, 0>(CUtensorMap)","1","7","(192, 1, 1)","(148, 1, 1)","0","10.0","Command line profiler metrics","gpu__time_duration.sum","ns","100,000"
+'''
+    launches = LS.parse_launches(csv_text.splitlines(keepends=True))
+    assert launches == [("void fth::gemm_bf16_kernel<256, 4, 0, 0, 0>", 200.0), ("fth::rope_kernel", 28.5),
+                        ("void fth::gemm_bf16_kernel<256, 4, 0, 0, 0>", 100.0)]
+    s = LS.summarise(launches)
+    assert s["launches"] == 3 and abs(s["total_us"] - 328.5) < 1e-6
+    assert s["kernels"][0]["kernel"].startswith("void fth::gemm") and s["kernels"][0]["launches"] == 2
+    prev = {"total_us": 400.0, "kernels": [{"kernel": "fth::rope_kernel", "launches": 1, "us": 60.0, "share": 0.15},
+                                          {"kernel": "fth::old_kernel", "launches": 1, "us": 340.0, "share": 0.85}]}
+    d = LS.with_delta(s, prev)
+    rope = [k for k in d["kernels"] if k["kernel"] == "fth::rope_kernel"][0]
+    assert rope["delta_us"] == -31.5 and d["kernels"][0]["delta_us"] is None and d["gone"] == ["fth::old_kernel"]
+    md = LS.to_markdown(d)
+    assert "delta us" in md and "no longer launched" in md and "-31.5" in md
+    p = tmp_path / "l.csv"
+    p.write_text(csv_text)
+    assert LS.main([str(p), "--json", str(tmp_path / "s.json"), "--md", str(tmp_path / "s.md")]) == 0
+    assert (tmp_path / "s.json").exists() and (tmp_path / "s.md").read_text().startswith("3 launches")
+
+
+def test_env_check_reports_pins_and_toolkit():
+    from forge_train_harness_b200.harness import env_check
+    rows = env_check.checks(nvcc_output="Cuda compilation tools, release 12.9, V12.9.86")
+    names = {r[0]: r for r in rows}
+    assert names["python"][1] and names["torch"][1] and names["cuda toolkit (nvcc, sm_100a)"][1]
+    bad = {r[0]: r for r in env_check.checks(nvcc_output="Cuda compilation tools, release 11.8, V11.8.89")}
+    assert not bad["cuda toolkit (nvcc, sm_100a)"][1]
