@@ -659,7 +659,11 @@ struct BwdSmem {
   static constexpr int kDsOff = kQdOOff + kStages * 2 * kTile;    // dS^T as an MN-major operand: 2 x [128 x 128 B]
   static constexpr int kStgOff = kDsOff + 32768;                  // fp32 staging: one [128 rows x 128 B] per warpgroup
   static constexpr int kVecOff = kStgOff + 32768;                 // per stage: lse2[128], delta[128] fp32
-  static constexpr int kBarOff = kVecOff + kStages * 1024;
+  // augmentation operands (K-major, no swizzle, 8-row groups 256 B apart): a constant [128 x 16] tile of ones and two
+  // [128 x 16] tiles with -lse2 / scale_log2 and -delta of the step's queries as bf16 high + low parts in columns 0 and 1
+  static constexpr int kOnesOff = kVecOff + kStages * 1024;       // 4 KB
+  static constexpr int kAugOff = kOnesOff + 4096;                 // 2 x 4 KB
+  static constexpr int kBarOff = kAugOff + 8192;
   static constexpr int kTotal = kBarOff + 512 + 1024;
 };
 
@@ -718,7 +722,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
   uint64_t* pds_full = sdp_full + 1;   // P^T, dS^T written (one arrival per compute warp)
   uint64_t* dq_full = pds_full + 1;    // dV, dK, dQ MMAs of this step finished
   uint64_t* dq_drained = dq_full + 1;  // dQ read out of tensor memory (one arrival per warp)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 1);
+  uint64_t* aug_full = dq_drained + 1; // augmentation tiles of the step written (one arrival per compute warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aug_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -742,6 +747,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
     mbar_init(pds_full, 8);        // one arrival per compute warp
     mbar_init(dq_full, 1);
     mbar_init(dq_drained, 8);
+    mbar_init(aug_full, 8);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -798,7 +804,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
       const uint32_t ds_addr = smem_u32(smem + L::kDsOff);
       bool ok = mbar_wait(kv_full, 0, abort_flag, status, kTimeoutSmemFull);
       int stage = 0;
-      uint32_t phase = 0, ph_pds = 0, ph_drain = 0;
+      uint32_t phase = 0, ph_pds = 0, ph_drain = 0, ph_aug = 0;
       auto issue_sdp = [&](uint32_t q_addr, uint32_t do_addr) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -810,9 +816,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
           const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
           umma_bf16_ss(tm_dp, make_smem_desc(v_addr + off, 0, 1024), make_smem_desc(do_addr + off, 0, 1024), idesc_st, kk != 0);
         }
+        // one more k-step each: ones x (-lse2 / scale_log2) and ones x (-delta), so the accumulators hold the exp2 argument
+        // and dP - delta and the compute warps fetch no per-query vectors (their broadcast shared-memory loads were what the
+        // math phase waited for)
+        const uint64_t ones_desc = make_smem_desc_plain(smem_u32(smem + L::kOnesOff), 128, 256);
+        umma_bf16_ss(tm_s, ones_desc, make_smem_desc_plain(smem_u32(smem + L::kAugOff), 128, 256), idesc_st, 1u);
+        umma_bf16_ss(tm_dp, ones_desc, make_smem_desc_plain(smem_u32(smem + L::kAugOff + 4096), 128, 256), idesc_st, 1u);
         umma_commit(sdp_full);
       };
       if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, status, kTimeoutSmemFull);
+      if (ok) { ok = mbar_wait(aug_full, ph_aug, abort_flag, status, kTimeoutSmemFull); ph_aug ^= 1; }
       if (ok) {
         tc_fence_after();
         const uint32_t q0a = smem_u32(smem + L::kQdOOff);
@@ -849,6 +862,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
             if (!mbar_wait(dq_drained, ph_drain, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
             ph_drain ^= 1;
           }
+          if (!mbar_wait(aug_full, ph_aug, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          ph_aug ^= 1;
           tc_fence_after();
           const uint32_t qn = smem_u32(smem + L::kQdOOff + nstage * 2 * L::kTile);
           issue_sdp(qn, qn + L::kTile);
@@ -895,11 +910,36 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         }
       }
     };
+    {
+      // one-time: zero the augmentation tiles (only columns 0 and 1 are rewritten) and build the ones tile
+      const int t = threadIdx.x;   // 0 .. 255
+      uint4* z = reinterpret_cast<uint4*>(smem + L::kAugOff);
+      for (int i = t; i < 8192 / 16; i += 256) z[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (t < 128) {
+        unsigned char* one_row = smem + L::kOnesOff + (t >> 3) * 256 + (t & 7) * 16;
+        *reinterpret_cast<uint4*>(one_row) = make_uint4(0x3F803F80u, 0u, 0u, 0u);   // bf16 1.0, 1.0, zeros
+        *reinterpret_cast<uint4*>(one_row + 128) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      named_barrier_sync(3, 256);
+    }
+    const float inv_scale_log2 = 1.f / scale_log2, inv_scale = 1.f / scale;
     for (int st = 0; st < steps && ok; ++st) {
       const int m = n + st;
       // q_full is also what delivers lse2 / delta of this query block
       if (!mbar_wait(&q_full[stage], qphase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
-      const float* vec = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024) + 64 * h;
+      {
+        // thread t < 128 writes the S^T tile's row of query t, thread 128 + t the dP^T tile's: value as bf16 high + low part.
+        // The previous step's products have finished reading the tiles (this warp has seen their sdp_full).
+        const int t = threadIdx.x, q = t & 127;
+        const float* vsrc = reinterpret_cast<const float*>(smem + L::kVecOff + stage * 1024);
+        const float val = (t < 128) ? -vsrc[q] * inv_scale_log2 : -vsrc[128 + q] * inv_scale;
+        const __nv_bfloat16 hi = __float2bfloat16(val);
+        const __nv_bfloat16 lo = __float2bfloat16(val - __bfloat162float(hi));
+        unsigned char* dst = smem + L::kAugOff + (t < 128 ? 0 : 4096) + (q >> 3) * 256 + (q & 7) * 16;
+        *reinterpret_cast<uint32_t*>(dst) = (uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(lo) << 16);
+        fence_proxy_async();
+        mbar_arrive_warp(aug_full);
+      }
       if (!mbar_wait(sdp_full, ph_sdp, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
       ph_sdp ^= 1;
       tc_fence_after();
@@ -917,14 +957,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           const int qc = c * 32 + e;
-          float p0 = exp2f(fmaf(__uint_as_float(sv[qc]), scale_log2, -vec[qc]));
-          float p1 = exp2f(fmaf(__uint_as_float(sv[qc + 1]), scale_log2, -vec[qc + 1]));
+          float p0 = exp2f(__uint_as_float(sv[qc]) * scale_log2);        // the accumulator already holds S - lse
+          float p1 = exp2f(__uint_as_float(sv[qc + 1]) * scale_log2);
           if (diag) {
             if (key > q_first + qc) p0 = 0.f;
             if (key > q_first + qc + 1) p1 = 0.f;
           }
-          const float d0 = p0 * fmaf(__uint_as_float(dv[qc]), scale, -vec[128 + qc]);
-          const float d1 = p1 * fmaf(__uint_as_float(dv[qc + 1]), scale, -vec[128 + qc + 1]);
+          const float d0 = (p0 * scale) * __uint_as_float(dv[qc]);           // ... and dP - delta
+          const float d1 = (p1 * scale) * __uint_as_float(dv[qc + 1]);
           pk[e / 2] = pack_bf16(p0, p1);
           dk[e / 2] = pack_bf16(d0, d1);
         }

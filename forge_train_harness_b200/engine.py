@@ -204,6 +204,17 @@ class Trainer:
                     self.graph_replays += 1
                     self.stats += self._graph_stats
                     continue
+            last = mb == self.grad_accum - 1
+            if last and self.cfg.parallel.overlap_grad_reduce and self.opt.overlap_eligible():
+                # eager last micro-batch: each gradient bucket is handed to the DP reduction as soon as the backward has
+                # passed its parameters, so the collective runs under the rest of the backward
+                self.opt.begin_overlap()
+                self.chunks[0].on_grads_final = self.opt.grads_final
+                try:
+                    self.stats += self._fwd_bwd(batch)
+                finally:
+                    self.chunks[0].on_grads_final = None
+                continue
             self.stats += self._fwd_bwd(batch)
 
     def _run_microbatches_pp(self):

@@ -66,6 +66,7 @@ class ModelChunk:
         self.ds_mtp = cfg.depth_scale(cfg.mtp_num_layers)
         self.capture = capture  # optional hook: capture(kind, fqn, tensor)
         self.recompute = False
+        self.on_grads_final = None  # callable(prefix): every parameter under `prefix` has its final gradient of the step
 
     # ------------------------------------------------------------------
     def _cap(self, kind, fqn, t):
@@ -209,15 +210,23 @@ class ModelChunk:
     def run_backward(self, batch: dict, cache: ChunkCache, g_out: torch.Tensor | None = None):
         """Accumulates weight gradients; returns dL/dx_in (None on an embedding chunk)."""
         S = batch["seq_len"]
+        done = self.on_grads_final
         if self.spec.has_head:
             extra = self._mtp_bwd(batch, cache, S) if cache.mtp is not None else None
             g = self._head_bwd({"dlogits": cache.dlogits, "nff": cache.nff, "x_last": cache.x_last,
                                 "rstd_f": cache.rstd_f}, "norm.weight", extra)
             cache.dlogits = None
+            if done is not None:
+                done("mtp.")
+                done("norm.weight")
+                if not self.cfg.tie_embeddings:   # a tied head shares the embedding's gradient, final only at the very end
+                    done("output.weight")
         else:
             g = g_out
         for li, c in zip(reversed(self.spec.layers), reversed(cache.layers)):
             g = self._layer_bwd(f"layers.{li}.", c, g, self.ds, S)
+            if done is not None:
+                done(f"layers.{li}.")
         if self.spec.has_embedding:
             self._cap("bwd", "tok_embeddings", g)
             self._embed_bwd(g, cache.ids)

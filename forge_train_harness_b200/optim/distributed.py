@@ -117,14 +117,52 @@ class DistributedOptimizer:
                 "tok_embeddings.weight" in st.grads and (topo.is_first_stage or topo.is_last_stage):
             dist.all_reduce(st.g("tok_embeddings.weight"), group=topo.embed_group)
 
+    # -- bucket-by-bucket overlap of the DP reduction with the last micro-batch's backward -------------------------
+    def overlap_eligible(self) -> bool:
+        """Buckets can be reduced while the backward still runs when nothing has to be summed over model-parallel ranks
+        first (no TP / PP) and the library path is in use (the peer-memory path reduces after its own flag barrier)."""
+        t = self.topo
+        return t.dp > 1 and t.tp == 1 and t.pp == 1 and self.fused is None
+
+    def begin_overlap(self) -> None:
+        self._done_names: set = set()
+        self._launched = 0
+        self._works: list = []
+        self.overlapped_buckets = 0
+
+    def grads_final(self, prefix: str) -> None:
+        """Called by the backward when every parameter whose name starts with ``prefix`` has its final gradient of this
+        step.  Launches, in bucket order, the asynchronous reduction of every bucket that is now complete (the flat
+        buffer is laid out in backward order, so buckets complete front to back)."""
+        st, topo = self.store, self.topo
+        self._done_names.update(n for n in st.offsets if n.startswith(prefix))
+        while self._launched < len(st.buckets) and all(n in self._done_names for n in st.buckets[self._launched].names):
+            b = st.buckets[self._launched]
+            buf = st.flat_grad[b.start:b.end]
+            if self.sharded and buf.device.type != "cpu":
+                r0, r1, _ = self.my_ranges[self._launched]
+                w = dist.reduce_scatter_tensor(st.flat_grad[r0:r1], buf, group=topo.dp_group, async_op=True)
+            else:
+                w = dist.all_reduce(buf, group=topo.dp_group, async_op=True)
+            self._works.append(w)
+            self._launched += 1
+            self.overlapped_buckets += 1
+
     def _reduce_grads(self) -> None:
         topo, st = self.topo, self.store
         if topo.dp == 1:
             return
+        launched = getattr(self, "_launched", 0)
+        for w in getattr(self, "_works", []):
+            w.wait()
+        self._works, self._launched = [], 0
         if not self.sharded:
-            dist.all_reduce(st.flat_grad, group=topo.dp_group)
+            if launched == 0:
+                dist.all_reduce(st.flat_grad, group=topo.dp_group)
+            elif launched < len(st.buckets):
+                dist.all_reduce(st.flat_grad[st.buckets[launched].start:], group=topo.dp_group)
             return
-        for b, (r0, r1, _) in zip(st.buckets, self.my_ranges):
+        for b, (r0, r1, _) in list(zip(st.buckets, self.my_ranges))[launched:]:
             buf = st.flat_grad[b.start:b.end]
             if buf.device.type == "cpu":
                 dist.all_reduce(buf, group=topo.dp_group)

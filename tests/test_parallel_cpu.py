@@ -85,3 +85,27 @@ def test_tp2_pp2_dp2_sp_zero_interleaved():
                    use_distributed_optimizer=True, gbs=16, ddp_bucket_elems=20000)
     res = run_ranks(8, _train, cfg)
     check(single(cfg), res[0])
+
+
+def _train_overlap(rank, world, cfg):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    out = []
+    for _ in range(cfg.train.num_steps):
+        r = tr.train_step()
+        out.append((float(r["loss"]), float(r["grad_norm"])))
+    n = getattr(tr.opt, "overlapped_buckets", 0)
+    nb = len(tr.store.buckets)
+    tr.close()
+    return out, n, nb
+
+
+@pytest.mark.parametrize("zero", [False, True])
+def test_dp2_bucket_overlap_is_the_same_reduction(zero):
+    """Buckets handed to the DP reduction while the last micro-batch's backward still runs give the same numbers as the
+    reduction after the backward, and all buckets but the one holding the (tied) embedding go out early."""
+    cfg = base_cfg(steps=3, mbs=2, gbs=8, use_distributed_optimizer=zero, ddp_bucket_elems=20000, overlap_grad_reduce=True)
+    on = run_ranks(2, _train_overlap, cfg)
+    off = run_ranks(2, _train_overlap, cfg.replace(parallel={"overlap_grad_reduce": False}))
+    assert on[0][0] == off[0][0] and on[0][0] == on[1][0]
+    assert off[0][1] == 0
+    assert on[0][2] > 2 and 0 < on[0][1] < on[0][2]
