@@ -15,7 +15,8 @@ import tokenize
 
 BANNED = ["megatron", "deepspeed", "torch.nn.Module", "torch.optim", "torch.autograd", "torch.utils.data", "torch.amp",
           ".backward(", "requires_grad=True", "torch.compile", "import triton"]
-PROXY = ["baseline._ref", "baseline/_ref", "training_engine_tensor", "train_pure_mup_mtp", "/root/reference"]
+PROXY = ["baseline._ref", "baseline/_ref", "training_engine_tensor", "train_pure_mup_mtp", "model_pure_mup_mtp"]
+PROXY += [p for p in os.environ.get("FORGE_REFERENCE_ROOTS", "").split(os.pathsep) if p]   # checkout paths of the reference, if any
 ENGINE_DIRS = ["models", "ops", "optim", "parallel", "data", "ckpt", "engine.py", "train.py"]
 ALLOW = {"ops/torch_ops.py": {"torch.nn.Module"}, "data/sources.py": {"megatron"}}  # the corpus FORMAT is called Megatron binary
 
