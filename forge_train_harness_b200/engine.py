@@ -180,7 +180,7 @@ class Trainer:
             self.store.zero_grad()
 
     def _launch_count(self) -> int:
-        if self.device.type != "cuda" or self.ops.name != "sm100":
+        if self.device.type != "cuda" or not self.ops.name.startswith("sm100"):
             return 0
         from .ops.cuda_ops import _C
         return int(_C.launch_count())
