@@ -759,7 +759,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
 // works on the other half and on the next step:
 //     MMA order:  ... | dV_A dK_A (i) | S_A dP_A (i+1) | dV_B dK_B (i) | dQ (i) | S_B dP_B (i+1) | dV_A dK_A (i+1) | ...
 // Warpgroup h computes half h.  dS^T lives in a double-buffered shared-memory operand and dQ in a double-buffered
-// tensor-memory tile (512 columns: S^T 128, dP^T 128, dK 64, dV 64, dQ 2 x 64), so neither stalls the next step.
+// tensor-memory tile; tensor memory (512 columns): S^T 128, dP^T 128, dK 64, dV 64, dQ 64, K 32, V 32.
 // ---------------------------------------------------------------------------------------------------------------------
 struct Bwd64Smem {
   static constexpr int kTile = 128 * 64 * 2;
@@ -793,6 +793,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   uint64_t* pds_full = sdp_full + 2;    // [2] per half: P^T, dS^T written (4 arrivals, one per warp)
   uint64_t* dq_full = pds_full + 2;     // [2] per dQ buffer
   uint64_t* dq_drained = dq_full + 2;   // [2] per dQ buffer (4 arrivals)
+  uint64_t* kv_tmem = dq_drained + 1;   // K and V copied into tensor memory (4 arrivals); dq_full / dq_drained use slot 0 only
   uint64_t* aug_full = dq_drained + 2;  // [2] per stage: augmentation tiles written (4 arrivals, one per drain warp)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aug_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -813,6 +814,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
+    mbar_init(kv_tmem, 4);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[2 * s], 1); mbar_init(&q_full[2 * s + 1], 1);
       mbar_init(&q_empty[2 * s], 1); mbar_init(&q_empty[2 * s + 1], 1);
@@ -830,7 +832,10 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dk = tmem_base + 256, tm_dv = tmem_base + 320;
-  const uint32_t tm_dq0 = tmem_base + 384;  // two 64-column buffers
+  const uint32_t tm_dq0 = tmem_base + 384;  // one 64-column buffer
+  // K and V as bf16 A operands in tensor memory (32 columns each): S^T = K Q^T and dP^T = V dO^T then fetch only their
+  // 2 KB B operand from shared memory per MMA instead of 6 KB, and the shared-memory ports are what these MMAs wait for
+  const uint32_t tm_k = tmem_base + 448, tm_v = tmem_base + 480;
 
   if (warp == 12) {
     if (elect_one()) {
@@ -864,16 +869,17 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);
       const uint32_t k_addr = smem_u32(smem + L::kKOff), v_addr = smem_u32(smem + L::kVOff);
       bool ok = mbar_wait(kv_full, 0, abort_flag, status, kTimeoutSmemFull);
+      if (ok) ok = mbar_wait(kv_tmem, 0, abort_flag, status, kTimeoutTmemFull);
       // S^T_h = K Q_h^T and dP^T_h = V dO_h^T for query half h of the tile in `stage`
       auto issue_sdp = [&](int stage, int h) {
         const uint32_t q_addr = smem_u32(smem + L::kQdOOff + stage * 2 * L::kTile) + h * 8192;
         const uint32_t do_addr = q_addr + L::kTile;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ss(tm_s + 64 * h, make_smem_desc(k_addr + kk * 32, 0, 1024), make_smem_desc(q_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
+          umma_bf16_ts(tm_s + 64 * h, tm_k + kk * 8, make_smem_desc(q_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ss(tm_dp + 64 * h, make_smem_desc(v_addr + kk * 32, 0, 1024), make_smem_desc(do_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
+          umma_bf16_ts(tm_dp + 64 * h, tm_v + kk * 8, make_smem_desc(do_addr + kk * 32, 0, 1024), idesc_st, kk != 0);
         // fifth k-step: ones x (-lse2 / scale_log2) resp. ones x (-delta), so the accumulators already hold the exponent
         // argument and dP - delta and no thread has to fetch per-query vectors
         const uint32_t aug = smem_u32(smem + L::kAugOff + stage * 8192);
@@ -934,17 +940,17 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
           issue_sdp(nstage, 1);
         }
         // ---- dQ(st) = dS K into buffer st & 1 (free once dQ(st-2) was drained)
-        if (st >= 2) {
-          if (!mbar_wait(&dq_drained[st & 1], ((st >> 1) - 1) & 1, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
+        if (st >= 1) {   // the drain warps have read dQ(st - 1) out of the (single) buffer
+          if (!mbar_wait(&dq_drained[0], (st - 1) & 1, abort_flag, status, kTimeoutTmemEmpty)) { ok = false; break; }
           tc_fence_after();
         }
         FTH_MS(5);
         const uint32_t ds_addr = smem_u32(smem + L::kDsOff + (st & 1) * 32768);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ss(tm_dq0 + 64 * (st & 1), make_smem_desc(ds_addr + kk * 2048, 16384, 1024),
+          umma_bf16_ss(tm_dq0, make_smem_desc(ds_addr + kk * 2048, 16384, 1024),
                        make_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_dq, kk != 0);
-        umma_commit(&dq_full[st & 1]);
+        umma_commit(&dq_full[0]);
         FTH_MS(6);
       }
 #undef FTH_MS
@@ -1004,16 +1010,33 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       write_aug(0);
       if (steps > 1) write_aug(1);
     }
-    bool ok = true;
+    bool ok = mbar_wait(kv_full, 0, abort_flag, status, kTimeoutSmemFull);
+    if (ok) {
+      // row r of the 128B-swizzled K / V tile -> lane r, 32 columns of packed bf16 (the layout a tensor-memory A operand has)
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const unsigned char* rowp = smem + (which == 0 ? L::kKOff : L::kVOff) + r * 128;
+        uint32_t w[32];
+#pragma unroll
+        for (int p8 = 0; p8 < 8; ++p8) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(rowp + ((p8 ^ (r & 7)) * 16));
+          w[p8 * 4] = q4.x; w[p8 * 4 + 1] = q4.y; w[p8 * 4 + 2] = q4.z; w[p8 * 4 + 3] = q4.w;
+        }
+        tmem_st_32x16((which == 0 ? tm_k : tm_v) + lane_off, w);
+        tmem_st_32x16((which == 0 ? tm_k : tm_v) + lane_off + 16, w + 16);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(kv_tmem);
+    }
     for (int st = 0; st < steps && ok; ++st) {
-      const int pb = st & 1;
-      if (!mbar_wait(&dq_full[pb], (st >> 1) & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
+      if (!mbar_wait(&dq_full[0], st & 1, abort_flag, status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       // dq_full(st) also covers the S^T / dP^T products of step st + 1, so the tiles of parity st + 1 can take step st + 3
       // (and, the first time round, those of parity 0 step 2): always more than a step ahead of the MMA warp's need
       if (st == 0 && steps > 2) write_aug(2);
       if (st + 3 < steps) write_aug(st + 3);
-      drain64(tm_dq0 + 64 * pb, q_col, grow0 + (n + st) * 128, &dq_drained[pb]);
+      drain64(tm_dq0, q_col, grow0 + (n + st) * 128, &dq_drained[0]);
     }
     if (ok) {   // the last dQ commit also covers the final dK / dV accumulation
       drain64(tm_dk, k_col, grow0 + n * 128, nullptr);
