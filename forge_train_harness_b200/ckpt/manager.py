@@ -214,6 +214,10 @@ def _ordered_names(tr):
 
 
 def _save_legacy(tr, root: str) -> str:
+    """Writes exactly what the reference's ``save_checkpoint`` writes (train_loop.py:1354-1406), so that its own
+    ``load_checkpoint`` (train_loop.py:1409-1486) reads the file: tensors in lists in parameter order, the numpy and python
+    RNG states as ``pickle.dumps`` BYTES, the torch CPU and CUDA generator states as uint8 tensors.  ``data_cursor`` is an
+    extra key the reference ignores."""
     if tr.topo.tp != 1 or tr.topo.pp != 1:
         raise ValueError("the legacy step_<N>/training_state.pt format supports TP = PP = 1 only")
     state = _per_param_optimizer_state(tr)
@@ -223,20 +227,32 @@ def _save_legacy(tr, root: str) -> str:
         names = _ordered_names(tr)
         rng = tr.rng_state()
         import pickle
+        cuda_rng = rng.get("cuda")
+        if cuda_rng is None:  # written on a CPU run: a well-formed (seed 0, offset 0) CUDA generator state
+            cuda_rng = torch.zeros(16, dtype=torch.uint8)
         obj = {"fp32_master": [state[n]["master"] for n in names],
                "exp_avgs": [state[n]["exp_avg"] for n in names],
                "exp_avg_sqs": [state[n]["exp_avg_sq"] for n in names],
                "state_steps": [torch.tensor(float(tr.opt.step_count)) for _ in names],
                "step": torch.tensor(tr.step, dtype=torch.int32),
-               "rng_torch": rng["torch"], "rng_cuda": rng.get("cuda"),
-               "rng_numpy": torch.frombuffer(bytearray(pickle.dumps(rng["numpy"])), dtype=torch.uint8),
-               "rng_random": torch.frombuffer(bytearray(pickle.dumps(rng["python"])), dtype=torch.uint8),
+               "rng_torch": rng["torch"], "rng_cuda": cuda_rng.cpu(),
+               "rng_numpy": pickle.dumps(rng["numpy"]),
+               "rng_random": pickle.dumps(rng["python"]),
                "data_cursor": torch.tensor(tr.data_state().get("cursor", -1), dtype=torch.int64)}
         tmp = os.path.join(d, "training_state.pt.tmp")
         _fsync_write(tmp, obj)
         os.replace(tmp, os.path.join(d, "training_state.pt"))
     _barrier()
     return d
+
+
+def _unpickle_rng(blob):
+    """RNG states arrive as ``pickle.dumps`` bytes (the reference's files and this module's) or as the uint8 tensor of
+    those bytes (files written by earlier versions of this module)."""
+    import pickle
+    if isinstance(blob, torch.Tensor):
+        blob = blob.cpu().numpy().tobytes()
+    return pickle.loads(blob)
 
 
 def _load_legacy(tr, file: str, weights_only: bool) -> int:
@@ -255,8 +271,17 @@ def _load_legacy(tr, file: str, weights_only: bool) -> int:
     tr.opt.scatter_full_state(flat, opt_step, weights_only=weights_only)
     if not weights_only:
         tr.step = int(sd["step"])
-        import pickle
-        torch.set_rng_state(sd["rng_torch"])
+        # all four generators, as the reference restores them (train_loop.py:1476-1483)
+        import random
+
+        import numpy as np
+        torch.set_rng_state(sd["rng_torch"].cpu())
+        if tr.device.type == "cuda" and sd.get("rng_cuda") is not None:
+            torch.cuda.set_rng_state(sd["rng_cuda"].cpu(), tr.device)
+        if sd.get("rng_numpy") is not None:
+            np.random.set_state(_unpickle_rng(sd["rng_numpy"]))
+        if sd.get("rng_random") is not None:
+            random.setstate(_unpickle_rng(sd["rng_random"]))
         cur = int(sd.get("data_cursor", torch.tensor(-1)))
         if cur >= 0:
             tr.source.load_state_dict({"cursor": cur})

@@ -33,6 +33,10 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
                   long long ldc, int M, int N, int K, float alpha, int epi, int bn, int max_ctas, int* status,
                   cudaStream_t stream);
 
+// Deterministic mode: one k split per output tile, so the fp32 reduce-adds of an accumulating epilogue have a fixed order.
+void fth_gemm_set_deterministic(int on);
+void fth_tmap_cache_stats(unsigned long long* hits, unsigned long long* misses);
+
 int fth_flash_fwd(const void* qkv, void* out, float* lse, int B, int S, int n_kv, int g, int d, int* status,
                   cudaStream_t stream);
 

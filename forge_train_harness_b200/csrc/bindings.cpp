@@ -385,6 +385,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_segments", &adamw_segments);
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
+  m.def("gemm_set_deterministic", [](bool on) { fth_gemm_set_deterministic(on ? 1 : 0); });
+  m.def("tmap_cache_stats", []() {
+    unsigned long long h = 0, mi = 0;
+    fth_tmap_cache_stats(&h, &mi);
+    return std::vector<int64_t>{(int64_t)h, (int64_t)mi};
+  });
   m.def("mxfp8_quant", &mxfp8_quant);
   m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("flash_fwd", &flash_fwd);

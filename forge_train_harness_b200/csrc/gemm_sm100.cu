@@ -13,9 +13,17 @@
 // reference does with a bf16 GEMM followed by .float() and add_ (backward.py:90).
 //
 // CTA = 6 warps: warp 0 TMA producer, warp 1 MMA issuer (one elected thread) and TMEM owner, warps 2-5
-// epilogue (one TMEM lane quarter each).  Tile 128 x BN x 64, 4-6 stage ring, two accumulator stages
+// epilogue (one TMEM lane quarter each).  Tile 128 x BN x 64, 4-8 stage ring, two accumulator stages
 // (2 x BN <= 512 TMEM columns) so the epilogue of tile i overlaps the mainloop of tile i+1.  Ragged M / N / K
 // are handled by TMA zero fill on loads and predicated stores.  Every mbarrier wait is bounded.
+//
+// CTAS = 2 is the CTA-pair form (tcgen05.mma.cta_group::2): a cluster of two CTAs on neighbouring SMs computes one
+// 256 x BN tile.  Each CTA loads its own 128 rows of A and only HALF of the B tile (its BN/2 rows) with unicast TMA,
+// and keeps its own 128 x BN accumulator in its own tensor memory, so per output element the shared-memory fill and
+// the L2 -> SM operand traffic drop by a third against the one-CTA 128 x 256 tile.  CTA rank 0 issues the MMAs for
+// both; the ring's "full" barriers live in rank 0 and count the bytes of both CTAs' loads, "empty" / "accumulator
+// full" are signalled in both CTAs by one multicast tcgen05.commit, "accumulator empty" collects the eight epilogue
+// warps of the pair in rank 0.  No TMA load is multicast.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -31,10 +39,10 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kGemmThreads = 192;
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CTAS = 1>
 struct GemmSmem {
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBBytes = (BN / CTAS) * BK * 2;  // a CTA of a pair holds half of the B tile
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiOffset = STAGES * kStageBytes;  // two 128-row x 128-byte staging buffers
   static constexpr int kEpiBytes = 2 * BM * 128;
@@ -44,12 +52,14 @@ struct GemmSmem {
 
 enum EpiMode : int { kEpiBf16 = 0, kEpiF32Accum = 1, kEpiF32Store = 2 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, int M, int N, int K, float alpha, int accumulate,
                  int group_m, int k_splits, int* __restrict__ status) {
-  using S = GemmSmem<BN, STAGES>;
+  using S = GemmSmem<BN, STAGES, CTAS>;
+  constexpr int BNH = BN / CTAS;       // B rows this CTA loads
+  constexpr int TM = BM * CTAS;        // rows of the tile the CTA (pair) computes
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
@@ -60,7 +70,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+  const int unit = (int)blockIdx.x / CTAS, n_units = (int)gridDim.x / CTAS;  // a unit = a CTA or a CTA pair
+  const int m_tiles = (M + TM - 1) / TM, n_tiles = (N + BN - 1) / BN;
   // split-K (accumulating fp32 epilogue only): work item = (k split, tile); every split reduce-adds into C
   const int mn_tiles = m_tiles * n_tiles;
   const int total_tiles = mn_tiles * k_splits;
@@ -74,18 +86,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tempty_bar[a], 4 * CTAS);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_pair(tmem_slot, 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -109,27 +127,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += n_units) {
         int mb, nb;
         tile_coords(t, mb, nb);
+        const int row_a = (mb * CTAS + (int)cta_rank) * BM;   // this CTA's rows of A
+        const int row_b = nb * BN + (int)cta_rank * BNH;      // this CTA's rows of B
         const int kb0 = (t / mn_tiles) * k_per_split;
         const int kb1 = min(kb0 + k_per_split, k_blocks_all);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) { ok = false; break; }
           unsigned char* sa = smem + stage * S::kStageBytes;
           unsigned char* sb = sa + S::kABytes;
-          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
-          if constexpr (!A_MN) {
-            tma_load_2d(sa, &tmap_a, kb * BK, mb * BM, &full_bar[stage]);
-          } else {
+          if constexpr (CTAS == 2) {
+            // rank 0's barrier counts the bytes of both CTAs; a peer's bytes may land before the expectation is posted
+            const uint32_t fb = map_to_cta(&full_bar[stage], 0);
+            if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::kStageBytes);
+            if constexpr (!A_MN) {
+              tma_load_2d_pair(sa, &tmap_a, kb * BK, row_a, fb);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmap_a, mb * BM + c * 64, kb * BK, &full_bar[stage]);
-          }
-          if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmap_b, kb * BK, nb * BN, &full_bar[stage]);
-          } else {
+              for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * 8192, &tmap_a, row_a + c * 64, kb * BK, fb);
+            }
+            if constexpr (!B_MN) {
+              tma_load_2d_pair(sb, &tmap_b, kb * BK, row_b, fb);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tmap_b, nb * BN + c * 64, kb * BK, &full_bar[stage]);
+              for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * 8192, &tmap_b, row_b + c * 64, kb * BK, fb);
+            }
+          } else {
+            mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+            if constexpr (!A_MN) {
+              tma_load_2d(sa, &tmap_a, kb * BK, row_a, &full_bar[stage]);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmap_a, row_a + c * 64, kb * BK, &full_bar[stage]);
+            }
+            if constexpr (!B_MN) {
+              tma_load_2d(sb, &tmap_b, kb * BK, row_b, &full_bar[stage]);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BNH / 64; ++c) tma_load_2d(sb + c * 8192, &tmap_b, row_b + c * 64, kb * BK, &full_bar[stage]);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -138,14 +176,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+    if (cta_rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(TM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += n_units) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -160,13 +198,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t adesc = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024) : make_smem_desc(sa + kk * 32, 0, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024) : make_smem_desc(sb + kk * 32, 0, 1024);
-            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+            if constexpr (CTAS == 2) umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+            else umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if constexpr (CTAS == 2) umma_commit_pair(&empty_bar[stage], 3);
+          else umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        // accumulator complete
+        if constexpr (CTAS == 2) umma_commit_pair(&tfull_bar[acc], 3);
+        else umma_commit(&tfull_bar[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -183,16 +226,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int t = unit; t < total_tiles; t += n_units) {
       int mb, nb;
       tile_coords(t, mb, nb);
+      const int row0 = (mb * CTAS + (int)cta_rank) * BM;  // first output row of this CTA
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kTimeoutTmemFull)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / CW; ++c) {
         const int col0 = nb * BN + c * CW;
-        if (col0 >= N) break;  // uniform across the epilogue warps
+        if (col0 >= N || row0 >= M) break;  // uniform across the epilogue warps
         uint32_t r[CW];
         tmem_ld_32x32(taddr + c * CW, r);
         if constexpr (CW == 64) tmem_ld_32x32(taddr + c * CW + 32, r + 32);
@@ -220,15 +264,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         fence_proxy_async();
         named_barrier_sync(1, 128);
         if (issuer) {
-          if (OUT_F32 && accumulate) tma_reduce_add_2d(&tmap_c, stg + buf * (BM * 128), col0, mb * BM);
-          else tma_store_2d(&tmap_c, stg + buf * (BM * 128), col0, mb * BM);
+          if (OUT_F32 && accumulate) tma_reduce_add_2d(&tmap_c, stg + buf * (BM * 128), col0, row0);
+          else tma_store_2d(&tmap_c, stg + buf * (BM * 128), col0, row0);
           tma_commit_group();
         }
         buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        if constexpr (CTAS == 2) mbar_arrive_cluster(map_to_cta(&tempty_bar[acc], 0));
+        else mbar_arrive(&tempty_bar[acc]);
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (issuer) tma_wait_group<0>();
@@ -244,9 +291,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     while (clock64() - t0 < 2000000LL) { __nanosleep(200); }
     __syncthreads();
   }
+  if constexpr (CTAS == 2) cluster_sync_all();  // no CTA leaves while its peer may still signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if constexpr (CTAS == 2) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -267,19 +316,54 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
+// Encoded tensor maps are cached: a map depends only on (address, extents, pitch, box, element type), never on the
+// contents, and a training step asks for the same few hundred combinations on every micro-batch.  Encoding costs a
+// driver call per operand, which an eager (not graph-replayed) step would otherwise pay three times per GEMM.
+namespace {
+struct TmapKey {
+  const void* ptr;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows, box_cols;
+  int dt;
+  bool operator<(const TmapKey& o) const {
+    return std::tie(ptr, rows, cols, ld, box_rows, box_cols, dt) <
+           std::tie(o.ptr, o.rows, o.cols, o.ld, o.box_rows, o.box_cols, o.dt);
+  }
+};
+std::mutex g_tmap_mu;
+std::map<TmapKey, CUtensorMap> g_tmap_cache;
+unsigned long long g_tmap_hits = 0, g_tmap_misses = 0;
+constexpr size_t kTmapCacheMax = 8192;
+}  // namespace
+
 // 2-D tensor map over a row-major [rows, cols] matrix with `ld` elements between rows, 128-byte swizzle.
 static int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int esize, const void* ptr, uint64_t rows, uint64_t cols,
                         uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * esize) & 15)) return -11;
+  const TmapKey key{ptr, rows, cols, ld, box_rows, box_cols, (int)dt};
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *out = it->second;
+      ++g_tmap_hits;
+      return 0;
+    }
+  }
   EncodeTiledFn enc = get_encode();
   if (enc == nullptr) return -10;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * esize) & 15)) return -11;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * esize};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  if (r != CUDA_SUCCESS) return -12;
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  if (g_tmap_cache.size() >= kTmapCacheMax) g_tmap_cache.clear();
+  g_tmap_cache.emplace(key, *out);
+  ++g_tmap_misses;
+  return 0;
 }
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
                       uint32_t box_cols) {
@@ -305,33 +389,100 @@ static int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+static bool g_deterministic = false;  // one k split per output tile: the fp32 reduce-adds then have a fixed order
+
+// Number of k splits for an accumulating epilogue: fill the last wave without cutting the reduction too thin.
+static int choose_k_splits(int tiles, int k_blocks, int units) {
+  if (g_deterministic) return 1;
+  int max_splits = k_blocks / 8;
+  if (max_splits > 16) max_splits = 16;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int ks = 1; ks <= max_splits; ++ks) {
+    const int per = (k_blocks + ks - 1) / ks;
+    if (per * (ks - 1) >= k_blocks) continue;  // every split must own at least one k block
+    const long long items = (long long)tiles * ks;
+    const long long waves = (items + units - 1) / units;
+    // time ~ waves x (k blocks per item + fixed cost of a tile: pipeline fill + epilogue, about 6 k blocks)
+    const double cost = (double)waves * (per + 6.0);
+    if (cost < best_cost * 0.97) { best_cost = cost; best = ks; }
+  }
+  return best;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, int CTAS>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int M, int N, int K,
                        float alpha, int accumulate, int* status, int max_ctas, cudaStream_t stream) {
-  using S = GemmSmem<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32>;
+  using S = GemmSmem<BN, STAGES, CTAS>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32, CTAS>;
   static bool attr_set = false;
+  static int max_units = 0;  // CTAs (or CTA pairs) that can be resident at once
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -20;
+    max_units = sm_count();
+    if (CTAS == 2) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0) != cudaSuccess) cudaGetLastError();
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(sm_count() / 2 * 2);
+      q.blockDim = dim3(kGemmThreads);
+      q.dynamicSmemBytes = S::kTotal;
+      cudaLaunchAttribute at;
+      at.id = cudaLaunchAttributeClusterDimension;
+      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+      q.attrs = &at; q.numAttrs = 1;
+      int n_clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&n_clusters, kern, &q) != cudaSuccess || n_clusters <= 0) {
+        cudaGetLastError();
+        n_clusters = sm_count() / 2;
+      }
+      max_units = n_clusters;
+    }
     attr_set = true;
   }
-  int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  int tiles = m_tiles * n_tiles;
-  int grid = tiles < max_ctas ? tiles : max_ctas;
-  int group_m = m_tiles < 16 ? m_tiles : 16;
+  int units = max_ctas / CTAS;
+  if (units > max_units) units = max_units;
+  if (units < 1) units = 1;
+  const int m_tiles = (M + BM * CTAS - 1) / (BM * CTAS), n_tiles = (N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  int group_m = 16 / CTAS;
+  if (group_m > m_tiles) group_m = m_tiles;
   // split-K when the output has too few tiles to fill the GPU and the epilogue accumulates anyway
   int k_splits = 1;
-  if (OUT_F32 && accumulate) {
-    const int k_blocks = (K + BK - 1) / BK;
-    k_splits = max_ctas / tiles;                 // floor: keep everything in one wave
-    if (k_splits > k_blocks / 8) k_splits = k_blocks / 8;
-    if (k_splits < 1) k_splits = 1;
-    // every split must own at least one k block
-    while (k_splits > 1 && ((k_blocks + k_splits - 1) / k_splits) * (k_splits - 1) >= k_blocks) --k_splits;
+  if (OUT_F32 && accumulate) k_splits = choose_k_splits(tiles, (K + BK - 1) / BK, units);
+  const long long items = (long long)tiles * k_splits;
+  const int grid_units = items < units ? (int)items : units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid_units * CTAS);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute at;
+  at.id = cudaLaunchAttributeClusterDimension;
+  at.val.clusterDim.x = CTAS; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+  cfg.attrs = &at;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, M, N, K, alpha, accumulate, group_m, k_splits, status) != cudaSuccess) {
+    cudaGetLastError();
+    return -21;
   }
-  grid = tiles * k_splits < max_ctas ? tiles * k_splits : max_ctas;
-  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, tc, M, N, K, alpha, accumulate, group_m, k_splits, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  return 0;
+}
+
+// Tile choice.  Candidates: CTA pair 256 x 256, CTA pair 256 x 128, one CTA 128 x 256, one CTA 128 x 128.  The estimate is
+// waves x (time one SM spends on its share of a tile); the weights are ratios measured on B200 with the variants timed
+// interleaved (FC1 / FC2 / QKV shapes of the 0.5B model, K = 1024 .. 4096), in units of a 128 x 128 block on the pair form.
+static void choose_tile(int M, int N, int max_ctas, int* bn, int* ctas) {
+  struct Cand { int bn, ctas; double w; };
+  const Cand cands[4] = {{256, 2, 2.0}, {128, 2, 1.2}, {256, 1, 2.32}, {128, 1, 1.33}};
+  double best = 1e30;
+  for (const Cand& c : cands) {
+    if (c.ctas == 2 && M <= BM) continue;  // a pair would leave one CTA without rows
+    const long long mt = (M + BM * c.ctas - 1) / (BM * c.ctas), nt = (N + c.bn - 1) / c.bn;
+    const long long units = max_ctas / c.ctas > 0 ? max_ctas / c.ctas : 1;
+    const long long waves = (mt * nt + units - 1) / units;
+    const double cost = (double)waves * c.w;
+    if (cost < best) { best = cost; *bn = c.bn; *ctas = c.ctas; }
+  }
 }
 
 }  // namespace fth
@@ -340,31 +491,44 @@ using namespace fth;
 
 extern "C" {
 
+void fth_gemm_set_deterministic(int on) { g_deterministic = on != 0; }
+
+void fth_tmap_cache_stats(unsigned long long* hits, unsigned long long* misses) {
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  *hits = g_tmap_hits;
+  *misses = g_tmap_misses;
+}
+
 // C[M,N] (op)= alpha * A x B^T in the operand-major sense described at the top of this file.
 //   a: K-major -> [M, K] with lda;  MN-major -> [K, M] with lda.   b likewise with N.
 //   epi: 0 = store bf16, 1 = fp32 accumulate (C += ...), 2 = fp32 store.
-//   bn:  128 or 256 (tile width); 0 = choose.   max_ctas: 0 = one per SM.
+//   bn:  tile code.  0 = choose; 128 / 256 = one CTA per 128 x bn tile; -128 / -256 = a CTA pair per 256 x |bn| tile.
+//   max_ctas: 0 = one per SM.
 int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, long long ldb, int b_mn_major, void* c,
                   long long ldc, int M, int N, int K, float alpha, int epi, int bn, int max_ctas, int* status,
                   cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (epi == kEpiBf16 ? (ldc % 8) : (ldc % 4)) return -2;
   if (max_ctas <= 0) max_ctas = sm_count();
-  if (bn == 0 && epi == kEpiF32Accum && N > 128) bn = 256;  // split-K fills the GPU; wide tiles reuse A best
-  if (bn == 0) {
-    // fewer, fatter tiles unless that leaves the last wave mostly empty
-    long long t256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    long long t128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
-    double w256 = (double)((t256 + max_ctas - 1) / max_ctas) * 2.0;  // cost in units of a 128-wide tile
-    double w128 = (double)((t128 + max_ctas - 1) / max_ctas) * 1.15;
-    bn = (w256 <= w128) ? 256 : 128;
+  int ctas = 1;
+  if (bn < 0) { ctas = 2; bn = -bn; }
+  else if (bn == 0) {
+    if (epi == kEpiF32Accum) {
+      // split-K fills the GPU whatever the tile count: take the widest tile the output has room for
+      bn = N > 128 ? 256 : 128;
+      ctas = M > 128 ? 2 : 1;
+    } else {
+      choose_tile(M, N, max_ctas, &bn, &ctas);
+    }
   }
+  if (bn != 128 && bn != 256) return -3;
+  const uint32_t bnh = (uint32_t)(bn / ctas);
   CUtensorMap ta, tb;
   int r;
   if (!a_mn_major) r = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
   else r = make_tmap_bf16_2d(&ta, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, 64);
   if (r) return r;
-  if (!b_mn_major) r = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, BK);
+  if (!b_mn_major) r = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, bnh, BK);
   else r = make_tmap_bf16_2d(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
   if (r) return r;
   CUtensorMap tc;
@@ -373,22 +537,24 @@ int fth_gemm_bf16(const void* a, long long lda, int a_mn_major, const void* b, l
   else r = make_tmap_bf16_2d(&tc, c, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, BM, 64);
   if (r) return r;
   const int accum = epi == kEpiF32Accum ? 1 : 0;
-#define FTH_GEMM_CASE(BN_, ST_, AM_, BM_)                                                                             \
-  do {                                                                                                                \
-    if (f32) return launch_gemm<BN_, ST_, AM_, BM_, true>(ta, tb, tc, M, N, K, alpha, accum, status, max_ctas, stream); \
-    return launch_gemm<BN_, ST_, AM_, BM_, false>(ta, tb, tc, M, N, K, alpha, accum, status, max_ctas, stream);         \
+#define FTH_GEMM_CASE(BN_, ST_, AM_, BM_, CT_)                                                                              \
+  do {                                                                                                                      \
+    if (f32) return launch_gemm<BN_, ST_, AM_, BM_, true, CT_>(ta, tb, tc, M, N, K, alpha, accum, status, max_ctas, stream); \
+    return launch_gemm<BN_, ST_, AM_, BM_, false, CT_>(ta, tb, tc, M, N, K, alpha, accum, status, max_ctas, stream);         \
   } while (0)
-  if (bn == 256) {
-    if (!a_mn_major && !b_mn_major) FTH_GEMM_CASE(256, 4, false, false);
-    if (!a_mn_major && b_mn_major) FTH_GEMM_CASE(256, 4, false, true);
-    if (a_mn_major && b_mn_major) FTH_GEMM_CASE(256, 4, true, true);
-    FTH_GEMM_CASE(256, 4, true, false);
-  } else if (bn == 128) {
-    if (!a_mn_major && !b_mn_major) FTH_GEMM_CASE(128, 6, false, false);
-    if (!a_mn_major && b_mn_major) FTH_GEMM_CASE(128, 6, false, true);
-    if (a_mn_major && b_mn_major) FTH_GEMM_CASE(128, 6, true, true);
-    FTH_GEMM_CASE(128, 6, true, false);
+#define FTH_GEMM_MAJORS(BN_, ST_, CT_)                                          \
+  do {                                                                          \
+    if (!a_mn_major && !b_mn_major) FTH_GEMM_CASE(BN_, ST_, false, false, CT_); \
+    if (!a_mn_major && b_mn_major) FTH_GEMM_CASE(BN_, ST_, false, true, CT_);   \
+    if (a_mn_major && b_mn_major) FTH_GEMM_CASE(BN_, ST_, true, true, CT_);     \
+    FTH_GEMM_CASE(BN_, ST_, true, false, CT_);                                  \
+  } while (0)
+  if (ctas == 2) {
+    if (bn == 256) FTH_GEMM_MAJORS(256, 6, 2);
+    FTH_GEMM_MAJORS(128, 8, 2);
   }
+  if (bn == 256) FTH_GEMM_MAJORS(256, 4, 1);
+  FTH_GEMM_MAJORS(128, 6, 1);
   return -3;
 }
 

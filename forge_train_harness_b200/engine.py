@@ -110,6 +110,12 @@ class Trainer:
         self.stats = torch.zeros(4, dtype=torch.float64, device=self.device)
         self.launch_count = 0
         self.last = {}
+        # Reader of the device status word the sm_100a kernels write when a bounded wait gives up (an mbarrier that never
+        # completed, a peer flag that never arrived).  None when no such kernel can run (CPU, oracle ops).
+        self._read_status = None
+        if self.device.type == "cuda" and self.ops.name.startswith("sm100"):
+            from .ops.cuda_ops import _C
+            self._read_status = lambda: int(_C.read_status(True))
 
     # ------------------------------------------------------------------
     def _seed_all(self, seed: int):
@@ -156,6 +162,20 @@ class Trainer:
         ch.run_backward(batch, cache)
         return stats
 
+    def verify_kernels(self, sync: bool = True) -> None:
+        """Raise if any kernel of the work enqueued so far gave up on a bounded wait.  A kernel that gives up returns
+        early, so whatever consumed its output (a gradient sum, a parameter push, a gathered shard) is wrong: the step
+        must not be logged, checkpointed or followed by another one.  Synchronises the host with the device."""
+        if self._read_status is None:
+            return
+        if sync and self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        code = self._read_status()
+        if code:
+            from .ops.status import STATUS_NAMES
+            raise RuntimeError(f"step {self.step}: sm_100a kernel reported status {code} "
+                               f"({STATUS_NAMES.get(code, 'unknown')}); the step's results are not valid")
+
     def _try_capture_graph(self, batch: dict):
         """Capture forward + loss + backward of ONE micro-batch (train_loop.py:1926-2125)."""
         try:
@@ -165,6 +185,7 @@ class Trainer:
                 self._fwd_bwd(batch)  # warm-up: allocator, lazy handles
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
+            self.verify_kernels(sync=False)
             self.store.zero_grad()
             g = torch.cuda.CUDAGraph()
             n0 = self._launch_count()
@@ -172,6 +193,14 @@ class Trainer:
                 self._graph_stats = self._fwd_bwd(batch)
             self.graph_launches = self._launch_count() - n0
             self._graph = g
+        except RuntimeError as e:
+            if "kernel reported status" in str(e):
+                raise
+            self._graph, self._graph_failed = None, True
+            if not self.quiet and self.rank == 0:
+                print(f"[debug] CUDA graph capture failed, running eager: {e}", file=sys.stderr, flush=True)
+            torch.cuda.synchronize()
+            self.store.zero_grad()
         except Exception as e:  # fall back to eager, as the reference does
             self._graph, self._graph_failed = None, True
             if not self.quiet and self.rank == 0:
@@ -252,8 +281,10 @@ class Trainer:
         self.links.drain()
 
     # ------------------------------------------------------------------
-    def train_step(self) -> dict:
-        """Runs one optimizer step.  Returns device tensors (no host sync): loss, grad_norm, tokens."""
+    def train_step(self, verify: bool = False) -> dict:
+        """Runs one optimizer step.  Returns device tensors (no host sync): loss, grad_norm, tokens.  With ``verify`` the
+        host waits for the step and raises if a kernel reported a wait that ran out (``verify_kernels``); callers that
+        pipeline steps without a sync (the benchmark) call ``verify_kernels`` themselves at their own sync points."""
         topo = self.topo
         self.start_data()
         step_abs = self.step + 1
@@ -291,6 +322,8 @@ class Trainer:
             self.capture.loss_scalar("post", stats)
         self.step = step_abs
         self.last = {"loss": loss, "grad_norm": norm, "tokens": stats[1], "lr": lr}
+        if verify:
+            self.verify_kernels()
         return self.last
 
     def weights_changed(self):
@@ -370,6 +403,8 @@ def run_training_loop(cfg: RunConfig, *, trainer: Trainer | None = None, loss_ta
             dt = e0.elapsed_time(e1) / 1e3
         else:
             dt = time.perf_counter() - tw
+        # before the loss line is printed and before any checkpoint is written: a kernel whose wait ran out left wrong data
+        tr.verify_kernels(sync=False)
         dt_max = _max_over_ranks(dt, tr.device)
         loss, gn = float(res["loss"]), float(res["grad_norm"])
         mfu = mfu_percent(tr.flops_per_token, tokens_per_step, dt_max, tr.world, peak)

@@ -40,6 +40,12 @@ class ParamSpec:
         return len(self.full_shape) >= 2
 
 
+def is_head_partial(spec: ParamSpec) -> bool:
+    """Replicated weights applied per attention head (the q / k norms of the Qwen3 variant): under tensor parallelism a
+    rank sees only its own heads, so its gradient is a partial sum that must be added over the TP group."""
+    return spec.kind == "replicated" and spec.name.endswith(("q_norm.weight", "k_norm.weight"))
+
+
 def full_param_specs(cfg: ModelConfig) -> list[ParamSpec]:
     """Every logical parameter in the reference's ``named_parameters`` order."""
     H, F, V = cfg.hidden_size, cfg.ffn_hidden_size, cfg.padded_vocab_size

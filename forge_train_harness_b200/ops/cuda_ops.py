@@ -32,13 +32,14 @@ _C = _load()
 ADAM_CHUNK = 8192  # elements per thread block of the segment AdamW kernel
 
 
+from .status import STATUS_NAMES  # noqa: E402
+
+
 def check_status(reset: bool = True) -> None:
     """Raise if any kernel reported a bounded wait that gave up (host sync: call after an event sync)."""
     code = _C.read_status(reset)
     if code:
-        names = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
-                 3: "accumulator never committed", 4: "accumulator never drained", 5: "peer flag never set", 6: "timeout"}
-        raise RuntimeError(f"sm_100a kernel reported status {code}: {names.get(code, 'unknown')}")
+        raise RuntimeError(f"sm_100a kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
 class Sm100Ops:

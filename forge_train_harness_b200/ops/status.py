@@ -1,0 +1,4 @@
+"""Codes of the device status word (``csrc/common.cuh::StatusCode``): which bounded wait of an sm_100a kernel gave up."""
+
+STATUS_NAMES = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
+                3: "accumulator never committed", 4: "accumulator never drained", 5: "peer flag never set", 6: "timeout"}

@@ -99,8 +99,11 @@ class DistributedOptimizer:
         sequence-parallel partial sums of replicated (norm) weights over TP, replicated KV-head
         rows over their replica group, and the tied embedding over first + last stage."""
         st, topo = self.store, self.topo
-        if self.sp:
-            bufs = [st.g(s.name) for s in st.specs if s.kind == "replicated"]
+        if topo.tp > 1:
+            # With sequence parallelism every replicated weight (the norms) saw only this rank's rows.  Without it the
+            # per-head q / k norm weights still saw only this rank's heads: their gradients are partial sums whatever
+            # the sequence layout, and left alone the replicas would drift apart.
+            bufs = [st.g(s.name) for s in st.specs if s.kind == "replicated" and (self.sp or P.is_head_partial(s))]
             if bufs:
                 flat = torch.cat([b.reshape(-1) for b in bufs])
                 dist.all_reduce(flat, group=topo.tp_group)

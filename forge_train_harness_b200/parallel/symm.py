@@ -30,7 +30,12 @@ def symm_empty(numel: int, dtype, device, group) -> SymmBuffer:
 class PeerBarrier:
     """Device-side flag barrier over a group (bounded wait; a timeout lands in the kernel status word)."""
 
-    def __init__(self, device, group, lanes: int = 4, limit_s: float = 2.0):
+    def __init__(self, device, group, lanes: int = 4, limit_s: float | None = None):
+        # A training rank can legitimately be late by tens of seconds (first-step graph capture, a lazy build, a data
+        # stall), so the training-path limit is long (host-side collective timeouts are 30 minutes); when it does run
+        # out, the status word makes the step raise (``Trainer.verify_kernels``).  Tests pass short limits.
+        if limit_s is None:
+            limit_s = float(os.environ.get("FORGE_PEER_WAIT_S", "120"))
         self.buf = symm_empty(8 * lanes, torch.int32, device, group)
         self.buf.tensor.zero_()
         torch.cuda.synchronize()

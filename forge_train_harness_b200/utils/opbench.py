@@ -35,11 +35,33 @@ def timeit(fn, iters=10, warmup=3, flush=None):
     return ts[len(ts) // 2] * 1e-3
 
 
+def timeit_many(fns: dict, iters=10, warmup=3, flush=None) -> dict:
+    """Times several implementations of one op INTERLEAVED (a, b, c, a, b, c, ...), so that all of them see the same
+    clocks: on a power-capped part whichever variant ran last in a back-to-back sweep measured the hottest GPU."""
+    for _ in range(warmup):
+        for fn in fns.values():
+            fn()
+    torch.cuda.synchronize()
+    ts = {k: [] for k in fns}
+    for _ in range(iters):
+        for k, fn in fns.items():
+            if flush is not None:
+                flush.add_(1.0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts[k].append(e0.elapsed_time(e1))
+    return {k: sorted(v)[len(v) // 2] * 1e-3 for k, v in ts.items()}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="minicpm4_0.5b")
     ap.add_argument("--mbs", type=int, default=4)
     ap.add_argument("--only", default="")
+    ap.add_argument("--tp", type=int, default=1, help="time the GEMMs at the shapes one tensor-parallel rank sees")
     ap.add_argument("--json", default="")
     a = ap.parse_args(argv)
     from ..ops.cuda_ops import Sm100Ops as ops, _C, check_status
@@ -67,20 +89,26 @@ def main(argv=None):
     def want(n):
         return not a.only or any(k in n for k in a.only.split(","))
 
-    gemms = [("qkv", cfg.qkv_dim, H), ("wo", H, cfg.q_dim), ("fc1", 2 * F, H), ("fc2", H, F), ("lm_head", V, H)]
+    tp = a.tp
+    gemms = [("qkv", cfg.qkv_dim // tp, H), ("wo", H, cfg.q_dim // tp), ("fc1", 2 * F // tp, H), ("fc2", H, F // tp),
+             ("lm_head", (V + tp - 1) // tp // 8 * 8, H)]
     for name, N, K in gemms:
         if not want("gemm") and not want(name):
             continue
         x, w, dy = r(M, K), r(N, K), r(M, N)
         mg = torch.zeros(N, K, device=dev)
         fl = 2.0 * M * N * K
-        for bn in (128, 256):
-            rec(f"gemm_fwd_{name}_bn{bn}", timeit(lambda: _C.gemm(x, False, w, False, None, 1.0, 0, bn, 0), flush=flush), fl)
-            rec(f"gemm_dgrad_{name}_bn{bn}", timeit(lambda: _C.gemm(dy, False, w, True, None, 1.0, 0, bn, 0), flush=flush), fl)
-            rec(f"gemm_wgrad_{name}_bn{bn}", timeit(lambda: _C.gemm(dy, True, x, True, mg, 1.0, 1, bn, 0), flush=flush), fl)
-        rec(f"cublas_fwd_{name}", timeit(lambda: x @ w.t(), flush=flush), fl)
-        rec(f"cublas_dgrad_{name}", timeit(lambda: dy @ w, flush=flush), fl)
-        rec(f"cublas_wgrad_{name}", timeit(lambda: dy.t() @ x, flush=flush), fl)
+        # tile codes: one-CTA tiles (128, 256), CTA-pair tiles (-128, -256), the library's own choice (0); cuBLAS beside them
+        fns = {}
+        for bn in (128, 256, -128, -256, 0):
+            fns[f"gemm_fwd_{name}_bn{bn}"] = lambda bn=bn: _C.gemm(x, False, w, False, None, 1.0, 0, bn, 0)
+            fns[f"gemm_dgrad_{name}_bn{bn}"] = lambda bn=bn: _C.gemm(dy, False, w, True, None, 1.0, 0, bn, 0)
+            fns[f"gemm_wgrad_{name}_bn{bn}"] = lambda bn=bn: _C.gemm(dy, True, x, True, mg, 1.0, 1, bn, 0)
+        fns[f"cublas_fwd_{name}"] = lambda: x @ w.t()
+        fns[f"cublas_dgrad_{name}"] = lambda: dy @ w
+        fns[f"cublas_wgrad_{name}"] = lambda: dy.t() @ x
+        for k, t in timeit_many(fns, flush=flush).items():
+            rec(k, t, fl)
         del x, w, dy, mg
     if want("mxfp8"):
         from ..ops import mxfp8 as mx

@@ -84,3 +84,20 @@ def test_reshard_tp2pp2_to_dp2_zero_and_single(tmp_path):
     l4 = float(tr.train_step()["loss"])
     tr.close()
     assert abs(l4 - full[3]) / abs(full[3]) < 2e-4
+
+
+def test_legacy_codec_round_trips_with_the_reference(tmp_path):
+    """``step_<N>/training_state.pt`` written here is read by the reference's own ``load_checkpoint`` and the other way
+    round (weights, both moments, step counters and all four RNG states); run in a child process because the reference
+    reads its model geometry from the environment when it is imported."""
+    import subprocess
+    import sys
+    ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "training_engine_tensor")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    env = dict(os.environ, NUM_LAYERS="4", HIDDEN_SIZE="64", NUM_ATTENTION_HEADS="4", NUM_QUERY_GROUPS="2", HEAD_DIM="16",
+               FFN_HIDDEN_SIZE="128", PADDED_VOCAB_SIZE="512", MAX_POSITION_EMBEDDINGS="64", NORM_EPSILON="1e-5",
+               ROTARY_BASE="10000")
+    r = subprocess.run([sys.executable, os.path.join(os.path.dirname(__file__), "_legacy_codec_worker.py"), str(tmp_path)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "LEGACY_CODEC_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]

@@ -82,3 +82,28 @@ def test_loss_decreases():
     assert len(recs) == 6
     assert recs[-1].loss < recs[0].loss
     assert all(math.isfinite(r.grad_norm) for r in recs)
+
+
+def test_kernel_status_stops_the_step_before_it_is_logged_or_saved(tmp_path):
+    """A kernel whose bounded wait ran out returns early and leaves wrong data behind.  The loop must raise after the
+    step's sync, before the loss line is printed and before a checkpoint is written (fake status reader: code 5)."""
+    import io
+
+    import pytest
+    cfg = tiny_cfg(num_steps=2, save_path=str(tmp_path / "ck"), save_interval=1)
+    cfg = cfg.replace(model={"seq_length": 32, "padded_vocab_size": 256})
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    assert tr._read_status is None          # no sm_100a kernel can run here: nothing to read
+    tr.verify_kernels()                      # and nothing raises
+    codes = iter([0, 5])
+    tr._read_status = lambda: next(codes)
+    out = io.StringIO()
+    with pytest.raises(RuntimeError, match="status 5.*peer flag never set"):
+        fth.run_training_loop(cfg, trainer=tr, out=out)
+    lines = [l for l in out.getvalue().splitlines() if l.startswith("[LOSS")]
+    assert len(lines) == 1                   # the first step was fine and logged; the second was not
+    assert not (tmp_path / "ck" / "iter_0000002").exists()
+    tr._read_status = lambda: 3
+    with pytest.raises(RuntimeError, match="accumulator never committed"):
+        tr.train_step(verify=True)
+    tr.close()

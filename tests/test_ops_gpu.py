@@ -159,7 +159,7 @@ GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 1280, 1024), (200, 264, 72
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, -128, -256, 0])  # one-CTA tiles, CTA-pair (cta_group::2) tiles, automatic choice
 def test_gemm_variants(ops, M, N, K, bn):
     from forge_train_harness_b200.ops.cuda_ops import _C, check_status
     K8 = (K + 7) // 8 * 8

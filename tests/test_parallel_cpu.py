@@ -62,6 +62,31 @@ def test_tp2(sp):
     check(single(cfg), res[0])
 
 
+def _train_qk(rank, world, cfg):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    out = []
+    for _ in range(cfg.train.num_steps):
+        r = tr.train_step()
+        out.append((float(r["loss"]), float(r["grad_norm"])))
+    w = torch.cat([tr.store.p(n).float().reshape(-1) for n in tr.store.params if n.endswith(("q_norm.weight", "k_norm.weight"))])
+    tr.close()
+    return out, w
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2_qk_norm_weights_stay_replicated(sp):
+    """The per-head q / k norm weights see only the local heads under TP: their gradients are summed over the TP group
+    with and without sequence parallelism, so every rank applies the same update and the run matches one process."""
+    import dataclasses
+    cfg = base_cfg(steps=4, tensor_parallel_size=2, sequence_parallel=sp)
+    cfg = dataclasses.replace(cfg, model=dataclasses.replace(cfg.model, qk_norm=True),
+                              optim=dataclasses.replace(cfg.optim, lr=2e-2))
+    res = run_ranks(2, _train_qk, cfg)
+    check(single(cfg), res[0][0])
+    assert torch.equal(res[0][1], res[1][1])
+    assert (res[0][1] - 1.0).abs().max() > 1e-3  # the norm weights did move
+
+
 def test_tp4_kv_replication_sp():
     cfg = base_cfg(tensor_parallel_size=4, sequence_parallel=True)
     res = run_ranks(4, _train, cfg)
