@@ -148,6 +148,7 @@ def run_ours(a):
     bracket()
     clocks = sampler.stop() if rank == 0 else None
     check_status()
+    paths = tr.paths()   # which of the fused peer-memory paths / the CUDA graph actually ran
     tr.close()
     if rank == 0:
         value = tokens_per_step * a.steps / dt
@@ -162,7 +163,7 @@ def run_ours(a):
                        "micro_batch": a.mbs, "grad_accum": a.accum,
                        "parallelism": f"dp{world}" + ("+zero1" if world > 1 else ""),
                        "l2": "no explicit flush: every step streams tens of GB of activations/weights/grads, far above the 126 MB L2",
-                       "cuda_graph": tr._graph is not None},
+                       "cuda_graph": tr._graph is not None, "paths": paths},
             "tokens_per_sec_per_gpu": value / world,
             "mfu_percent_of_measured_sustained_bf16": 100.0 * tr.flops_per_token * value / (world * peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) * 1e12),
             "peaks_source": peaks.get("source"), "final_loss": loss, "grad_norm": gnorm,

@@ -134,8 +134,14 @@ class ParallelConfig:
     overlap_grad_reduce: bool = True
     fused_comm: bool = True  # in-kernel NVLink collectives where available
     fp8: str = "off"  # "off" | "mxfp8"
+    # Layers per pipeline model chunk, in chunk order (chunk v*pp + p lives on stage p); empty = an even split.  The last
+    # chunk also runs the final norm, the LM head and the loss (about 2.6 layers' worth of work at the 0.5B shape), so an
+    # even split leaves the last stage the slowest: e.g. (7, 6, 6, 5) for 24 layers on pp = 2 x 2 virtual stages
+    # (Megatron: --decoder-first/last-pipeline-num-layers).
+    pipeline_layer_split: tuple = ()
 
     def __post_init__(self):
+        object.__setattr__(self, "pipeline_layer_split", tuple(int(x) for x in self.pipeline_layer_split))
         if self.fp8 not in ("off", "mxfp8"):
             raise ValueError("fp8 must be 'off' or 'mxfp8'")
         if self.context_parallel_size != 1:

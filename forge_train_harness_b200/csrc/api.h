@@ -58,7 +58,8 @@ int fth_adamw_push(float* master, float* m, float* v, const float* grad, void* c
 int fth_gemm_rs(const void* a, long long lda, const void* b, long long ldb, int b_mn, void* const* out_shards, long long ldo,
                 int M, int N, int K, int tp, int rank, float alpha, int* status, cudaStream_t stream);
 int fth_ag_gemm(void* const* gather, long long ldx, const void* b, long long ldb, int b_mn, void* out, long long ldo, int M, int N,
-                int K, int tp, int rank, int n_copy_ctas, int* flags, int epoch, float alpha, int* status, cudaStream_t stream);
+                int K, int tp, int rank, int n_copy_ctas, int* flags, int epoch, int* ctr, void* const* ready, float alpha,
+                int* status, cudaStream_t stream);
 
 // MXFP8 (e4m3 payload + e8m0 scale per 32 elements of the contraction dimension); see mxfp8_sm100.cu.
 size_t fth_mxfp8_sf_bytes(int rows, int K);

@@ -49,12 +49,21 @@ int read_status(bool reset) {
   return v;
 }
 
+// `y_out` (optional): where the normalised rows go, e.g. this rank's rows of an all-gather buffer, instead of a new tensor.
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& res, double res_scale,
-                                    const at::Tensor& w, double eps, double out_scale) {
+                                    const at::Tensor& w, double eps, double out_scale, const c10::optional<at::Tensor>& y_out) {
   need_bf16(x, "x");
   need_bf16(w, "w");
   const int M = x.size(0), H = x.size(1);
-  at::Tensor y = at::empty_like(x), rstd = at::empty({M}, x.options().dtype(at::kFloat));
+  at::Tensor y;
+  if (y_out.has_value()) {
+    need_bf16(*y_out, "y_out");
+    TORCH_CHECK(y_out->dim() == 2 && y_out->size(0) == M && y_out->size(1) == H, "rmsnorm_fwd: y_out shape");
+    y = *y_out;
+  } else {
+    y = at::empty_like(x);
+  }
+  at::Tensor rstd = at::empty({M}, x.options().dtype(at::kFloat));
   at::Tensor r;
   const void* resp = nullptr;
   void* rp = nullptr;
@@ -354,16 +363,27 @@ void gemm_rs(const at::Tensor& a, const at::Tensor& b, bool b_mn, const std::vec
 }
 
 // gather buffers [M, K] (symmetric; own shard already written) x b -> out [M, N]; this rank's buffer ends up fully gathered.
+// `ctr` / `ready` select the self-sequenced form (see fth_ag_gemm); pass None / [] for the host-sequenced one.
 at::Tensor ag_gemm(const std::vector<int64_t>& gather, int64_t M, int64_t K, const at::Tensor& b, bool b_mn, int64_t rank,
-                   int64_t n_copy_ctas, at::Tensor& flags, int64_t epoch, double alpha) {
+                   int64_t n_copy_ctas, at::Tensor& flags, int64_t epoch, double alpha, c10::optional<at::Tensor> ctr,
+                   const std::vector<int64_t>& ready) {
   TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kBFloat16 && b.dim() == 2 && b.stride(1) == 1, "b: 2-D bf16");
   need_i32(flags, "flags");
   const int64_t N = b_mn ? b.size(1) : b.size(0);
   std::vector<void*> p(gather.size());
   for (size_t i = 0; i < p.size(); ++i) p[i] = reinterpret_cast<void*>(gather[i]);
+  std::vector<void*> rp(ready.size());
+  for (size_t i = 0; i < rp.size(); ++i) rp[i] = reinterpret_cast<void*>(ready[i]);
+  int* ctr_ptr = nullptr;
+  if (ctr.has_value()) {
+    need_i32(*ctr, "ctr");
+    TORCH_CHECK(ctr->numel() >= 2 && rp.size() == p.size(), "ag_gemm: ctr needs 2 ints and one ready array per rank");
+    ctr_ptr = ctr->data_ptr<int>();
+  }
   at::Tensor out = at::empty({M, N}, b.options());
   check(fth_ag_gemm(p.data(), K, b.data_ptr(), b.stride(0), b_mn ? 1 : 0, out.data_ptr(), N, (int)M, (int)N, (int)K, (int)p.size(),
-                    (int)rank, (int)n_copy_ctas, flags.data_ptr<int>(), (int)epoch, (float)alpha, status_ptr(), cur_stream()),
+                    (int)rank, (int)n_copy_ctas, flags.data_ptr<int>(), (int)epoch, ctr_ptr, ctr_ptr ? rp.data() : nullptr,
+                    (float)alpha, status_ptr(), cur_stream()),
         "ag_gemm");
   return out;
 }

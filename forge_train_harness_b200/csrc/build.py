@@ -18,7 +18,7 @@ SO = os.path.join(PKG, "_C.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 CU_SOURCES = ["elementwise.cu", "gemm_sm100.cu", "attention_sm100.cu", "comm_sm100.cu", "comm_gemm_sm100.cu", "mxfp8_sm100.cu"]
-HEADERS = ["common.cuh", "sm100_ptx.cuh", "api.h", "noalloc.h"]
+HEADERS = ["common.cuh", "sm100_ptx.cuh", "gemm_pipe.cuh", "api.h", "noalloc.h"]
 
 
 def _newer(src_list, target):

@@ -31,24 +31,9 @@
 #include <mutex>
 #include <tuple>
 
-#include "sm100_ptx.cuh"
+#include "gemm_pipe.cuh"
 
 namespace fth {
-
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int kGemmThreads = 192;
-
-template <int BN, int STAGES, int CTAS = 1>
-struct GemmSmem {
-  static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = (BN / CTAS) * BK * 2;  // a CTA of a pair holds half of the B tile
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kEpiOffset = STAGES * kStageBytes;  // two 128-row x 128-byte staging buffers
-  static constexpr int kEpiBytes = 2 * BM * 128;
-  static constexpr int kBarOffset = kEpiOffset + kEpiBytes;
-  static constexpr int kTotal = kBarOffset + 256 + 1024;  // + barriers + alignment slack
-};
 
 enum EpiMode : int { kEpiBf16 = 0, kEpiF32Accum = 1, kEpiF32Store = 2 };
 
@@ -61,13 +46,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int BNH = BN / CTAS;       // B rows this CTA loads
   constexpr int TM = BM * CTAS;        // rows of the tile the CTA (pair) computes
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tfull_bar = empty_bar + STAGES;
-  uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned char* smem = align_smem_1024(smem_raw);
+  PipeBars<STAGES> bars(smem + S::kBarOffset);
+  volatile int* abort_flag = bars.abort_flag;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
@@ -79,33 +60,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int k_blocks_all = (K + BK - 1) / BK;
   const int k_per_split = (k_blocks_all + k_splits - 1) / k_splits;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4 * CTAS);  // one arrival per epilogue warp (of both CTAs of a pair)
-    }
-    *abort_flag = 0;
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  if (warp == 1) {
-    if constexpr (CTAS == 2) {
-      tmem_alloc_pair(tmem_slot, 2 * BN);
-      tmem_relinquish_pair();
-    } else {
-      tmem_alloc(tmem_slot, 2 * BN);
-      tmem_relinquish();
-    }
-  }
-  tc_fence_before();
-  if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
-  else __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = pipe_setup<BN, STAGES, CTAS, 0>(bars, true);
 
   // tile -> (m_blk, n_blk): groups of `group_m` row blocks, m fastest inside a group, so that
   // concurrently running CTAs share a few B tiles and a few A tiles out of L2.
@@ -135,40 +90,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int kb0 = (t / mn_tiles) * k_per_split;
         const int kb1 = min(kb0 + k_per_split, k_blocks_all);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) { ok = false; break; }
+          if (!mbar_wait(&bars.empty[stage], phase ^ 1, abort_flag, status, kTimeoutSmemEmpty)) { ok = false; break; }
           unsigned char* sa = smem + stage * S::kStageBytes;
-          unsigned char* sb = sa + S::kABytes;
-          if constexpr (CTAS == 2) {
-            // rank 0's barrier counts the bytes of both CTAs; a peer's bytes may land before the expectation is posted
-            const uint32_t fb = map_to_cta(&full_bar[stage], 0);
-            if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::kStageBytes);
-            if constexpr (!A_MN) {
-              tma_load_2d_pair(sa, &tmap_a, kb * BK, row_a, fb);
-            } else {
-#pragma unroll
-              for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * 8192, &tmap_a, row_a + c * 64, kb * BK, fb);
-            }
-            if constexpr (!B_MN) {
-              tma_load_2d_pair(sb, &tmap_b, kb * BK, row_b, fb);
-            } else {
-#pragma unroll
-              for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * 8192, &tmap_b, row_b + c * 64, kb * BK, fb);
-            }
-          } else {
-            mbar_expect_tx(&full_bar[stage], S::kStageBytes);
-            if constexpr (!A_MN) {
-              tma_load_2d(sa, &tmap_a, kb * BK, row_a, &full_bar[stage]);
-            } else {
-#pragma unroll
-              for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmap_a, row_a + c * 64, kb * BK, &full_bar[stage]);
-            }
-            if constexpr (!B_MN) {
-              tma_load_2d(sb, &tmap_b, kb * BK, row_b, &full_bar[stage]);
-            } else {
-#pragma unroll
-              for (int c = 0; c < BNH / 64; ++c) tma_load_2d(sb + c * 8192, &tmap_b, row_b + c * 64, kb * BK, &full_bar[stage]);
-            }
-          }
+          pipe_load_stage<BN, CTAS, A_MN, B_MN>(sa, sa + S::kABytes, &tmap_a, &tmap_b, kb * BK, row_a, row_b,
+                                                &bars.full[stage], cta_rank);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -177,39 +102,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (cta_rank == 0 && elect_one()) {
-      constexpr uint32_t idesc = make_idesc_bf16(TM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = unit; t < total_tiles && ok; t += n_units) {
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, status, kTimeoutTmemEmpty)) break;
+        if (!mbar_wait(&bars.tempty[acc], acc_phase ^ 1, abort_flag, status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int kb0 = (t / mn_tiles) * k_per_split;
         const int kb1 = min(kb0 + k_per_split, k_blocks_all);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
+          if (!mbar_wait(&bars.full[stage], phase, abort_flag, status, kTimeoutSmemFull)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
-          const uint32_t sb = sa + S::kABytes;
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024) : make_smem_desc(sa + kk * 32, 0, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024) : make_smem_desc(sb + kk * 32, 0, 1024);
-            if constexpr (CTAS == 2) umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
-            else umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
-          }
-          // frees the stage (in both CTAs of a pair) when these MMAs have read it
-          if constexpr (CTAS == 2) umma_commit_pair(&empty_bar[stage], 3);
-          else umma_commit(&empty_bar[stage]);
+          pipe_mma_stage<BN, CTAS, A_MN, B_MN>(d_tmem, sa, sa + S::kABytes, kb == kb0);
+          pipe_commit<CTAS>(&bars.empty[stage]);  // frees the stage (in both CTAs of a pair) when these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        // accumulator complete
-        if constexpr (CTAS == 2) umma_commit_pair(&tfull_bar[acc], 3);
-        else umma_commit(&tfull_bar[acc]);
+        pipe_commit<CTAS>(&bars.tfull[acc]);  // accumulator complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -230,7 +143,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int mb, nb;
       tile_coords(t, mb, nb);
       const int row0 = (mb * CTAS + (int)cta_rank) * BM;  // first output row of this CTA
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kTimeoutTmemFull)) break;
+      if (!mbar_wait(&bars.tfull[acc], acc_phase, abort_flag, status, kTimeoutTmemFull)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
@@ -243,24 +156,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_wait_ld();
         if (issuer) tma_wait_group_read<1>();  // the store that last used this buffer has read it
         named_barrier_sync(1, 128);
-        unsigned char* row_ptr = stg + buf * (BM * 128) + r_in_tile * 128;
-#pragma unroll
-        for (int p8 = 0; p8 < 8; ++p8) {
-          uint4 v;
-          if constexpr (OUT_F32) {
-            v.x = __float_as_uint(__uint_as_float(r[p8 * 4 + 0]) * alpha);
-            v.y = __float_as_uint(__uint_as_float(r[p8 * 4 + 1]) * alpha);
-            v.z = __float_as_uint(__uint_as_float(r[p8 * 4 + 2]) * alpha);
-            v.w = __float_as_uint(__uint_as_float(r[p8 * 4 + 3]) * alpha);
-          } else {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p8 * 8 + e]) * alpha;
-            bf16x8 pk = pack8(f);
-            v = *reinterpret_cast<uint4*>(&pk);
-          }
-          *reinterpret_cast<uint4*>(row_ptr + ((p8 ^ (r_in_tile & 7)) * 16)) = v;
-        }
+        pipe_stage_row<OUT_F32>(stg + buf * (BM * 128) + r_in_tile * 128, r_in_tile, r, alpha);
         fence_proxy_async();
         named_barrier_sync(1, 128);
         if (issuer) {
@@ -272,31 +168,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if constexpr (CTAS == 2) mbar_arrive_cluster(map_to_cta(&tempty_bar[acc], 0));
-        else mbar_arrive(&tempty_bar[acc]);
-      }
+      if (lane == 0) pipe_release_acc<CTAS>(&bars.tempty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (issuer) tma_wait_group<0>();
   }
 
-  // ---------------- teardown ----------------
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    // A wait gave up.  Let TMA copies that were already issued land before the CTA's shared memory
-    // is handed to another CTA (bounded delay, no barrier that could itself hang).
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) { __nanosleep(200); }
-    __syncthreads();
-  }
-  if constexpr (CTAS == 2) cluster_sync_all();  // no CTA leaves while its peer may still signal its barriers
-  if (warp == 1) {
-    tc_fence_after();
-    if constexpr (CTAS == 2) tmem_dealloc_pair(tmem_base, 2 * BN);
-    else tmem_dealloc(tmem_base, 2 * BN);
-  }
+  pipe_teardown<BN, CTAS>(abort_flag, tmem_base, true);
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
@@ -419,24 +297,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   static int max_units = 0;  // CTAs (or CTA pairs) that can be resident at once
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return -20;
-    max_units = sm_count();
-    if (CTAS == 2) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0) != cudaSuccess) cudaGetLastError();
-      cudaLaunchConfig_t q = {};
-      q.gridDim = dim3(sm_count() / 2 * 2);
-      q.blockDim = dim3(kGemmThreads);
-      q.dynamicSmemBytes = S::kTotal;
-      cudaLaunchAttribute at;
-      at.id = cudaLaunchAttributeClusterDimension;
-      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-      q.attrs = &at; q.numAttrs = 1;
-      int n_clusters = 0;
-      if (cudaOccupancyMaxActiveClusters(&n_clusters, kern, &q) != cudaSuccess || n_clusters <= 0) {
-        cudaGetLastError();
-        n_clusters = sm_count() / 2;
-      }
-      max_units = n_clusters;
-    }
+    max_units = pipe_max_units<CTAS>(kern, S::kTotal, sm_count());
     attr_set = true;
   }
   int units = max_ctas / CTAS;
@@ -451,17 +312,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   if (OUT_F32 && accumulate) k_splits = choose_k_splits(tiles, (K + BK - 1) / BK, units);
   const long long items = (long long)tiles * k_splits;
   const int grid_units = items < units ? (int)items : units;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid_units * CTAS);
-  cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = S::kTotal;
-  cfg.stream = stream;
-  cudaLaunchAttribute at;
-  at.id = cudaLaunchAttributeClusterDimension;
-  at.val.clusterDim.x = CTAS; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-  cfg.attrs = &at;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, M, N, K, alpha, accumulate, group_m, k_splits, status) != cudaSuccess) {
+  if (pipe_launch<CTAS>(kern, grid_units, S::kTotal, stream, ta, tb, tc, M, N, K, alpha, accumulate, group_m, k_splits, status) !=
+      cudaSuccess) {
     cudaGetLastError();
     return -21;
   }

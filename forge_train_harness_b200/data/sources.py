@@ -226,7 +226,9 @@ class Prefetcher:
 class BatchStager:
     """Packs a micro-batch into one pinned buffer and moves it with one async copy."""
 
-    def __init__(self, micro_batch: int, seq_len: int, device, with_mtp: bool):
+    def __init__(self, micro_batch: int, seq_len: int, device, with_mtp: bool, dev_slots: int = 1):
+        """``dev_slots`` device-side copies are kept (a pipeline schedule holds every micro-batch of a step until its
+        backward pass has run); ``stage(b, slot)`` picks which one the copy lands in."""
         self.B, self.S, self.device = micro_batch, seq_len, torch.device(device)
         n = micro_batch * seq_len
         self.fields = ["ids", "labels", "mask"] + (["mtp_ids", "mtp_labels", "mtp_mask"] if with_mtp else [])
@@ -235,12 +237,19 @@ class BatchStager:
         self.hosts = [torch.empty(self.nbytes, dtype=torch.uint8, pin_memory=pin) for _ in range(2 if pin else 1)]
         self.events = [None] * len(self.hosts)
         self.turn = 0
-        self.dev = torch.empty(self.nbytes, dtype=torch.uint8, device=self.device) if pin else self.hosts[0]
-        self.dviews = {}
         self._n = n
-        for i, f in enumerate(self.fields):
-            dt = torch.float32 if f.endswith("mask") else torch.int32
-            self.dviews[f] = self.dev[4 * n * i: 4 * n * (i + 1)].view(dt)
+        self._pin = pin
+        self.devs, self.dviews_all = [], []
+        for _ in range(max(1, dev_slots)):
+            dev = torch.empty(self.nbytes, dtype=torch.uint8, device=self.device) if pin else \
+                torch.empty(self.nbytes, dtype=torch.uint8)
+            views = {}
+            for i, f in enumerate(self.fields):
+                dt = torch.float32 if f.endswith("mask") else torch.int32
+                views[f] = dev[4 * n * i: 4 * n * (i + 1)].view(dt)
+            self.devs.append(dev)
+            self.dviews_all.append(views)
+        self.dev, self.dviews = self.devs[0], self.dviews_all[0]
 
     def _hviews(self, host):
         n, out = self._n, {}
@@ -249,10 +258,10 @@ class BatchStager:
             out[f] = host[4 * n * i: 4 * n * (i + 1)].view(dt)
         return out
 
-    def stage(self, b: dict) -> dict:
+    def stage(self, b: dict, slot: int = 0) -> dict:
         """``b`` holds CPU ``tokens``/``labels``/``loss_mask`` ``[B, S]``.  Fills one of two pinned
         buffers (waiting only for that buffer's previous copy) and enqueues one async H2D copy on
-        the current stream.  Returns device views."""
+        the current stream into device copy ``slot``.  Returns device views."""
         k = self.turn
         self.turn = (self.turn + 1) % len(self.hosts)
         if self.events[k] is not None:
@@ -266,11 +275,14 @@ class BatchStager:
             hv["mtp_ids"].copy_(mi.reshape(-1))
             hv["mtp_labels"].copy_(ml.reshape(-1))
             hv["mtp_mask"].copy_(mm.reshape(-1))
-        if self.dev is not self.hosts[k]:
-            self.dev.copy_(self.hosts[k], non_blocking=True)
+        dev = self.devs[slot]
+        if self._pin:
+            dev.copy_(self.hosts[k], non_blocking=True)
             if self.events[k] is None:
                 self.events[k] = torch.cuda.Event()
             self.events[k].record()
-        out = dict(self.dviews)
+        else:
+            dev.copy_(self.hosts[k])
+        out = dict(self.dviews_all[slot])
         out["seq_len"] = self.S
         return out

@@ -70,12 +70,13 @@ class Trainer:
             from .ops.mxfp8 import Mxfp8Ops
             self.ops = Mxfp8Ops(self.ops)
         self.tpc = TPComm(topo.tp_group, topo.tp, topo.tp_rank, par.sequence_parallel)
+        want_tp = os.environ.get("FORGE_FUSED_TP", "1")  # "0" = NCCL collectives, "require" = fail instead of falling back
         if self.tpc.sp and self.device.type == "cuda" and par.fused_comm and self.dtype == torch.bfloat16 and par.fp8 == "off" \
-                and os.environ.get("FORGE_FUSED_TP", "1") == "1":
+                and want_tp != "0":
             from .parallel import fused_tp
             self.tpc.fused = fused_tp.try_create(topo.tp_group, topo.tp, topo.tp_rank, t.micro_batch_size * m.seq_length,
-                                                 m.hidden_size, self.device)
-        chunks = pipeline_chunks(m, topo.pp, par.virtual_pipeline_stages, topo.pp_rank)
+                                                 m.hidden_size, self.device, required=want_tp == "require")
+        chunks = pipeline_chunks(m, topo.pp, par.virtual_pipeline_stages, topo.pp_rank, par.pipeline_layer_split)
         self.store = ParamStore(m, chunks, tp=topo.tp, tp_rank=topo.tp_rank, dp=topo.dp, dtype=self.dtype,
                                 device=self.device, bucket_elems=par.ddp_bucket_elems, pp=topo.pp)
         self._init_weights(init_mode)
@@ -87,10 +88,10 @@ class Trainer:
         for c in self.chunks:
             c.recompute = t.recompute
         fused = None
-        if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 \
-                and os.environ.get("FORGE_FUSED_DP", "1") == "1":
+        want_dp = os.environ.get("FORGE_FUSED_DP", "1")
+        if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 and want_dp != "0":
             from .parallel import fused_dp
-            fused = fused_dp.try_create(self.store, topo)
+            fused = fused_dp.try_create(self.store, topo, required=want_dp == "require")
         self.opt = DistributedOptimizer(self.store, topo, cfg.optim, self.ops, sharded=par.use_distributed_optimizer,
                                         sequence_parallel=par.sequence_parallel, fused_backend=fused)
         self.links = PipeLinks(topo)
@@ -98,7 +99,8 @@ class Trainer:
         self.source = build_source(cfg.data, m, t.micro_batch_size, topo.dp_rank, topo.dp, t.seed)
         self.prefetch = None
         self.with_mtp = bool(m.mtp_num_layers) and topo.pp == 1
-        self.stager = BatchStager(t.micro_batch_size, m.seq_length, self.device, self.with_mtp)
+        self.stager = BatchStager(t.micro_batch_size, m.seq_length, self.device, self.with_mtp,
+                                  dev_slots=self.grad_accum if topo.pp > 1 else 1)
         self.step = t.start_step  # completed steps (absolute)
         self.peaks = load_peaks()
         self.flops_per_token = m.flops_per_token(self.with_mtp)
@@ -249,13 +251,8 @@ class Trainer:
     def _run_microbatches_pp(self):
         topo, t, m = self.topo, self.cfg.train, self.cfg.model
         n_mb = self.grad_accum
-        batches = []
-        for _ in range(n_mb):
-            b = self.prefetch.get()
-            d = {"ids": b["tokens"].reshape(-1).to(torch.int32).to(self.device, non_blocking=True),
-                 "labels": b["labels"].reshape(-1).to(torch.int32).to(self.device, non_blocking=True),
-                 "mask": b["loss_mask"].reshape(-1).to(self.device, non_blocking=True), "seq_len": m.seq_length}
-            batches.append(d)
+        # one pinned-buffer H2D copy per micro-batch, each into its own device copy (all are alive until their backward)
+        batches = [self.stager.stage(self.prefetch.get(), slot=i) for i in range(n_mb)]
         vpp = self.cfg.parallel.virtual_pipeline_stages
         sched = build_schedule(topo.pp, topo.pp_rank, vpp, n_mb)
         rows = t.micro_batch_size * m.seq_length
@@ -325,6 +322,12 @@ class Trainer:
         if verify:
             self.verify_kernels()
         return self.last
+
+    def paths(self) -> dict:
+        """Which implementation of each communication / launch path this trainer runs (reported by the benchmark and the
+        training log, so that a fallback to the library collectives is never silent)."""
+        return {"ops": self.ops.name, "fused_dp": self.opt.fused is not None, "fused_tp": self.tpc.fused is not None,
+                "cuda_graph": self._graph is not None, "tp": self.topo.tp, "pp": self.topo.pp, "dp": self.topo.dp}
 
     def weights_changed(self):
         """Tell op tables that keep derived copies of the weights (the MXFP8 quantised ones) that the bf16 parameters moved."""

@@ -54,6 +54,7 @@ class ChunkCache:
     nff: torch.Tensor = None
     dlogits: torch.Tensor = None
     mtp: dict = None
+    slot: int = 0  # which in-flight micro-batch of this chunk the cache belongs to (names the gather buffers it holds)
 
 
 class ModelChunk:
@@ -67,6 +68,8 @@ class ModelChunk:
         self.capture = capture  # optional hook: capture(kind, fqn, tensor)
         self.recompute = False
         self.on_grads_final = None  # callable(prefix): every parameter under `prefix` has its final gradient of the step
+        self._free_slots: list = []   # in-flight micro-batch slots released by finished backward passes
+        self._n_slots = 0
 
     # ------------------------------------------------------------------
     def _cap(self, kind, fqn, t):
@@ -89,18 +92,23 @@ class ModelChunk:
                                self.geo.vocab_start)
 
     # ------------------------------------------------------------------
-    def _layer_fwd(self, prefix, x, pending, ds, seq_len):
-        """``pending`` is the previous FC2 output still to be added (None at a chunk start)."""
+    def _layer_fwd(self, prefix, x, pending, ds, seq_len, slot=0):
+        """``pending`` is the previous FC2 output still to be added (None at a chunk start).  ``slot`` numbers the
+        in-flight micro-batch: with the one-kernel TP paths the gathered inputs of QKV / FC1 stay in per-(layer, slot)
+        buffers until the backward pass has used them, and the norms write their rows straight into those buffers."""
         ops, st, tp, geo, cfg = self.ops, self.store, self.tp, self.geo, self.cfg
         c = LayerCache()
         w_an = st.p(prefix + "attention_norm.weight")
+        k1, k2 = (id(self), prefix, 1, slot), (id(self), prefix, 2, slot)
+        out1 = tp.col_slot(k1, x.shape[0], x.shape[1], x.dtype)
+        kw1 = {} if out1 is None else {"y_out": out1}
         if pending is None:
-            n1, c.rstd1 = ops.rmsnorm_fwd(x, w_an, cfg.norm_epsilon)
+            n1, c.rstd1 = ops.rmsnorm_fwd(x, w_an, cfg.norm_epsilon, **kw1)
         else:
-            x, n1, c.rstd1 = ops.residual_rmsnorm_fwd(x, pending, ds, w_an, cfg.norm_epsilon)
+            x, n1, c.rstd1 = ops.residual_rmsnorm_fwd(x, pending, ds, w_an, cfg.norm_epsilon, **kw1)
         c.x = x
         self._cap("fwd", prefix + "attention_norm", n1)
-        qkv, c.n1f = tp.col_linear_fwd(ops, n1, st.p(prefix + "wqkv.weight"))
+        qkv, c.n1f = tp.col_linear_fwd(ops, n1, st.p(prefix + "wqkv.weight"), key=k1)
         self._cap("fwd", prefix + "wqkv", qkv)
         if cfg.qk_norm:
             c.qkv_pre = qkv
@@ -111,9 +119,11 @@ class ModelChunk:
         c.att, c.lse = ops.attention_fwd(qkv, seq_len, geo.n_kv_local, geo.g_local, geo.head_dim)
         a = tp.row_linear_fwd(ops, c.att, st.p(prefix + "wo.weight"))
         self._cap("fwd", prefix + "wo", a)
-        c.h, n2, c.rstd2 = ops.residual_rmsnorm_fwd(x, a, ds, st.p(prefix + "ffn_norm.weight"), cfg.norm_epsilon)
+        out2 = tp.col_slot(k2, x.shape[0], x.shape[1], x.dtype)
+        kw2 = {} if out2 is None else {"y_out": out2}
+        c.h, n2, c.rstd2 = ops.residual_rmsnorm_fwd(x, a, ds, st.p(prefix + "ffn_norm.weight"), cfg.norm_epsilon, **kw2)
         self._cap("fwd", prefix + "ffn_norm", n2)
-        c.gu, c.n2f = tp.col_linear_fwd(ops, n2, st.p(prefix + "wfc1.weight"))
+        c.gu, c.n2f = tp.col_linear_fwd(ops, n2, st.p(prefix + "wfc1.weight"), key=k2)
         self._cap("fwd", prefix + "wfc1", c.gu)
         c.inter = ops.swiglu_fwd(c.gu)
         c.m = tp.row_linear_fwd(ops, c.inter, st.p(prefix + "w2.weight"))
@@ -184,6 +194,11 @@ class ModelChunk:
         cfg, ops, tp = self.cfg, self.ops, self.tp
         S = batch["seq_len"]
         cache = ChunkCache()
+        if self._free_slots:
+            cache.slot = self._free_slots.pop()
+        else:
+            cache.slot = self._n_slots
+            self._n_slots += 1
         if self.spec.has_embedding:
             cache.ids = batch["ids"]
             x = self._embed(batch["ids"])
@@ -192,7 +207,7 @@ class ModelChunk:
             x = x_in
         pending = None
         for li in self.spec.layers:
-            c = self._layer_fwd(f"layers.{li}.", x, pending, self.ds, S)
+            c = self._layer_fwd(f"layers.{li}.", x, pending, self.ds, S, cache.slot)
             cache.layers.append(c)
             x, pending = c.h, c.m
         if not self.spec.has_head:
@@ -227,6 +242,7 @@ class ModelChunk:
             g = self._layer_bwd(f"layers.{li}.", c, g, self.ds, S)
             if done is not None:
                 done(f"layers.{li}.")
+        self._free_slots.append(cache.slot)  # the gather buffers of this micro-batch may be reused
         if self.spec.has_embedding:
             self._cap("bwd", "tok_embeddings", g)
             self._embed_bwd(g, cache.ids)

@@ -29,16 +29,23 @@ class ChunkSpec:
     has_head: bool
 
 
-def pipeline_chunks(cfg: ModelConfig, pp: int, vpp: int, pp_rank: int) -> list[ChunkSpec]:
-    """Layer assignment for interleaved pipelining: model chunk ``v*pp + p`` lives on stage ``p``."""
+def pipeline_chunks(cfg: ModelConfig, pp: int, vpp: int, pp_rank: int, layer_split=()) -> list[ChunkSpec]:
+    """Layer assignment for interleaved pipelining: model chunk ``v*pp + p`` lives on stage ``p``.  ``layer_split`` gives
+    the number of layers of every chunk in chunk order (empty: an even split)."""
     n_chunks = pp * vpp
-    if cfg.num_layers % n_chunks:
-        raise ValueError("num_layers must be divisible by pipeline stages * virtual stages")
-    per = cfg.num_layers // n_chunks
+    if layer_split:
+        counts = [int(x) for x in layer_split]
+        if len(counts) != n_chunks or sum(counts) != cfg.num_layers or min(counts) < 1:
+            raise ValueError(f"pipeline_layer_split needs {n_chunks} positive entries that sum to {cfg.num_layers}")
+    else:
+        if cfg.num_layers % n_chunks:
+            raise ValueError("num_layers must be divisible by pipeline stages * virtual stages")
+        counts = [cfg.num_layers // n_chunks] * n_chunks
+    starts = [sum(counts[:c]) for c in range(n_chunks)]
     out = []
     for v in range(vpp):
         c = v * pp + pp_rank
-        out.append(ChunkSpec(tuple(range(c * per, (c + 1) * per)), c == 0, c == n_chunks - 1))
+        out.append(ChunkSpec(tuple(range(starts[c], starts[c] + counts[c])), c == 0, c == n_chunks - 1))
     return out
 
 

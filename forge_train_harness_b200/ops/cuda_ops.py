@@ -56,13 +56,13 @@ class Sm100Ops:
 
     # ---- RMSNorm ---------------------------------------------------------
     @staticmethod
-    def rmsnorm_fwd(x, w, eps, out_scale=1.0):
-        y, rstd = _C.rmsnorm_fwd(x, None, 0.0, w, float(eps), float(out_scale))
+    def rmsnorm_fwd(x, w, eps, out_scale=1.0, y_out=None):
+        y, rstd = _C.rmsnorm_fwd(x, None, 0.0, w, float(eps), float(out_scale), y_out)
         return y, rstd
 
     @staticmethod
-    def residual_rmsnorm_fwd(h, a, scale, w, eps, out_scale=1.0):
-        r, y, rstd = _C.rmsnorm_fwd(h, a, float(scale), w, float(eps), float(out_scale))
+    def residual_rmsnorm_fwd(h, a, scale, w, eps, out_scale=1.0, y_out=None):
+        r, y, rstd = _C.rmsnorm_fwd(h, a, float(scale), w, float(eps), float(out_scale), y_out)
         return r, y, rstd
 
     @staticmethod

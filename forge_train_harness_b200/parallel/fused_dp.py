@@ -13,8 +13,7 @@ memory) with two kernels over symmetric memory:
 Ordering between ranks is three flag barriers per step (gradients complete -> pull; pulls done -> buffers reusable;
 pushes done -> parameters readable), each a bounded device-side wait.  With gradient accumulation the collectives run once
 per step after the last micro-batch; they are not interleaved with the backward (at 16 micro-batches per step the whole
-exchange is < 0.5 % of the step).  Roofline: bytes over NVLink per rank = (dp-1)/dp * 4P (pull) + (dp-1)/dp * 2P/… (push);
-see ``profiles/``.
+exchange is < 0.5 % of the step).  Roofline: bytes over NVLink per rank = (dp-1)/dp * 4P (pull) + (dp-1)/dp * 2P (push).
 """
 from __future__ import annotations
 
@@ -67,13 +66,18 @@ class FusedDP:
         self.barrier(2)  # every push has landed: parameters are readable everywhere
 
 
-def try_create(store, topo):
-    """Returns a ``FusedDP`` or None (then the NCCL path runs).  Needs bf16 parameters, dp <= 8, and symmetric memory."""
+def try_create(store, topo, required: bool = False):
+    """Returns a ``FusedDP`` or None (then the NCCL path runs).  Needs bf16 parameters, dp <= 8, and symmetric memory.
+    The reason for a fallback is printed by rank 0; with ``required`` (``FORGE_FUSED_DP=require``) it raises instead."""
     if store.dtype != torch.bfloat16 or topo.dp > 8:
+        if required:
+            raise RuntimeError("fused DP path needs bf16 parameters and dp <= 8")
         return None
     try:
         return FusedDP(store, topo)
     except Exception as e:  # noqa: BLE001
+        if required:
+            raise
         if topo.rank == 0:
-            print(f"[debug] fused DP path unavailable ({type(e).__name__}: {e}); using NCCL collectives", file=sys.stderr, flush=True)
+            print(f"[warn] fused DP path unavailable ({type(e).__name__}: {e}); using NCCL collectives", file=sys.stderr, flush=True)
         return None

@@ -29,10 +29,19 @@ class TPComm:
         f = self.fused
         return f is not None and self.sp and x.dtype == torch.bfloat16 and x.is_cuda
 
-    def col_linear_fwd(self, ops, x, w, alpha=1.0):
-        """Column-parallel forward: ``(y, x_full)`` with ``y = gather(x) @ w^T``."""
+    def col_slot(self, key, rows: int, cols: int, dtype):
+        """Where the producer of a column-parallel linear's input may write its ``[rows, cols]`` output directly (this
+        rank's rows of the call site's all-gather buffer), or None when the one-kernel path is not in use."""
+        f = self.fused
+        if f is None or not self.sp or key is None or dtype != torch.bfloat16 or not f.supports(rows * self.size, cols):
+            return None
+        return f.slot(key)
+
+    def col_linear_fwd(self, ops, x, w, alpha=1.0, key=None):
+        """Column-parallel forward: ``(y, x_full)`` with ``y = gather(x) @ w^T``.  ``key`` names the call site (layer,
+        linear, in-flight micro-batch slot) whose gathered input the backward pass keeps."""
         if self._fusable(x, w) and self.fused.supports(x.shape[0] * self.size, x.shape[1]):
-            return self.fused.ag_gemm(x, w, False, alpha)
+            return self.fused.ag_gemm(x, w, False, alpha, key=key)
         xf = self.col_input_fwd(x)
         return ops.linear_fwd(xf, w, alpha), xf
 

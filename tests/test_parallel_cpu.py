@@ -99,6 +99,13 @@ def test_pp2_1f1b():
     check(single(cfg), res[0])
 
 
+def test_pp2_uneven_layer_split():
+    """Three layers on the first stage, one (plus the head and the loss) on the last: same numbers as one process."""
+    cfg = base_cfg(pipeline_parallel_size=2, pipeline_layer_split=(3, 1), gbs=8)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg.replace(parallel={"pipeline_layer_split": ()})), res[0])
+
+
 def test_pp2_interleaved():
     cfg = base_cfg(pipeline_parallel_size=2, virtual_pipeline_stages=2, gbs=8)
     res = run_ranks(2, _train, cfg)
