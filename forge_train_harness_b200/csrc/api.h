@@ -47,7 +47,7 @@ int fth_flash_bwd(const void* d_out, const void* qkv, const void* out, const flo
                   const float* rope_table, int B, int S, int n_kv, int g, int d, int* status, cudaStream_t stream);
 
 int fth_peer_barrier(void* const* pads, int rank, int world, unsigned epoch, int lane_slot, int* status, double limit_s,
-                     cudaStream_t stream);
+                     unsigned* epoch_dev, cudaStream_t stream);
 int fth_dp_reduce_scatter_blocks(void);
 int fth_dp_reduce_scatter(void* const* grads, const void* mc_grads, long long start, long long count, int world, int rank,
                           double* partial, float* sumsq_accum, cudaStream_t stream);

@@ -317,11 +317,19 @@ at::Tensor flash_bwd(const at::Tensor& dout, const at::Tensor& qkv, const at::Te
 }
 
 // ---- peer-memory collectives (pointers come from torch symmetric memory: handle.buffer_ptrs / multicast_ptr) ----------
-void peer_barrier(const std::vector<int64_t>& pads, int64_t rank, int64_t epoch, int64_t lane_slot, double limit_s) {
+// `epoch_dev` (int32[lanes], optional): number the barrier from a device counter instead of `epoch` (graph-replayable).
+void peer_barrier(const std::vector<int64_t>& pads, int64_t rank, int64_t epoch, int64_t lane_slot, double limit_s,
+                  c10::optional<at::Tensor> epoch_dev) {
   std::vector<void*> p(pads.size());
   for (size_t i = 0; i < pads.size(); ++i) p[i] = reinterpret_cast<void*>(pads[i]);
-  check(fth_peer_barrier(p.data(), (int)rank, (int)pads.size(), (unsigned)epoch, (int)lane_slot, status_ptr(), limit_s, cur_stream()),
-        "peer_barrier");
+  unsigned* ed = nullptr;
+  if (epoch_dev.has_value()) {
+    need_i32(*epoch_dev, "epoch_dev");
+    TORCH_CHECK(epoch_dev->numel() > lane_slot, "peer_barrier: epoch_dev needs one counter per lane");
+    ed = reinterpret_cast<unsigned*>(epoch_dev->data_ptr<int>()) + lane_slot;
+  }
+  check(fth_peer_barrier(p.data(), (int)rank, (int)pads.size(), (unsigned)epoch, (int)lane_slot, status_ptr(), limit_s, ed,
+                         cur_stream()), "peer_barrier");
 }
 
 void dp_reduce_scatter(const std::vector<int64_t>& grads, int64_t mc_grads, int64_t start, int64_t count, int64_t rank,

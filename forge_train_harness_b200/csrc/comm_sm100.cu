@@ -33,10 +33,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// pads.p[r] points at rank r's pad: `world` uint32 slots per barrier lane.  One thread per peer.
+// pads.p[r] points at rank r's pad: `world` uint32 slots per barrier lane.  One thread per peer (one warp).
+// `epoch_dev` (optional): the barrier numbers itself from a device counter (epoch = *epoch_dev + 1, written back when the
+// barrier has completed), so the same launch can be replayed from a CUDA graph; every rank makes the same sequence of calls.
 __global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, int lane_slot, int* status,
-                                    long long limit_cycles) {
+                                    long long limit_cycles, uint32_t* epoch_dev) {
   const int t = threadIdx.x;
+  if (epoch_dev != nullptr) {
+    epoch = *reinterpret_cast<volatile uint32_t*>(epoch_dev) + 1;
+    __syncwarp();                      // every lane has read the counter before lane 0 may advance it
+    if (t == 0) *epoch_dev = epoch;    // advanced even if the wait below runs out: the ranks stay in step
+  }
   if (t >= world) return;
   __threadfence_system();
   uint32_t* remote = reinterpret_cast<uint32_t*>(pads.p[t]) + lane_slot * kMaxPeers + rank;
@@ -198,12 +205,12 @@ using namespace fth;
 extern "C" {
 
 int fth_peer_barrier(void* const* pads, int rank, int world, unsigned epoch, int lane_slot, int* status, double limit_s,
-                     cudaStream_t stream) {
+                     unsigned* epoch_dev, cudaStream_t stream) {
   if (world > kMaxPeers) return -2;
   PeerPtrs pp;
   for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = i < world ? pads[i] : nullptr;
   long long limit = (long long)(limit_s * 1.9e9);
-  peer_barrier_kernel<<<1, 32, 0, stream>>>(pp, rank, world, epoch, lane_slot, status, limit);
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(pp, rank, world, epoch, lane_slot, status, limit, epoch_dev);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

@@ -109,6 +109,7 @@ class Trainer:
         self._graph_failed = False
         self.graph_launches = 0  # sm_100a kernels recorded in the captured micro-batch graph
         self.graph_replays = 0
+        self._layer_graphs = False  # TP / PP runs: the chunks' layer loops are replayed from CUDA graphs (after one eager step)
         self.stats = torch.zeros(4, dtype=torch.float64, device=self.device)
         self.launch_count = 0
         self.last = {}
@@ -216,6 +217,27 @@ class Trainer:
         from .ops.cuda_ops import _C
         return int(_C.launch_count())
 
+    def _maybe_enable_layer_graphs(self) -> None:
+        """Tensor / pipeline-parallel runs cannot capture a whole micro-batch (pipeline send / recv and the library
+        collectives of the embedding and the head sit between the chunks), but the layer loops between them can be: after
+        the first step has run eagerly (lazy allocations, symmetric-memory rendezvous of every call site), each chunk
+        captures its forward and backward layer loop once per in-flight slot and replays them from then on.  The decision
+        depends only on the configuration, so every rank of the job takes it at the same step."""
+        t, topo = self.cfg.train, self.topo
+        if self._layer_graphs or not t.cuda_graph or self.device.type != "cuda" or self.capture is not None:
+            return
+        if topo.tp == 1 and topo.pp == 1:
+            return                       # the whole micro-batch is captured instead (_try_capture_graph)
+        if self.ops.name != "sm100" or os.environ.get("FORGE_LAYER_GRAPHS", "1") == "0":
+            return
+        if topo.tp > 1 and self.tpc.fused is None:
+            return                       # library collectives inside the layer loop: left eager
+        if self.with_mtp or self.cfg.model.qk_norm:
+            return
+        for c in self.chunks:
+            c.enable_graphs()
+        self._layer_graphs = True
+
     def _use_graph(self) -> bool:
         t = self.cfg.train
         return (t.cuda_graph and self.device.type == "cuda" and self.topo.pp == 1 and self.topo.tp == 1
@@ -318,6 +340,7 @@ class Trainer:
             self.capture.grads("post", self.store, scale=inv_tokens)
             self.capture.loss_scalar("post", stats)
         self.step = step_abs
+        self._maybe_enable_layer_graphs()
         self.last = {"loss": loss, "grad_norm": norm, "tokens": stats[1], "lr": lr}
         if verify:
             self.verify_kernels()
@@ -327,7 +350,7 @@ class Trainer:
         """Which implementation of each communication / launch path this trainer runs (reported by the benchmark and the
         training log, so that a fallback to the library collectives is never silent)."""
         return {"ops": self.ops.name, "fused_dp": self.opt.fused is not None, "fused_tp": self.tpc.fused is not None,
-                "cuda_graph": self._graph is not None, "tp": self.topo.tp, "pp": self.topo.pp, "dp": self.topo.dp}
+                "cuda_graph": self._graph is not None or self._layer_graphs, "tp": self.topo.tp, "pp": self.topo.pp, "dp": self.topo.dp}
 
     def weights_changed(self):
         """Tell op tables that keep derived copies of the weights (the MXFP8 quantised ones) that the bf16 parameters moved."""
@@ -394,12 +417,15 @@ def run_training_loop(cfg: RunConfig, *, trainer: Trainer | None = None, loss_ta
     records = []
     sink = open(t.metrics_jsonl, "a") if (t.metrics_jsonl and rank0) else None
     end_step = tr.step + t.num_steps
+    from .utils.step_profile import StepProfiler
+    prof = StepProfiler(tr.rank)   # FORGE_PROFILE_STEP=<n>: that step of one rank runs under the profiler
     while tr.step < end_step:
         if cuda:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         tw = time.perf_counter()
-        res = tr.train_step()
+        with prof.maybe(tr.step + 1):
+            res = tr.train_step()
         if cuda:
             e1.record()
             e1.synchronize()

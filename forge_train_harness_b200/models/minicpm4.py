@@ -70,6 +70,10 @@ class ModelChunk:
         self.on_grads_final = None  # callable(prefix): every parameter under `prefix` has its final gradient of the step
         self._free_slots: list = []   # in-flight micro-batch slots released by finished backward passes
         self._n_slots = 0
+        # CUDA-graph replay of the layer loops (forward and backward, one pair per in-flight slot); see enable_graphs()
+        self.graph_pool = None
+        self._graphs: dict = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------
     def _cap(self, kind, fqn, t):
@@ -205,14 +209,12 @@ class ModelChunk:
             self._cap("fwd", "tok_embeddings", x)
         else:
             x = x_in
-        pending = None
-        for li in self.spec.layers:
-            c = self._layer_fwd(f"layers.{li}.", x, pending, self.ds, S, cache.slot)
-            cache.layers.append(c)
-            x, pending = c.h, c.m
+        if self.graph_pool is not None:
+            x, pending = self._graphed_layers_fwd(x, cache, S)
+        else:
+            x, pending = self._layers_fwd(x, cache, S)
         if not self.spec.has_head:
-            x_out = ops.residual_add(x, pending, self.ds) if pending is not None else x
-            return x_out, cache
+            return x, cache
         hc: dict = {}
         labels, mask = batch["labels"], batch["mask"]
         out = {"nll": self._head_fwd(x, pending, self.ds, labels, mask, 1.0, "norm.weight", hc)}
@@ -221,6 +223,75 @@ class ModelChunk:
         if cfg.mtp_num_layers and "mtp_ids" in batch:
             out["mtp_nll"] = self._mtp_fwd(batch, cache, S)
         return out, cache
+
+    def _layers_fwd(self, x, cache: ChunkCache, S):
+        """The chunk's layer loop.  Returns ``(x, pending)``: on a head chunk the last FC2 output is still to be added (the
+        final norm fuses that add); otherwise the add is done here and ``pending`` is None."""
+        pending = None
+        for li in self.spec.layers:
+            c = self._layer_fwd(f"layers.{li}.", x, pending, self.ds, S, cache.slot)
+            cache.layers.append(c)
+            x, pending = c.h, c.m
+        if not self.spec.has_head and pending is not None:
+            x, pending = self.ops.residual_add(x, pending, self.ds), None
+        return x, pending
+
+    def _layers_bwd(self, g, cache: ChunkCache, S):
+        done = self.on_grads_final
+        for li, c in zip(reversed(self.spec.layers), reversed(cache.layers)):
+            g = self._layer_bwd(f"layers.{li}.", c, g, self.ds, S)
+            if done is not None:
+                done(f"layers.{li}.")
+        return g
+
+    # -- CUDA-graph replay of the layer loops ------------------------------------------------------------------------
+    def enable_graphs(self, pool=True) -> None:
+        """From now on the layer loops of ``forward`` / ``run_backward`` are captured once per in-flight slot and replayed.
+        Everything a replay touches has a fixed address: the loop's input is copied into a static tensor, the per-layer
+        caches are the tensors the forward capture of the slot allocated (the backward graph of the slot reads them),
+        all-gather buffers are the per-(layer, slot) symmetric buffers, and the cross-rank ordering of the fused TP kernels
+        is numbered on the device.  Every graph has a memory pool of its OWN: a pipeline schedule replays the graphs in an
+        order other than the capture order and keeps several slots' caches alive at once, and in a shared pool the
+        temporaries of one graph may be handed to a later capture as its long-lived tensors, which the first graph's next
+        replay would then overwrite.  Embedding, LM head, loss, pipeline send / recv and the library
+        collectives stay outside the graphs.  Call after at least one eager step (lazy allocations, symmetric-memory
+        rendezvous of the call sites) and on every rank of the model-parallel group at the same step."""
+        self.graph_pool = pool
+
+    def _capture(self, fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            out = fn()
+        return g, out
+
+    def _graphed_layers_fwd(self, x, cache: ChunkCache, S):
+        ent = self._graphs.get(("F", cache.slot))
+        if ent is None:
+            x_in = x.clone()
+            sc = ChunkCache()
+            sc.slot = cache.slot
+            g, (x_out, pending) = self._capture(lambda: self._layers_fwd(x_in, sc, S))
+            ent = {"g": g, "x_in": x_in, "layers": sc.layers, "x_out": x_out, "pending": pending}
+            self._graphs[("F", cache.slot)] = ent
+        else:
+            ent["x_in"].copy_(x)
+        ent["g"].replay()
+        self.graph_replays += 1
+        cache.layers = ent["layers"]
+        return ent["x_out"], ent["pending"]
+
+    def _graphed_layers_bwd(self, g_top, cache: ChunkCache, S):
+        ent = self._graphs.get(("B", cache.slot))
+        if ent is None:
+            g_in = g_top.clone()
+            g, g_x = self._capture(lambda: self._layers_bwd(g_in, cache, S))
+            ent = {"g": g, "g_in": g_in, "g_x": g_x}
+            self._graphs[("B", cache.slot)] = ent
+        else:
+            ent["g_in"].copy_(g_top)
+        ent["g"].replay()
+        self.graph_replays += 1
+        return ent["g_x"]
 
     def run_backward(self, batch: dict, cache: ChunkCache, g_out: torch.Tensor | None = None):
         """Accumulates weight gradients; returns dL/dx_in (None on an embedding chunk)."""
@@ -238,10 +309,10 @@ class ModelChunk:
                     done("output.weight")
         else:
             g = g_out
-        for li, c in zip(reversed(self.spec.layers), reversed(cache.layers)):
-            g = self._layer_bwd(f"layers.{li}.", c, g, self.ds, S)
-            if done is not None:
-                done(f"layers.{li}.")
+        if self.graph_pool is not None:
+            g = self._graphed_layers_bwd(g, cache, S)
+        else:
+            g = self._layers_bwd(g, cache, S)
         self._free_slots.append(cache.slot)  # the gather buffers of this micro-batch may be reused
         if self.spec.has_embedding:
             self._cap("bwd", "tok_embeddings", g)

@@ -47,6 +47,7 @@ class FusedTP:
         self.ready = symm_empty(8, torch.int32, device, group)            # ready[q]: last call rank q's shard is in place for
         self.ready.tensor.zero_()
         self.barrier = PeerBarrier(device, group)                          # also orders the zeroing above before any use
+        self.barrier.device_epochs = True   # the barrier numbers its own calls: the layer code can be replayed from CUDA graphs
         self.g_turn = self.s_turn = 0
         self.n_copy = n_copy_ctas
         self.calls = {"ag_gemm": 0, "gemm_rs": 0, "copy_in": 0}

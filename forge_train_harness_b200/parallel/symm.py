@@ -43,8 +43,15 @@ class PeerBarrier:
         dist.barrier(group=group)  # every pad is zero before the first epoch is written
         self.epoch = [0] * lanes
         self.limit_s = limit_s
+        # device-side epoch counters: with ``device_epochs`` the kernel numbers its own calls, so a captured CUDA graph
+        # that contains barriers can be replayed (a host-side epoch would be frozen into the graph)
+        self.epoch_dev = torch.zeros(lanes, dtype=torch.int32, device=device)
+        self.device_epochs = False
 
     def __call__(self, lane: int = 0):
         from ..ops.cuda_ops import _C
+        if self.device_epochs:
+            _C.peer_barrier(self.buf.ptrs, self.buf.rank, 0, lane, self.limit_s, self.epoch_dev)
+            return
         self.epoch[lane] += 1
-        _C.peer_barrier(self.buf.ptrs, self.buf.rank, self.epoch[lane], lane, self.limit_s)
+        _C.peer_barrier(self.buf.ptrs, self.buf.rank, self.epoch[lane], lane, self.limit_s, None)

@@ -43,6 +43,8 @@ def main(argv=None):
     ap.add_argument("--model", default="minicpm4_8b")
     ap.add_argument("--mbs", type=int, default=1)
     ap.add_argument("--json", default="")
+    ap.add_argument("--skip-dp", action="store_true", help="time only the tensor-parallel paths")
+    ap.add_argument("--n-copy", type=int, default=0, help="copy CTAs of the all-gather kernel (0 = its default)")
     a = ap.parse_args(argv)
     init_distributed()
     rank, tp = dist.get_rank(), dist.get_world_size()
@@ -55,15 +57,16 @@ def main(argv=None):
     M, H, F = a.mbs * cfg.seq_length, cfg.hidden_size, cfg.ffn_hidden_size
     Ms = M // tp
     group = dist.group.WORLD
-    f = fused_tp.try_create(group, tp, rank, M, H, dev)
-    assert f is not None, "fused TP path unavailable"
+    f = fused_tp.try_create(group, tp, rank, M, H, dev, required=True)
+    f.n_copy = a.n_copy
     nccl = TPComm(group, tp, rank, True)
     r = lambda *s: torch.randn(*s, device=dev, dtype=torch.float32).mul_(0.3).to(torch.bfloat16)
     rows = []
 
-    def rec(name, t_fused, t_lib, flops, link_bytes):
+    def rec(name, t_fused, t_lib, flops, link_bytes, t_gemm=None):
         roof = max(flops / (peaks["bf16_tflops"] * 1e12), link_bytes / (NVLINK_GBS * 1e9))
         row = {"path": name, "tp": tp, "fused_ms": t_fused * 1e3, "library_ms": t_lib * 1e3, "speedup_vs_library": t_lib / t_fused,
+               "gemm_alone_ms": None if t_gemm is None else t_gemm * 1e3,
                "roofline_ms": roof * 1e3, "achieved_fraction_of_roofline": roof / t_fused,
                "bound": "compute" if flops / (peaks["bf16_tflops"] * 1e12) >= link_bytes / (NVLINK_GBS * 1e9) else "nvlink"}
         rows.append(row)
@@ -76,12 +79,22 @@ def main(argv=None):
         x, w = r(Ms, H), r(N, H)
         tf = timed(lambda: f.ag_gemm(x, w, False))
         tl = timed(lambda: ops.linear_fwd(nccl.gather_rows(x), w))
-        rec(name, tf, tl, 2.0 * M * N * H, link)
+        xf = r(M, H)
+        rec(name, tf, tl, 2.0 * M * N * H, link, timed(lambda: ops.linear_fwd(xf, w)))
     for name, K in (("gemm_rs_wo", cfg.q_dim // tp), ("gemm_rs_fc2", F // tp)):
         x, w = r(M, K), r(H, K)
         tf = timed(lambda: f.gemm_rs(x, w, False))
         tl = timed(lambda: nccl.reduce_scatter_rows(ops.linear_fwd(x, w)))
-        rec(name, tf, tl, 2.0 * M * H * K, link)
+        rec(name, tf, tl, 2.0 * M * H * K, link, timed(lambda: ops.linear_fwd(x, w)))
+    if a.skip_dp:
+        torch.cuda.synchronize()
+        check_status()
+        if a.json and rank == 0:
+            with open(a.json, "w") as fh:
+                json.dump({"peaks": peaks, "nvlink_gbs": NVLINK_GBS, "model": a.model, "mbs": a.mbs, "rows": rows}, fh, indent=1)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     # DP gradient path on a 1 G-element (fp32) buffer: pull reduce-scatter + sumsq, then AdamW with parameter push
     n = 256 * 1024 * 1024
 

@@ -31,7 +31,7 @@ def main():
                                 ffn_hidden_size=512, num_attention_heads=4, num_query_groups=2, head_dim=64)
     cfg = fth.RunConfig(model=model, optim=fth.OptimConfig(lr=2e-3, lr_schedule="constant"), parallel=fth.ParallelConfig(**par),
                         train=fth.TrainConfig(num_steps=4, micro_batch_size=2, global_batch_size=8, seed=5, dtype="bf16",
-                                              cuda_graph=False),
+                                              cuda_graph=mode.endswith(":graph")),
                         data=fth.DataConfig(prefetch_size=0))
     tr = fth.Trainer(cfg, quiet=True)
     out = []
@@ -42,9 +42,11 @@ def main():
     from forge_train_harness_b200.ops.cuda_ops import check_status
     check_status()
     fused = (tr.opt.fused is not None) or (tr.tpc.fused is not None)
+    replays = sum(c.graph_replays for c in tr.chunks)
     tr.close()
     if tr.rank == 0:
-        print("RESULT " + json.dumps({"mode": mode, "fused": fused, "steps": out}), flush=True)
+        print("RESULT " + json.dumps({"mode": mode, "fused": fused, "steps": out, "graph_replays": replays,
+                                      "paths": tr.paths()}), flush=True)
     import torch.distributed as dist
     if dist.is_initialized():
         dist.barrier()

@@ -145,3 +145,24 @@ def test_env_check_reports_pins_and_toolkit():
     assert names["python"][1] and names["torch"][1] and names["cuda toolkit (nvcc, sm_100a)"][1]
     bad = {r[0]: r for r in env_check.checks(nvcc_output="Cuda compilation tools, release 11.8, V11.8.89")}
     assert not bad["cuda toolkit (nvcc, sm_100a)"][1]
+
+
+def test_step_profile_summary_and_delta(tmp_path, monkeypatch):
+    """One env var profiles one step of one rank; the summary has per-kernel totals, busy / idle time and a delta."""
+    from forge_train_harness_b200.utils import step_profile as sp
+    agg = {"gemm": {"launches": 2, "us": 30.0}, "norm": {"launches": 1, "us": 5.0}}
+    cur = sp._finish(dict(agg), [(0.0, 10.0), (5.0, 25.0), (40.0, 45.0)])
+    assert cur["busy_us"] == 30.0 and cur["span_us"] == 45.0 and cur["idle_us"] == 15.0 and cur["n_launches"] == 3
+    prev = sp._finish({"gemm": {"launches": 2, "us": 40.0}, "old": {"launches": 1, "us": 1.0}}, [(0.0, 41.0)])
+    md = sp.render_md(cur, prev)
+    assert "| `gemm` | 2 | 30 |" in md and "-10 |" in md and "new |" in md and "no longer launched: `old`" in md
+    # the hook in the training loop: CPU run, step 2 profiled (CPU activities only; the file is still written)
+    import forge_train_harness_b200 as fth
+    monkeypatch.setenv("FORGE_PROFILE_STEP", "2")
+    monkeypatch.setenv("FORGE_PROFILE_DIR", str(tmp_path))
+    cfg = fth.RunConfig(model=fth.preset("tiny"), optim=fth.OptimConfig(lr=1e-3, lr_schedule="constant"),
+                        train=fth.TrainConfig(num_steps=2, micro_batch_size=1, grad_accum_steps=1, dtype="fp32", cuda_graph=False),
+                        data=fth.DataConfig(prefetch_size=0)).replace(model={"seq_length": 32, "padded_vocab_size": 256})
+    import io
+    fth.run_training_loop(cfg, out=io.StringIO())
+    assert (tmp_path / "step_2_rank0.json").exists() and (tmp_path / "step_2_rank0.md").exists()

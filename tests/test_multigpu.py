@@ -53,6 +53,19 @@ def test_tp2_sp_fused_and_nccl_and_pp2_match_single_gpu():
     close(single, run("pp", 2), 2e-2)
 
 
+@needs2
+def test_tp2_layer_loops_replayed_from_cuda_graphs_match_eager():
+    """After one eager step the layer loops run from CUDA graphs (fused TP kernels with device-numbered ordering inside):
+    same losses as the eager run of the same layout, and the graphs really were replayed."""
+    eager = run("tp_sp", 2)
+    graph = run("tp_sp:graph", 2)
+    assert graph["graph_replays"] > 0 and eager["graph_replays"] == 0 and graph["fused"]
+    close(eager, graph, 5e-3)
+    pp = run("pp:graph", 2)
+    assert pp["graph_replays"] > 0
+    close(run("single", 1), pp, 2e-2)
+
+
 needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 
 
@@ -72,6 +85,9 @@ def test_tp2_pp2_and_interleaved_match_single_gpu():
     single = run("single", 1)
     close(single, run("tp2pp2", 4), 2e-2)
     close(single, run("tp2pp2v2", 4), 2e-2)
+    g = run("tp2pp2v2:graph", 4)
+    assert g["graph_replays"] > 0
+    close(single, g, 2e-2)
 
 
 @needs4

@@ -276,7 +276,7 @@ def test_bounded_peer_wait_runs_out_and_reports_status(ops):
     _C.read_status(True)
     pads = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
     # rank 0 of a 2-rank barrier whose rank 1 does not exist: slot 1 of the own pad is never written
-    _C.peer_barrier([p.data_ptr() for p in pads], 0, 1, 0, 0.05)
+    _C.peer_barrier([p.data_ptr() for p in pads], 0, 1, 0, 0.05, None)
     torch.cuda.synchronize()
     assert int(pads[1][0]) == 1 and int(pads[0][0]) == 1      # the release stores went out
     with pytest.raises(RuntimeError, match="peer flag never set"):
@@ -284,7 +284,7 @@ def test_bounded_peer_wait_runs_out_and_reports_status(ops):
     check_status()                                             # the read cleared it
     # the same barrier completes once the missing flag is there, and ordinary kernels still run
     pads[0][1] = 2
-    _C.peer_barrier([p.data_ptr() for p in pads], 0, 2, 0, 0.05)
+    _C.peer_barrier([p.data_ptr() for p in pads], 0, 2, 0, 0.05, None)
     x, w = rnd(64, 256), rnd(256)
     y, _ = ops.rmsnorm_fwd(x, w, 1e-6)
     torch.cuda.synchronize()
