@@ -21,6 +21,8 @@ int fth_embedding_fwd(const int* ids, const void* w, void* out, int M, int H, in
                       cudaStream_t stream);
 int fth_embedding_bwd(const void* dout, const int* ids, float* main_grad, int M, int H, int vocab_start, int vocab_local,
                       float scale, cudaStream_t stream);
+int fth_embedding_bwd_det(const void* dout, const int* order, const int* seg_start, const int* seg_id, float* main_grad,
+                          int n_seg, int H, float scale, cudaStream_t stream);
 int fth_cross_entropy(void* logits, const int* labels, const float* mask, float* nll, float* st_max, float* st_sum,
                       float* st_tgt, const float* lse_in, int M, int V, long long ld, int vocab_start, float grad_scale,
                       int mode, cudaStream_t stream);

@@ -155,6 +155,21 @@ void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& ma
         "embedding_bwd");
 }
 
+// Deterministic embedding backward: `order` = row indices sorted (stably) by token id, `seg_start` [n_seg + 1] the runs of
+// equal ids in that order, `seg_id` [n_seg] each run's row of main_grad (ids outside this vocabulary shard already removed).
+void embedding_bwd_det(const at::Tensor& dout, const at::Tensor& order, const at::Tensor& seg_start, const at::Tensor& seg_id,
+                       at::Tensor& main_grad, double scale) {
+  need_bf16(dout, "dout");
+  need_i32(order, "order");
+  need_i32(seg_start, "seg_start");
+  need_i32(seg_id, "seg_id");
+  need_f32(main_grad, "main_grad");
+  TORCH_CHECK(seg_start.numel() == seg_id.numel() + 1, "embedding_bwd_det: seg_start needs n_seg + 1 entries");
+  check(fth_embedding_bwd_det(dout.data_ptr(), order.data_ptr<int>(), seg_start.data_ptr<int>(), seg_id.data_ptr<int>(),
+                              main_grad.data_ptr<float>(), (int)seg_id.numel(), (int)main_grad.size(1), (float)scale, cur_stream()),
+        "embedding_bwd_det");
+}
+
 // mode 0: returns nll; logits overwritten with the gradient.
 at::Tensor cross_entropy(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& mask, double grad_scale,
                          int64_t vocab_start) {
@@ -407,6 +422,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("residual_add", &residual_add);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_bwd_det", &embedding_bwd_det);
   m.def("cross_entropy", &cross_entropy);
   m.def("ce_stats", &ce_stats);
   m.def("ce_grad", &ce_grad);

@@ -311,6 +311,34 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, con
   }
 }
 
+// Deterministic form: the rows are visited token by token in a fixed order.  `order` lists the row indices sorted by
+// token id (stable, so equal ids keep their row order), `seg_start[s] .. seg_start[s+1]` is the run of rows of one token
+// and `seg_id[s]` that token (already relative to the shard and inside it).  One block per run sums its rows in that
+// order in fp32 and adds the total to main_grad once: no atomics, the result does not depend on the schedule.
+__global__ void embedding_bwd_det_kernel(const __nv_bfloat16* __restrict__ dout, const int* __restrict__ order,
+                                         const int* __restrict__ seg_start, const int* __restrict__ seg_id,
+                                         float* __restrict__ main_grad, int n_seg, int H, float scale) {
+  const int vpr = H / 8;
+  for (int s = blockIdx.x; s < n_seg; s += gridDim.x) {
+    const int r0 = seg_start[s], r1 = seg_start[s + 1];
+    float* dst = main_grad + (size_t)seg_id[s] * H;
+    for (int v = threadIdx.x; v < vpr; v += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = r0; j < r1; ++j) {
+        float f[8];
+        load8(dout + (size_t)order[j] * H + v * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
+      float cur[8];
+      load8(dst + v * 8, cur);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) cur[e] += acc[e] * scale;
+      store8(dst + v * 8, cur);
+    }
+  }
+}
+
 // ---- fused cross-entropy ------------------------------------------------------------------------
 constexpr int kCeThreads = 1024;
 
@@ -627,6 +655,17 @@ int fth_embedding_bwd(const void* dout, const int* ids, float* main_grad, int M,
   int grid = (int)min((total + 255) / 256, (size_t)num_sms() * 16);
   embedding_bwd_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dout, ids, main_grad, M, H, vocab_start,
                                                  vocab_local, scale);
+  return 0;
+}
+
+int fth_embedding_bwd_det(const void* dout, const int* order, const int* seg_start, const int* seg_id, float* main_grad,
+                          int n_seg, int H, float scale, cudaStream_t stream) {
+  if (H % 8) return -1;
+  if (n_seg <= 0) return 0;
+  const int threads = H / 8 < 128 ? 64 : 128;
+  const int grid = n_seg < num_sms() * 16 ? n_seg : num_sms() * 16;
+  embedding_bwd_det_kernel<<<grid, threads, 0, stream>>>((const __nv_bfloat16*)dout, order, seg_start, seg_id, main_grad,
+                                                        n_seg, H, scale);
   return 0;
 }
 

@@ -127,10 +127,26 @@ class MegatronBinary:
         return order
 
     def state_dict(self):
-        return {"kind": "megatron_binary", "epoch": self.epoch, "pos": self.pos}
+        """``pos`` counts samples of THIS rank's round-robin share, so the state also records the DP degree it belongs to
+        and the layout-independent number of samples the whole DP group has consumed in the epoch."""
+        return {"kind": "megatron_binary", "epoch": self.epoch, "pos": self.pos, "dp_size": self.dp_size,
+                "consumed_in_epoch": self.pos * self.dp_size}
 
     def load_state_dict(self, sd):
-        self.epoch, self.pos = int(sd["epoch"]), int(sd["pos"])
+        epoch, pos = int(sd["epoch"]), int(sd["pos"])
+        old_dp = int(sd.get("dp_size", self.dp_size))
+        if old_dp != self.dp_size:
+            # Another DP degree: in epoch 0 every rank reads ``order[rank::dp]`` of ONE shared shuffle, so "the group has
+            # consumed the first n samples" carries over.  Later epochs permute each rank's share with a seed that depends
+            # on the layout (the reference's rule), so a position inside them has no counterpart in another layout.
+            if epoch != 0:
+                raise ValueError(f"data position was saved at dp={old_dp} in epoch {epoch}; only an epoch-0 position can be "
+                                 f"moved to dp={self.dp_size} (later epochs are shuffled per DP rank)")
+            consumed = int(sd.get("consumed_in_epoch", pos * old_dp))
+            if consumed % self.dp_size:
+                raise ValueError(f"{consumed} samples consumed at dp={old_dp} do not split evenly over dp={self.dp_size}")
+            pos = consumed // self.dp_size
+        self.epoch, self.pos = epoch, pos
         self._order = self._order_for_epoch(self.epoch)
 
     def seek_microbatches(self, n: int):

@@ -64,6 +64,8 @@ class Trainer:
             os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
             torch.use_deterministic_algorithms(True, warn_only=True)
         self.ops = ops or get_ops(self.device)
+        if hasattr(self.ops, "set_deterministic"):
+            self.ops.set_deterministic(bool(t.deterministic))
         if par.fp8 == "mxfp8" and self.dtype == torch.bfloat16:
             # block-scaled fp8 for every linear product whose dimensions are multiples of 32 (the ragged vocabulary
             # products stay bf16); the one-kernel TP paths are bf16 kernels, so this option uses the library collectives

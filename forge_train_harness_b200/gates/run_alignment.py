@@ -1,7 +1,13 @@
 """Alignment gate against a LIVE run of the reference: same init, same data, same hyper-parameters, compare ``[LOSS]`` lines.
 
     python -m forge_train_harness_b200.gates.run_alignment --model minicpm4_0.5b --steps 60 --window 21 61 \
-        [--nproc 1] [--mbs 4] [--accum 2] [--layers 24] [--out gates_out]
+        [--nproc 1] [--mbs 4] [--accum 2] [--layers 24] [--out gates_out] [--ref l0|engine]
+
+``--ref engine`` puts the reference's produced ENGINE (``training_engine_tensor.run_training_loop``, through
+``baseline/ref_engine_driver.py``) on the reference side instead of its L0 trainer; both sides then start from one
+``canonical_state_fp32.pt`` written here (the reference's own hand-off file, parameters.py:169-190).  The reference's gate of
+this name runs DP = 2, 200 steps, global batch 80, window [101, 201) (config/eval/dense_training/gate_config/long-train.toml):
+``--nproc 2 --steps 200 --mbs 4 --accum 10 --window 101 201 --ref engine``.
 
 The three steps of the reference's gate executor (evals/dispatcher.py:253-331): (1) run the reference side — its unmodified
 pure-PyTorch L0 trainer (ref/reference/train_pure_mup_mtp.py) from ``baseline/_ref`` as a child process; (2) run this
@@ -49,6 +55,7 @@ def main(argv=None):
     ap.add_argument("--out", default="gates_out")
     ap.add_argument("--timeout", type=float, default=1500.0)
     ap.add_argument("--split-logs", default="", help="also write <dir>/ref/ref.log and <dir>/ours/ours.log (dispatcher layout)")
+    ap.add_argument("--ref", default="l0", choices=["l0", "engine"], help="reference side: its L0 trainer or its produced engine")
     a = ap.parse_args(argv)
     m = preset(a.model)
     if a.layers:
@@ -81,6 +88,16 @@ def main(argv=None):
     with open(os.path.join(out, "data_path.txt"), "w") as f:
         f.write(f"1.0 {prefix}\n")
 
+    canon_root = ""
+    if a.ref == "engine":
+        # one weight file for both sides: every full tensor from one seeded CPU generator in the reference's parameter order
+        import torch
+        from ..models import params as P
+        canon_root = os.path.join(out, "canonical")
+        os.makedirs(canon_root, exist_ok=True)
+        state = {spec.name: full for spec, full in P.iter_full_init(m, 1234, True)}
+        torch.save(state, os.path.join(canon_root, "canonical_state_fp32.pt"))
+        del state
     port = 29600 + os.getpid() % 300
     # ---- (1) reference side --------------------------------------------------------------------------------
     env = dict(os.environ)
@@ -99,6 +116,12 @@ def main(argv=None):
                "--weight-decay", "0.1", "--adam-beta1", "0.9", "--adam-beta2", "0.95", "--clip-grad", "1.0", "--seed", "1234",
                "--init-method-std", str(m.init_method_std), "--init-ones", "1", "--eagle-num-layers", "0",
                "--out-dir", os.path.join(out, "ref_out"), "--no-deterministic"]
+    if a.ref == "engine":
+        ref_cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.nproc}", "--master-addr",
+                   "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "baseline", "ref_engine_driver.py"),
+                   "--model", a.model, "--layers", str(m.num_layers), "--steps", str(a.steps), "--mbs", str(a.mbs),
+                   "--accum", str(a.accum), "--data-prefix", prefix, "--ckpt-root", canon_root, "--lr", str(a.lr)]
+        env = dict(os.environ)
     r = subprocess.run(ref_cmd, env=env, cwd=out, capture_output=True, text=True, timeout=a.timeout)
     open(os.path.join(out, "ref.log"), "w").write(r.stdout + "\n--- stderr ---\n" + r.stderr[-20000:])
     ref_recs = wire.parse_loss_lines(r.stdout, strict=False)
@@ -111,6 +134,8 @@ def main(argv=None):
                 "lr_schedule = \"wsd\"\nweight_decay = 0.1\nadam_beta1 = 0.9\nadam_beta2 = 0.95\nclip_grad = 1.0\n")
         f.write(f"\n[train]\nnum_steps = {a.steps}\nmicro_batch_size = {a.mbs}\nglobal_batch_size = {gbs}\nseed = 1234\ndtype = \"bf16\"\n")
         f.write(f"\n[data]\ndata_loader = \"megatron_binary\"\ndata_path = {json.dumps(prefix)}\n")
+        if canon_root:
+            f.write(f"\n[ckpt]\ncheckpoint_root = {json.dumps(canon_root)}\n")
     ours_cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.nproc}", "--master-addr", "127.0.0.1",
                 "--master-port", str(port + 1), "-m", "forge_train_harness_b200.train", "--config", cfg_path]
     o = subprocess.run(ours_cmd, cwd=ROOT, capture_output=True, text=True, timeout=a.timeout)
@@ -122,7 +147,7 @@ def main(argv=None):
             if side == "ref" or not os.path.isfile(os.path.join(a.split_logs, side, "ours.log")):
                 open(os.path.join(a.split_logs, side, f"{side}.log"), "w").write(text)
     # ---- (3) verdict ---------------------------------------------------------------------------------------------
-    res = {"model": m.name, "layers": m.num_layers, "nproc": a.nproc, "global_batch": gbs, "steps": a.steps,
+    res = {"model": m.name, "layers": m.num_layers, "nproc": a.nproc, "reference_side": a.ref, "global_batch": gbs, "steps": a.steps,
            "ref_rc": r.returncode, "ours_rc": o.returncode, "ref_steps": len(ref_recs), "ours_steps": len(our_recs)}
     if ref_recs and our_recs:
         res["first_step"] = {"ref": ref_recs[0].loss, "ours": our_recs[0].loss,

@@ -85,11 +85,21 @@ def long_train(ref_records, our_records, window: tuple[int, int], loss_rel_thres
 
 def trajectory(ref_records, our_records, window: tuple[int, int] | None = None, atol: float = 0.0, rtol: float = 0.0,
                check_grad_norm: bool = True) -> dict:
-    """``atol = rtol = 0`` is the bitwise rule (max abs diff == 0); anything else is the tolerance gate."""
+    """``atol = rtol = 0`` is the bitwise rule (max abs diff == 0); anything else is the tolerance gate.  With a window,
+    EVERY step of ``[window[0], window[1])`` must be present on both sides (a run that printed one step and died must not
+    pass; the reference compares over the whole gate window, verdicts/resume.py:143-188); without one, the steps both
+    sides have are compared."""
     ref, ours = by_step(ref_records), by_step(our_records)
     steps = sorted(set(ref) & set(ours))
     if window:
-        steps = [s for s in steps if window[0] <= s < window[1]]
+        want = list(range(window[0], window[1]))
+        missing_ref = [s for s in want if s not in ref]
+        missing_ours = [s for s in want if s not in ours]
+        if missing_ref or missing_ours:
+            return {"passed": False, "reason": f"window [{window[0]}, {window[1]}) incomplete: baseline lacks "
+                                               f"{len(missing_ref)} step(s), candidate lacks {len(missing_ours)}",
+                    "missing_baseline_steps": missing_ref[:20], "missing_candidate_steps": missing_ours[:20]}
+        steps = want
     if not steps:
         return {"passed": False, "reason": "no overlapping steps"}
     worst_l = worst_g = 0.0
@@ -112,11 +122,18 @@ def align(ref_dump: str, our_dump: str, family: str, backward: bool = False) -> 
     return r
 
 
-def resume(text: str, window: tuple[int, int]) -> dict:
-    """One log holding ``[LOSS_REF]`` (uninterrupted) and ``[LOSS_RES]`` (resumed) lines."""
+def resume(text: str, window: tuple[int, int], returncode: int | None = None) -> dict:
+    """One log holding ``[LOSS_REF]`` (uninterrupted) and ``[LOSS_RES]`` (resumed) lines.  ``returncode`` is the exit
+    status of the run that produced the log: a run that failed cannot pass, whatever it printed before it died."""
     ref = wire.parse_loss_lines(text, "LOSS_REF")
     res = wire.parse_loss_lines(text, "LOSS_RES")
-    return trajectory(ref, res, window)
+    out = trajectory(ref, res, window)
+    if returncode is not None:
+        out["script_succeeded"] = returncode == 0
+        if returncode != 0:
+            out["passed"] = False
+            out.setdefault("reason", f"the resume run exited with status {returncode}")
+    return out
 
 
 def resume_startup(text: str, budget_s: float) -> dict:

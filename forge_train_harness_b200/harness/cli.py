@@ -2,6 +2,8 @@
 
     python -m forge_train_harness_b200.harness run <suite> [--registry configs/eval/dense_training.toml] [--timeout S] [--arg k=v]
     python -m forge_train_harness_b200.harness guard | anti-proxy | unit | info | doctor | echo-config <toml> | render <gate.toml> ...
+    python -m forge_train_harness_b200.harness budget <suite> | env-probe | resources provision|verify | prefetch <prefix> <dir> | sync push <dest>
+    python -m forge_train_harness_b200.harness op-inventory | op-status | op-long <op> --config <toml> [--steps N --window A B --nproc N]
 
 Local suites (``guard``, ``anti-proxy``, ``unit``) run in-process / as a pytest child; gate suites go request -> dispatcher ->
 result JSON between the result markers.  Timeout precedence: ``--timeout`` > ``HARNESS_RUN_TIMEOUT_S`` > the registry value.
@@ -15,7 +17,7 @@ import subprocess
 import sys
 
 from ..config import schema
-from . import dispatcher, guards, render
+from . import dispatcher, guards, render, stage2, workspace
 from . import run_schema as RS
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -37,8 +39,29 @@ def main(argv=None) -> int:
     r.add_argument("--timeout", type=float, default=0.0)
     r.add_argument("--arg", action="append", default=[])
     r.add_argument("--artifacts", default=os.path.join(ROOT, ".artifacts", "runs"))
-    for name in ("guard", "anti-proxy", "unit", "info", "doctor", "env"):
+    for name in ("guard", "anti-proxy", "unit", "info", "doctor", "env", "env-probe", "op-inventory", "op-status"):
         sub.add_parser(name)
+    b = sub.add_parser("budget")
+    b.add_argument("suite")
+    b.add_argument("--registry", default=os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    b.add_argument("--json", action="store_true")
+    rs = sub.add_parser("resources")
+    rs.add_argument("action", choices=["provision", "verify"])
+    pf = sub.add_parser("prefetch")
+    pf.add_argument("source_prefix")
+    pf.add_argument("data_dir")
+    pf.add_argument("--target-gb", type=float, default=0.0)
+    sy = sub.add_parser("sync")
+    sy.add_argument("action", choices=["push"])
+    sy.add_argument("dest")
+    ol = sub.add_parser("op-long")
+    ol.add_argument("op")
+    ol.add_argument("--config", required=True)
+    ol.add_argument("--steps", type=int, default=200)
+    ol.add_argument("--window", type=int, nargs=2, default=[101, 201])
+    ol.add_argument("--nproc", type=int, default=1)
+    ol.add_argument("--version", default=None)
+    ol.add_argument("--set", action="append", default=[])
     e = sub.add_parser("echo-config")
     e.add_argument("path")
     rn = sub.add_parser("render")
@@ -61,6 +84,46 @@ def main(argv=None) -> int:
     if a.cmd == "env":
         from . import env_check
         return env_check.main([])
+    if a.cmd == "env-probe":
+        res = workspace.env_probe()
+        print(json.dumps(res, indent=1))
+        return 0 if res["passed"] else 2
+    if a.cmd == "budget":
+        gate = render.load_toml(a.registry).get("evals", {}).get(a.suite)
+        if gate is None:
+            print(f"unknown suite {a.suite!r}", file=sys.stderr)
+            return 1
+        env = os.environ.get("HARNESS_RUN_TIMEOUT_S")
+        t, src = (float(env), "HARNESS_RUN_TIMEOUT_S") if env else (float(gate.get("timeout_s", 600)), "registry")
+        print(json.dumps({"suite": a.suite, "timeout_s": t, "source": src}) if a.json else int(t))
+        return 0
+    if a.cmd == "resources":
+        try:
+            if a.action == "provision":
+                print(json.dumps(workspace.provision(), indent=1))
+                return 0
+            missing = workspace.assert_provisioned()
+            print(json.dumps({"missing": missing}))
+            return 0 if not missing else 1
+        except workspace.ResourceError as e:
+            print(str(e), file=sys.stderr)
+            return 1
+    if a.cmd == "prefetch":
+        res = workspace.prefetch(a.source_prefix, a.data_dir, a.target_gb)
+        print(json.dumps(res))
+        return 0 if res["passed"] else 1
+    if a.cmd == "sync":
+        res = workspace.sync_push(a.dest)
+        print(json.dumps(res))
+        return 0 if res["passed"] else 1
+    if a.cmd in ("op-inventory", "op-status"):
+        r = stage2.op_inventory() if a.cmd == "op-inventory" else stage2.op_status()
+        RS.emit_result(stage2.as_result(a.cmd, r), sys.stdout)
+        return 0 if r["passed"] else 1
+    if a.cmd == "op-long":
+        r = stage2.op_long(a.op, a.config, a.steps, tuple(a.window), nproc=a.nproc, version=a.version, extra_sets=a.set)
+        RS.emit_result(stage2.as_result("op-long", r), sys.stdout)
+        return 0 if r.get("passed") else 1
     if a.cmd == "info":
         print(json.dumps({"result_markers": [RS.RESULT_BEGIN, RS.RESULT_END], "runner_metrics": RS.RUNNER_METRICS,
                           "schema_version": RS.RUN_SCHEMA_VERSION}, indent=1))
@@ -92,6 +155,8 @@ def main(argv=None) -> int:
     args = dict(kv.split("=", 1) for kv in a.arg)
     args["timeout_s"] = _timeout(a.timeout, gate.get("timeout_s", 600))
     req = RS.make_run_request(a.suite, args, gate.get("gpu_count", 1))
+    # sliding-window retention: all but the newest N run directories of this suite go before the new one is made
+    workspace.prune_old_runs(a.artifacts, a.suite, int(reg.get("artifacts", {}).get("retention", {}).get("per_suite", 0)))
     art = os.path.join(a.artifacts, req["run_id"])
     os.makedirs(art, exist_ok=True)
     with open(os.path.join(art, "request.json"), "w") as f:

@@ -48,7 +48,7 @@ def _run_side(argv, log_path, timeout_s, env=None, cwd=None):
     return rc, out, timed_out
 
 
-def _verdict(kind: str, gate: dict, run_dir: str) -> tuple[bool, dict]:
+def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) -> tuple[bool, dict]:
     ref_log = os.path.join(run_dir, "ref", "ref.log")
     our_log = os.path.join(run_dir, "ours", "ours.log")
     rd = lambda p: open(p).read() if os.path.isfile(p) else ""  # noqa: E731  (missing artefacts read as empty = failed)
@@ -64,7 +64,7 @@ def _verdict(kind: str, gate: dict, run_dir: str) -> tuple[bool, dict]:
         r = {"passed": r["passed"], "checks_total": r["overlap"], "bitwise_match": r["overlap"] - len(r["mismatched"]),
              "hash_capture_level": gate.get("hash_capture_level", 2), "mismatched": r["mismatched"][:20]}
     elif kind == "resume":
-        r = V.resume(rd(our_log), tuple(gate["gate_window"]))
+        r = V.resume(rd(our_log), tuple(gate["gate_window"]), returncode=ours_rc)
     elif kind == "resume_startup":
         r = V.resume_startup(rd(our_log), gate.get("resume_startup_budget_s", 18.0))
     elif kind == "wsd_sft":
@@ -104,12 +104,14 @@ def run_suite(request: dict, registry: dict, repo_root: str, artifact_dir: str, 
             if hit:
                 shutil.copytree(ref_dir, hit, dirs_exist_ok=True)
             details["ref_cache"] = "miss"
+    ours_rc = None
     if gate.get("ours_cmd"):
         rc, out, to = _run_side(_subst(gate["ours_cmd"], ctx), os.path.join(artifact_dir, "ours", "ours.log"), timeout_s, cwd=repo_root)
         if rc != 0:
             return RS.make_run_result(suite, False, f"engine side failed (rc {rc})", {},
                                       dict(details, failure_class=V.classify_failure(out, to), side="ours"))
-    ok, metrics = _verdict(gate["verdict"], gate, artifact_dir)
+        ours_rc = rc
+    ok, metrics = _verdict(gate["verdict"], gate, artifact_dir, ours_rc)
     metrics = {k: v for k, v in metrics.items() if k != "step_diffs"}
     res = RS.make_run_result(suite, ok, f"{suite}: {'PASS' if ok else 'FAIL'}", metrics, details)
     with open(os.path.join(artifact_dir, "result.json"), "w") as f:

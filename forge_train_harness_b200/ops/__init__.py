@@ -43,6 +43,14 @@ class RoutedOps:
             setattr(self, n, getattr(impl, n))
             self.versions[n] = ver
         self.name = default
+        self._impls = impls
+
+    def set_deterministic(self, on: bool) -> None:
+        """Forwarded to every implementation that has a deterministic mode (fixed summation orders instead of atomics)."""
+        for impl in self._impls.values():
+            f = getattr(impl, "set_deterministic", None)
+            if f is not None:
+                f(on)
 
 
 def get_ops(device="cpu"):

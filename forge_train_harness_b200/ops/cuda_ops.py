@@ -50,9 +50,32 @@ class Sm100Ops:
     def embedding_fwd(ids, weight, scale, vocab_start=0, sharded=False):
         return _C.embedding_fwd(ids, weight, float(scale), int(vocab_start))
 
+    deterministic = False  # set by the engine from train.deterministic: fixed summation orders, no float atomics
+
+    @staticmethod
+    def set_deterministic(on: bool) -> None:
+        """Deterministic mode: the embedding backward sums each token's rows in a fixed order instead of with float
+        atomics, and accumulating GEMMs use one k split per output tile (fixed reduce-add order).  The attention
+        backward still sums its partial dQ / dK / dV tiles with reduce-adds whose order is not fixed."""
+        Sm100Ops.deterministic = bool(on)
+        _C.gemm_set_deterministic(bool(on))
+
     @staticmethod
     def embedding_bwd(dout, ids, main_grad, scale, vocab_start=0):
-        _C.embedding_bwd(dout, ids, main_grad, float(scale), int(vocab_start))
+        if not Sm100Ops.deterministic:
+            _C.embedding_bwd(dout, ids, main_grad, float(scale), int(vocab_start))
+            return
+        local = ids.to(torch.int64) - int(vocab_start)
+        keep = (local >= 0) & (local < main_grad.shape[0])
+        rows = torch.nonzero(keep, as_tuple=False).reshape(-1)
+        if rows.numel() == 0:
+            return
+        sorted_ids, perm = torch.sort(local[rows], stable=True)
+        order = rows[perm].to(torch.int32)
+        seg_id, counts = torch.unique_consecutive(sorted_ids, return_counts=True)
+        seg_start = torch.zeros(seg_id.numel() + 1, dtype=torch.int32, device=ids.device)
+        seg_start[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        _C.embedding_bwd_det(dout, order, seg_start, seg_id.to(torch.int32), main_grad, float(scale))
 
     # ---- RMSNorm ---------------------------------------------------------
     @staticmethod
@@ -109,26 +132,30 @@ class Sm100Ops:
         return seq_len % 128 == 0 and d in (64, 128)
 
     @staticmethod
-    def attention_fwd(qkv, seq_len, n_kv, g, d):
+    def _require_attention_shape(seq_len, d):
+        """The flash kernels tile the sequence by 128 and exist for head sizes 64 and 128.  Anything else is refused here:
+        quietly handing such a shape to the PyTorch oracle would train on library kernels without anyone noticing (select
+        ``OP_ATTENTION_FWD=baseline`` etc. to run the oracle on purpose)."""
         if not Sm100Ops.attention_supported(seq_len, d):
-            from .torch_ops import TorchOps
-            return TorchOps.attention_fwd(qkv, seq_len, n_kv, g, d)
+            raise ValueError(f"sm_100a attention needs seq_len to be a multiple of 128 and head_dim 64 or 128 "
+                             f"(got seq_len={seq_len}, head_dim={d}); set OP_ATTENTION_FWD / OP_ATTENTION_BWD / "
+                             f"OP_ATTENTION_ROPE_BWD=baseline to use the PyTorch implementation")
+
+    @staticmethod
+    def attention_fwd(qkv, seq_len, n_kv, g, d):
+        Sm100Ops._require_attention_shape(seq_len, d)
         out, lse = _C.flash_fwd(qkv, seq_len, n_kv, g, d)
         return out, lse
 
     @staticmethod
     def attention_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d):
-        if not Sm100Ops.attention_supported(seq_len, d):
-            from .torch_ops import TorchOps
-            return TorchOps.attention_bwd(dout, qkv, out, lse, seq_len, n_kv, g, d)
+        Sm100Ops._require_attention_shape(seq_len, d)
         return _C.flash_bwd(dout, qkv, out, lse, None, seq_len, n_kv, g, d)
 
     @staticmethod
     def attention_rope_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d):
         """Attention backward with the RoPE backward folded into the gradient's bf16 write-out."""
-        if not Sm100Ops.attention_supported(seq_len, d):
-            from .torch_ops import TorchOps
-            return TorchOps.attention_rope_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d)
+        Sm100Ops._require_attention_shape(seq_len, d)
         return _C.flash_bwd(dout, qkv, out, lse, table, seq_len, n_kv, g, d)
 
     # ---- SwiGLU ---------------------------------------------------------------

@@ -8,6 +8,7 @@ Cases (a few hundred MB on the device at most, GEMM operands larger than the 126
   mxfp8_quant_row / mxfp8_quant_col     quantisation of a 16384 x 4096 bf16 activation
   flash_fwd / flash_bwd                 1 x 4096 tokens, 16 query / 2 KV heads of 64
   rmsnorm_fwd / rmsnorm_bwd / swiglu_fwd / swiglu_bwd / rope / cross_entropy    the 0.5B shapes at 16384 (CE: 4096) tokens
+  rmsnorm_plain / embedding_fwd / embedding_bwd / adamw                          the same shapes; AdamW on 64 Mi parameters
   microbatch                            engine steps of the 0.5B shape cut to 2 layers: one micro-batch of 4 x 4096 tokens per
                                         step, no CUDA graph, so that a launch list shows every kernel of a layer and of the head
 """
@@ -56,6 +57,23 @@ def main(argv=None):
         gw = torch.zeros(H, device=dev)
         fn = (lambda: ops.residual_rmsnorm_fwd(x, res, 0.3, w, 1e-6)) if a.op == "rmsnorm_fwd" else \
              (lambda: ops.rmsnorm_bwd(res, x, w, rstd, gw, res))
+    elif a.op == "rmsnorm_plain":
+        x, w = r(M, H), r(H)
+        fn = lambda: ops.rmsnorm_fwd(x, w, 1e-6)
+    elif a.op in ("embedding_fwd", "embedding_bwd"):
+        ids = torch.randint(0, V, (M,), device=dev, dtype=torch.int32)
+        w, dout = r(V, H), r(M, H)
+        mg = torch.zeros(V, H, device=dev)
+        fn = (lambda: ops.embedding_fwd(ids, w, 12.0)) if a.op == "embedding_fwd" else \
+             (lambda: ops.embedding_bwd(dout, ids, mg, 12.0))
+    elif a.op == "adamw":
+        n = 64 * 1024 * 1024
+        master, m_, v_, grad = (torch.randn(n, device=dev) for _ in range(4))
+        v_.abs_()
+        param = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        one = torch.ones((), device=dev)
+        table = ops.build_adam_table([(0, 0, n, 1.0, True)], dev)
+        fn = lambda: ops.adamw_segments(master, m_, v_, grad, param, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3, one, table)
     elif a.op in ("swiglu_fwd", "swiglu_bwd"):
         gu, di = r(M, 2 * F), r(M, F)
         fn = (lambda: ops.swiglu_fwd(gu)) if a.op == "swiglu_fwd" else (lambda: ops.swiglu_bwd(di, gu))

@@ -101,3 +101,44 @@ def test_legacy_codec_round_trips_with_the_reference(tmp_path):
     r = subprocess.run([sys.executable, os.path.join(os.path.dirname(__file__), "_legacy_codec_worker.py"), str(tmp_path)],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "LEGACY_CODEC_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_megatron_binary_cursor_moves_between_dp_degrees(tmp_path):
+    """The saved data position of an indexed corpus is a per-rank count: loading it at another DP degree must resume at
+    the same GLOBAL position (same set of consumed samples), or refuse when that is impossible."""
+    import numpy as np
+    from forge_train_harness_b200.data.sources import MegatronBinary, write_megatron_binary
+    rng = np.random.RandomState(0)
+    docs = [rng.randint(0, 1000, size=rng.randint(40, 90)).astype(np.int32) for _ in range(300)]
+    prefix = str(tmp_path / "corpus")
+    write_megatron_binary(prefix, docs)
+    S, mbs, seed = 16, 2, 11
+
+    def consume(dp, steps_mb, states=None):
+        """Run all ranks of a dp-way group for ``steps_mb`` micro-batches each; returns (rows seen, state of rank 0)."""
+        seen, st0 = [], None
+        for r in range(dp):
+            src = MegatronBinary(prefix, S, mbs, r, dp, seed)
+            if states is not None:
+                src.load_state_dict(states)
+            for _ in range(steps_mb):
+                b = next(src)
+                seen += [tuple(row.tolist()) for row in b["tokens"]]
+            if r == 0:
+                st0 = src.state_dict()
+        return seen, st0
+
+    first, st = consume(2, 6)                      # 2 ranks x 6 micro-batches x 2 = 24 samples
+    assert st["consumed_in_epoch"] == 24 and st["dp_size"] == 2
+    rest4, _ = consume(4, 2, st)                   # resume on 4 ranks
+    ref_all, _ = consume(1, 20)                    # one rank reading the same shared order: first 40 samples
+    assert sorted(first) == sorted(ref_all[:24])
+    assert sorted(rest4) == sorted(ref_all[24:40])
+    bad = dict(st, pos=5, consumed_in_epoch=10)    # 10 samples do not split over 4 ranks
+    with pytest.raises(ValueError, match="do not split evenly"):
+        MegatronBinary(prefix, S, mbs, 0, 4, seed).load_state_dict(bad)
+    with pytest.raises(ValueError, match="epoch 1"):
+        MegatronBinary(prefix, S, mbs, 0, 4, seed).load_state_dict(dict(st, epoch=1))
+    same = MegatronBinary(prefix, S, mbs, 1, 2, seed)
+    same.load_state_dict(dict(st, epoch=1))        # same layout: any epoch restores directly
+    assert same.epoch == 1 and same.pos == st["pos"]

@@ -36,6 +36,19 @@ def run(cfg, ops=None):
     return out, used_graph
 
 
+def deviations(ref, got, name):
+    """Worst relative loss / grad-norm deviation over the steps; also written next to the other run artefacts."""
+    import json
+    import os
+    dl = max(abs(l0 - l1) / abs(l0) for (l0, _), (l1, _) in zip(ref, got))
+    dg = max(abs(g0 - g1) / abs(g0) for (_, g0), (_, g1) in zip(ref, got))
+    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, "engine_parity.jsonl"), "a") as f:
+            f.write(json.dumps({"case": name, "max_rel_loss_dev": dl, "max_rel_grad_norm_dev": dg}) + "\n")
+    return dl, dg
+
+
 def baseline_ops():
     from forge_train_harness_b200.ops import RoutedOps, TorchOps
     return RoutedOps({"baseline": TorchOps}, "baseline")
@@ -46,17 +59,16 @@ def test_sm100_ops_match_pytorch_ops(kind):
     cfg = cfg_for(kind)
     ref, _ = run(cfg, baseline_ops())
     got, _ = run(cfg)
-    for (l0, g0), (l1, g1) in zip(ref, got):
-        assert abs(l0 - l1) / abs(l0) < 1e-2, (ref, got)
-        assert abs(g0 - g1) / abs(g0) < 1e-1, (ref, got)
+    dl, dg = deviations(ref, got, f"sm100_vs_pytorch_{kind}")
+    assert dl < 2e-3 and dg < 2e-2, (dl, dg, ref, got)
 
 
 def test_cuda_graph_replay_matches_eager():
     eager, g0 = run(cfg_for("plain", graph=False, steps=4))
     graph, g1 = run(cfg_for("plain", graph=True, steps=4))
     assert g1 and not g0
-    for (l0, n0), (l1, n1) in zip(eager, graph):
-        assert abs(l0 - l1) / abs(l0) < 2e-3 and abs(n0 - n1) / abs(n0) < 2e-2, (eager, graph)
+    dl, dg = deviations(eager, graph, "graph_vs_eager")
+    assert dl < 1e-3 and dg < 1e-2, (dl, dg, eager, graph)
 
 
 @pytest.mark.parametrize("graph", [False, True])
@@ -66,6 +78,5 @@ def test_mxfp8_linears_train_close_to_bf16(graph):
     ref, _ = run(cfg)
     got, used = run(cfg.replace(parallel={"fp8": "mxfp8"}))
     assert used == graph
-    for (l0, g0), (l1, g1) in zip(ref, got):
-        assert abs(l0 - l1) / abs(l0) < 2e-2, (ref, got)
-        assert abs(g0 - g1) / abs(g0) < 2e-1, (ref, got)
+    dl, dg = deviations(ref, got, f"mxfp8_vs_bf16_graph{int(graph)}")
+    assert dl < 1e-2 and dg < 8e-2, (dl, dg, ref, got)

@@ -189,6 +189,15 @@ def test_long_train_and_trajectory_verdicts():
     text = "\n".join(wire.format_loss_line(r.step, r.loss, 1.0, 0.1, 1.0, "LOSS_REF") for r in _recs(ref)) + "\n" + \
            "\n".join(wire.format_loss_line(r.step, r.loss, 1.0, 0.1, 1.0, "LOSS_RES") for r in _recs(ref)[10:])
     assert V.resume(text, (11, 41))["passed"]
+    # a resumed run that printed one step of the window and died must not pass, nor a run that exited non-zero
+    cut = "\n".join(wire.format_loss_line(r.step, r.loss, 1.0, 0.1, 1.0, "LOSS_REF") for r in _recs(ref)) + "\n" + \
+          wire.format_loss_line(11, _recs(ref)[10].loss, 1.0, 0.1, 1.0, "LOSS_RES")
+    trunc = V.resume(cut, (11, 41))
+    assert not trunc["passed"] and "candidate lacks 29" in trunc["reason"]
+    died = V.resume(text, (11, 41), returncode=1)
+    assert not died["passed"] and died["script_succeeded"] is False
+    assert V.resume(text, (11, 41), returncode=0)["passed"]
+    assert not V.trajectory(_recs(ref), _recs(ref[:5]), window=(1, 41))["passed"]
     assert V.resume_startup("[RESUME_STARTUP] seconds=7.16", 18)["passed"] and not V.resume_startup("x", 18)["passed"]
     assert V.classify_failure("", timed_out=True) == "timeout" and V.classify_failure("NCCL error: unhandled") == "network"
     assert V.classify_failure("CUDA out of memory") == "training_failure"

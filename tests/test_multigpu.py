@@ -24,9 +24,10 @@ def run(mode, nproc, env=None):
 
 
 def close(a, b, tol):
+    """Relative loss deviation below ``tol`` at every step, grad-norm deviation below ``max(2 tol, 2 %)``."""
     for (l0, g0), (l1, g1) in zip(a["steps"], b["steps"]):
         assert abs(l0 - l1) / abs(l0) < tol, (a, b)
-        assert abs(g0 - g1) / abs(g0) < 10 * tol, (a, b)
+        assert abs(g0 - g1) / abs(g0) < max(2 * tol, 2e-2), (a, b)
 
 
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -38,7 +39,7 @@ def test_fused_dp_matches_nccl_and_single_gpu():
     nccl = run("dp_zero", 2, {"FORGE_FUSED_DP": "0"})
     fused = run("dp_zero", 2, {"FORGE_FUSED_DP": "1"})
     assert fused["fused"] and not nccl["fused"]
-    close(single, nccl, 2e-2)
+    close(single, nccl, 5e-3)
     close(nccl, fused, 5e-3)
 
 
@@ -48,9 +49,9 @@ def test_tp2_sp_fused_and_nccl_and_pp2_match_single_gpu():
     nccl = run("tp_sp", 2, {"FORGE_FUSED_TP": "0"})
     fused = run("tp_sp", 2, {"FORGE_FUSED_TP": "1"})
     assert fused["fused"] and not nccl["fused"]
-    close(single, nccl, 2e-2)
-    close(single, fused, 2e-2)
-    close(single, run("pp", 2), 2e-2)
+    close(single, nccl, 5e-3)
+    close(single, fused, 5e-3)
+    close(single, run("pp", 2), 5e-3)
 
 
 @needs2
@@ -63,7 +64,7 @@ def test_tp2_layer_loops_replayed_from_cuda_graphs_match_eager():
     close(eager, graph, 5e-3)
     pp = run("pp:graph", 2)
     assert pp["graph_replays"] > 0
-    close(run("single", 1), pp, 2e-2)
+    close(run("single", 1), pp, 5e-3)
 
 
 needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
@@ -76,18 +77,18 @@ def test_tp4_with_replicated_kv_heads_fused_and_nccl_match_single_gpu():
     nccl = run("tp_sp", 4, {"FORGE_FUSED_TP": "0"})
     fused = run("tp_sp", 4, {"FORGE_FUSED_TP": "1"})
     assert fused["fused"] and not nccl["fused"]
-    close(single, nccl, 2e-2)
-    close(single, fused, 2e-2)
+    close(single, nccl, 5e-3)
+    close(single, fused, 5e-3)
 
 
 @needs4
 def test_tp2_pp2_and_interleaved_match_single_gpu():
     single = run("single", 1)
-    close(single, run("tp2pp2", 4), 2e-2)
-    close(single, run("tp2pp2v2", 4), 2e-2)
+    close(single, run("tp2pp2", 4), 5e-3)
+    close(single, run("tp2pp2v2", 4), 5e-3)
     g = run("tp2pp2v2:graph", 4)
     assert g["graph_replays"] > 0
-    close(single, g, 2e-2)
+    close(single, g, 5e-3)
 
 
 @needs4
@@ -98,10 +99,10 @@ def test_fused_dp_under_tp_and_under_pp_matches_single_gpu():
         nccl = run(mode, 4, {"FORGE_FUSED_DP": "0", "FORGE_FUSED_TP": "0"})
         fused = run(mode, 4)
         assert fused["fused"]
-        close(single, nccl, 2e-2)
-        close(single, fused, 2e-2)
+        close(single, nccl, 5e-3)
+        close(single, fused, 5e-3)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
 def test_tp2_pp2_dp2_matches_single_gpu():
-    close(run("single", 1), run("tp2pp2", 8), 2e-2)
+    close(run("single", 1), run("tp2pp2", 8), 5e-3)
