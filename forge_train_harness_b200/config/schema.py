@@ -182,7 +182,7 @@ class TrainConfig:
 
 @dataclass(frozen=True)
 class DataConfig:
-    data_loader: str = "synthetic"  # "synthetic" | "megatron_binary"
+    data_loader: str = "synthetic"  # "synthetic" | "megatron_binary" | "hf" (streaming parquet / JSON-lines packer) | "modelbest"
     data_path: str = ""
     prefetch_size: int = 8
     synthetic_seed: int = 0

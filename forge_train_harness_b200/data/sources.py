@@ -179,6 +179,12 @@ def build_source(data_cfg, model_cfg, micro_batch: int, dp_rank: int, dp_size: i
                                data_cfg.synthetic_seed)
     if data_cfg.data_loader == "megatron_binary":
         return MegatronBinary(data_cfg.data_path, model_cfg.seq_length, micro_batch, dp_rank, dp_size, seed)
+    if data_cfg.data_loader == "hf":
+        from .hf_stream import HFStream, parse_data_path
+        return HFStream(parse_data_path(data_cfg.data_path), model_cfg.seq_length, micro_batch, dp_rank, dp_size, seed)
+    if data_cfg.data_loader == "modelbest":
+        from .hf_stream import build_modelbest
+        return build_modelbest(data_cfg.data_path)
     raise ValueError(f"unknown data_loader {data_cfg.data_loader!r}")
 
 

@@ -72,8 +72,14 @@ class StagingRing:
 
 
 class CaptureSession:
-    def __init__(self, output_file: str | None, level: int = 1, rank: int = 0, fqn_alias=None, device=None):
-        self.out, self.level, self.rank = output_file, int(level), rank
+    """``mode="hash"`` keeps a digest per tensor (the bitwise gates); ``mode="tensor"`` keeps the tensors themselves on the
+    host and ``dump`` writes one ``torch.save`` file per rank, for the tolerance-mode alignment against a reference whose
+    kernels differ (``verdicts.align_tolerance``)."""
+
+    def __init__(self, output_file: str | None, level: int = 1, rank: int = 0, fqn_alias=None, device=None, mode: str = "hash"):
+        if mode not in ("hash", "tensor"):
+            raise ValueError("capture mode must be 'hash' or 'tensor'")
+        self.out, self.level, self.rank, self.mode = output_file, int(level), rank, mode
         self.records: dict[str, dict] = {}
         self.step, self.mb = 0, 0
         self.calls: dict[tuple, int] = {}
@@ -90,6 +96,9 @@ class CaptureSession:
         self.calls.clear()
 
     def _put(self, key: str, t: torch.Tensor):
+        if self.mode == "tensor":
+            self.records[key] = t.detach().to("cpu", copy=True)
+            return
         self.records[key] = hash_tensor(self.ring.stage(t) if self.ring else t)
 
     # -- capture points ---------------------------------------------------------
@@ -126,6 +135,10 @@ class CaptureSession:
         path = f"{self.out}.rank{self.rank}"
         tmp = path + ".tmp"
         os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        if self.mode == "tensor":
+            torch.save(self.records, tmp)
+            os.replace(tmp, path)
+            return
         with open(tmp, "w") as f:
             json.dump(self.records, f)
             f.flush()
@@ -146,6 +159,54 @@ def load_merged(output_file: str) -> dict:
         with open(fn) as f:
             out.update(json.load(f))
     return out
+
+
+_POS = __import__("re").compile(r"^step_\d+\.rank\d+\.(mb\d+\.)?")
+
+
+def family_key(key: str) -> str:
+    """``step_3.rank0.mb1.fwd.layers.0.wqkv#0`` -> ``fwd.layers.0.wqkv``; ``...grad.<fqn>.preallreduce`` -> ``grad.<fqn>``
+    (post-all-reduce records keep their suffix, so they never stand in for the local gradient)."""
+    k = _POS.sub("", key).split("#", 1)[0]
+    if k.endswith(".preallreduce"):
+        k = k[: -len(".preallreduce")]
+    return k
+
+
+def diff_tensors(baseline: dict, candidate: dict, *, family: str, rel_tol: float, fit_scale: bool = False) -> dict:
+    """Tolerance-mode alignment of two tensor captures.  Keys are reduced to ``<family>.<fqn>`` (the first occurrence of a
+    key wins: step, rank, micro-batch and call index are dropped), tensors are flattened to rows, and for every key both
+    sides have, ``max |a - b| / rms(b)`` must stay below ``rel_tol``.  ``fit_scale`` first removes the best common scalar
+    per key (gradients w.r.t. a module output depend on where a stack applies its residual scale); the fitted scalars are
+    reported.  No overlap, or a shape mismatch, fails."""
+    def reduce(d):
+        out = {}
+        for k, v in d.items():
+            fk = family_key(k)
+            if fk.startswith(family + ".") and isinstance(v, torch.Tensor) and fk not in out:
+                out[fk] = v
+        return out
+    b, c = reduce(baseline), reduce(candidate)
+    common = sorted(set(b) & set(c))
+    rows, worst, bad = {}, 0.0, []
+    for k in common:
+        x, y = c[k].double().reshape(-1), b[k].double().reshape(-1)
+        if x.numel() != y.numel():
+            bad.append(k)
+            rows[k] = {"error": f"sizes {tuple(c[k].shape)} vs {tuple(b[k].shape)}"}
+            continue
+        scale = 1.0
+        if fit_scale:
+            den = float((x * x).sum())
+            scale = float((x * y).sum()) / den if den > 0 else 1.0
+        rms = float(y.pow(2).mean().sqrt()) or 1.0
+        err = float((x * scale - y).abs().max()) / rms
+        rows[k] = {"max_rel_err": err, "scale": scale}
+        worst = max(worst, err)
+        if not err <= rel_tol:
+            bad.append(k)
+    return {"passed": bool(common) and not bad, "overlap": len(common), "mismatched": bad, "worst_rel_err": worst,
+            "rel_tol": rel_tol, "missing_in_candidate": sorted(set(b) - set(c)), "per_key": rows}
 
 
 def diff_captures(baseline: dict, candidate: dict, *, prefix: str = "", require_baseline_complete: bool = False) -> dict:

@@ -20,6 +20,8 @@ from ..runtime.launcher import BoundedTimeout, run_bounded
 from ..utils import wire
 from . import run_schema as RS
 
+ROOT_DIR = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 
 def _subst(argv, ctx):
     return [a.format(**ctx) for a in argv]
@@ -63,6 +65,13 @@ def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) ->
                     gate.get("family", ".fwd."), gate.get("backward", False))
         r = {"passed": r["passed"], "checks_total": r["overlap"], "bitwise_match": r["overlap"] - len(r["mismatched"]),
              "hash_capture_level": gate.get("hash_capture_level", 2), "mismatched": r["mismatched"][:20]}
+    elif kind == "align_tolerance":
+        r = V.align_tolerance(os.path.join(run_dir, "ours", "ref_capture.pt"), os.path.join(run_dir, "ours", "ours_capture.pt"),
+                              gate.get("family", "fwd"), gate.get("rel_tol", 3e-2), gate.get("fit_scale", False))
+    elif kind == "op_long":
+        from . import stage2
+        r = stage2.op_long(gate["op"], os.path.join(ROOT_DIR, gate["config"]), int(gate.get("steps", 200)),
+                           tuple(gate.get("gate_window", (101, 201))), out_dir=os.path.join(run_dir, "op_long"))
     elif kind == "resume":
         r = V.resume(rd(our_log), tuple(gate["gate_window"]), returncode=ours_rc)
     elif kind == "resume_startup":
@@ -70,7 +79,7 @@ def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) ->
     elif kind == "wsd_sft":
         r = V.wsd_sft(rd(ref_log), rd(our_log))
     elif kind == "production":
-        r = V.production(os.path.join(run_dir, "ours", "ckpt"), gate["expected_steps"])
+        r = V.production(os.path.join(run_dir, gate.get("ckpt_subdir", os.path.join("ours", "ckpt"))), gate["expected_steps"])
     else:
         raise KeyError(f"unknown verdict {kind!r}")
     return bool(r.get("passed")), r

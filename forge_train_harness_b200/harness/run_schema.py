@@ -25,6 +25,8 @@ RUNNER_METRICS = {
     "resume_startup": ["seconds", "budget_s"],
     "wsd_sft": ["phases"],
     "production": ["missing"],
+    "align_tolerance": ["checks_total", "within_tolerance", "worst_rel_err", "rel_tol"],
+    "op_long": ["mean_rel_diff", "max_rel_diff", "threshold"],
 }
 
 

@@ -60,7 +60,7 @@ def test_sm100_ops_match_pytorch_ops(kind):
     ref, _ = run(cfg, baseline_ops())
     got, _ = run(cfg)
     dl, dg = deviations(ref, got, f"sm100_vs_pytorch_{kind}")
-    assert dl < 2e-3 and dg < 2e-2, (dl, dg, ref, got)
+    assert dl < 5e-4 and dg < 1e-2, (dl, dg, ref, got)   # measured: 5e-6 .. 7e-5 and 3e-5 .. 5e-3
 
 
 def test_cuda_graph_replay_matches_eager():
@@ -68,7 +68,7 @@ def test_cuda_graph_replay_matches_eager():
     graph, g1 = run(cfg_for("plain", graph=True, steps=4))
     assert g1 and not g0
     dl, dg = deviations(eager, graph, "graph_vs_eager")
-    assert dl < 1e-3 and dg < 1e-2, (dl, dg, eager, graph)
+    assert dl < 1e-5 and dg < 1e-4, (dl, dg, eager, graph)   # measured: identical
 
 
 @pytest.mark.parametrize("graph", [False, True])
@@ -79,4 +79,4 @@ def test_mxfp8_linears_train_close_to_bf16(graph):
     got, used = run(cfg.replace(parallel={"fp8": "mxfp8"}))
     assert used == graph
     dl, dg = deviations(ref, got, f"mxfp8_vs_bf16_graph{int(graph)}")
-    assert dl < 1e-2 and dg < 8e-2, (dl, dg, ref, got)
+    assert dl < 2e-3 and dg < 1e-2, (dl, dg, ref, got)   # measured: 2e-4 and 8.5e-4

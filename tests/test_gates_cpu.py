@@ -201,3 +201,51 @@ def test_long_train_and_trajectory_verdicts():
     assert V.resume_startup("[RESUME_STARTUP] seconds=7.16", 18)["passed"] and not V.resume_startup("x", 18)["passed"]
     assert V.classify_failure("", timed_out=True) == "timeout" and V.classify_failure("NCCL error: unhandled") == "network"
     assert V.classify_failure("CUDA out of memory") == "training_failure"
+
+
+def test_hf_stream_packer_is_deterministic_sharded_and_resumable(tmp_path, monkeypatch, capsys):
+    import json
+    import torch
+    """Local parquet + JSON-lines sources, weighted mix, shuffle buffer, DP split, packing, [DATAHASH] lines, resume."""
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from forge_train_harness_b200.data.hf_stream import HFStream, build_modelbest, parse_data_path
+    a, b = tmp_path / "a", tmp_path / "b"
+    a.mkdir()
+    b.mkdir()
+    for i in range(2):
+        pq.write_table(pa.table({"content": [f"doc a{i}-{j} " + "x" * (j % 7) for j in range(40)] + [""]}), a / f"part{i}.parquet")
+    with open(b / "qa.jsonl", "w") as f:
+        for j in range(30):
+            f.write(json.dumps({"question": f"what is {j}+{j}?", "answer": str(2 * j)}) + "\n")
+    monkeypatch.setenv("CORPUS_A", str(a))
+    monkeypatch.setenv("CORPUS_B", str(b))
+    path = f"2.0 hf://org/a?split=train&text=content&local_env=CORPUS_A&tokenizer=bytes 1.0 hf://org/b?split=train&template=gsm8k_qa&local_env=CORPUS_B&glob=*.jsonl"
+    specs = parse_data_path(path)
+    assert [s.repo for s in specs] == ["org/a", "org/b"] and specs[1].template == "gsm8k_qa"
+
+    def take(rank, dp, n, state=None):
+        s = HFStream(parse_data_path(path), 32, 2, rank, dp, seed=5, buffer_size=16)
+        if state is not None:
+            s.load_state_dict(state)
+        out = [next(s) for _ in range(n)]
+        return out, s.state_dict()
+    x, st = take(0, 1, 6)
+    y, _ = take(0, 1, 6)
+    assert all(torch.equal(p["tokens"], q["tokens"]) and torch.equal(p["labels"], q["labels"]) for p, q in zip(x, y))
+    assert x[0]["tokens"].shape == (2, 32) and torch.equal(x[0]["tokens"][:, 1:], x[0]["labels"][:, :-1])
+    assert int(torch.cat([p["tokens"].reshape(-1) for p in x]).eq(256).sum()) > 0          # EOS between documents
+    first3, st3 = take(0, 1, 3)
+    rest, _ = take(0, 1, 3, st3)
+    assert all(torch.equal(p["tokens"], q["tokens"]) for p, q in zip(first3 + rest, x))      # resume = uninterrupted
+    r0, _ = take(0, 2, 3)
+    r1, _ = take(1, 2, 3)
+    assert not torch.equal(r0[0]["tokens"], r1[0]["tokens"])                                  # ranks read different documents
+    monkeypatch.setenv("FORGE_HF_DATA_DUMP", "1")
+    take(0, 1, 2)
+    assert capsys.readouterr().out.count("[DATAHASH] rank=0 batch=") == 2
+    monkeypatch.delenv("CORPUS_A")
+    with pytest.raises(FileNotFoundError, match="no network access"):
+        take(0, 1, 1)
+    with pytest.raises(RuntimeError, match="modelbest_sdk"):
+        build_modelbest("x")

@@ -166,3 +166,90 @@ def test_step_profile_summary_and_delta(tmp_path, monkeypatch):
     import io
     fth.run_training_loop(cfg, out=io.StringIO())
     assert (tmp_path / "step_2_rank0.json").exists() and (tmp_path / "step_2_rank0.md").exists()
+
+
+def test_stage2_inventory_status_and_op_long(tmp_path, monkeypatch):
+    """The per-op registry agrees with the op router; op-long swaps exactly one op and compares the loss window."""
+    import copy
+    from forge_train_harness_b200.harness import stage2
+    inv = stage2.op_inventory()
+    assert inv["passed"] and inv["ops_registered"] == inv["ops_total"], inv["problems"]
+    reg = copy.deepcopy(stage2.load_registry())
+    reg["ops"]["swiglu_fwd"]["env_var"] = "OP_SWIGLU"          # not what the router reads
+    reg["ops"]["rope_fwd_"]["kernel"] = "forge_train_harness_b200/csrc/elementwise.cu::no_such_kernel"
+    del reg["ops"]["sumsq"]
+    bad = stage2.op_inventory(reg)
+    assert not bad["passed"] and len(bad["problems"]) == 3
+    monkeypatch.setattr(stage2, "_results_dir", lambda: str(tmp_path / "op_long"))
+    st = stage2.op_status()
+    assert st["counts"]["not_started"] == 2 and st["counts"]["unverified"] == 19 and st["passed"]
+    # op-long on CPU: the candidate's one swapped op resolves to the same PyTorch code, so the windows agree exactly
+    r = stage2.op_long("swiglu_fwd", os.path.join(ROOT, "configs", "tiny_cpu_dp2.toml"), steps=6, window=(2, 7), version="baseline",
+                       out_dir=str(tmp_path / "run"), extra_sets=["parallel.use_distributed_optimizer=false", "train.micro_batch_size=1",
+                                                                   "train.global_batch_size=1"])
+    assert r["passed"] and r["mean_rel_diff"] == 0.0, r
+    st = stage2.op_status()
+    assert st["ops"]["swiglu_fwd"]["state"] == "merged" and st["counts"]["merged"] == 1
+    assert not stage2.op_long("swiglu_fwd", "x.toml", version="nope")["passed"]
+
+
+def test_workspace_resources_sync_prefetch_retention(tmp_path):
+    import numpy as np
+    from forge_train_harness_b200.data.sources import write_megatron_binary
+    from forge_train_harness_b200.harness import workspace as W
+    # resources: the first source that verifies is linked; a digest mismatch fails instead of feeding other bytes
+    tok = tmp_path / "src" / "tokenizer.model"
+    tok.parent.mkdir()
+    tok.write_bytes(b"tokenizer-bytes")
+    man = tmp_path / "external_resources.toml"
+    man.write_text(f'''[meta]\nversion = 1\n[[entry]]\nname = "tok"\nkind = "file"\nsha256 = "{W.sha256_file(str(tok))}"\n'''
+                   f'''canonical_relpath = ".resources/tok/tokenizer.model"\nsources = ["hf://org/repo#tokenizer.model", "file://{tmp_path}/nope", "file://{tok}"]\n''')
+    ws = tmp_path / "ws"
+    rep = W.provision(str(ws), str(man))
+    assert rep[0]["source"] == str(tok) and (ws / ".resources/tok/tokenizer.model").read_bytes() == b"tokenizer-bytes"
+    assert W.assert_provisioned(str(ws), str(man)) == []
+    tok.write_bytes(b"swapped")
+    with pytest.raises(W.ResourceError, match="no source verifies"):
+        W.provision(str(ws), str(man))
+    # sync: ignored paths stay behind, vanished files are removed on the far side
+    src = tmp_path / "tree"
+    (src / "forge_train_harness_b200").mkdir(parents=True)
+    (src / "forge_train_harness_b200" / "__init__.py").write_text("x = 1\n")
+    (src / "gpurun_out").mkdir()
+    (src / "gpurun_out" / "big.log").write_text("log")
+    (src / "a.txt").write_text("a")
+    dst = tmp_path / "remote"
+    r1 = W.sync_push(str(dst), str(src))
+    assert r1["passed"] and r1["copied"] == 2 and not (dst / "gpurun_out").exists()
+    (src / "a.txt").unlink()
+    (dst / "forge_train_harness_b200" / "__pycache__").mkdir()
+    r2 = W.sync_push(str(dst), str(src))
+    assert r2["removed"] == 1 and not (dst / "a.txt").exists() and not (dst / "forge_train_harness_b200" / "__pycache__").exists()
+    # prefetch: the corpus is staged next to the trainer and its index parses
+    docs = [np.arange(100, dtype=np.int32) for _ in range(5)]
+    write_megatron_binary(str(tmp_path / "corpus"), docs)
+    pf = W.prefetch(str(tmp_path / "corpus"), str(tmp_path / "data"))
+    assert pf["passed"] and pf["windows_of_17_tokens"] == 500 // 17
+    assert not W.prefetch(str(tmp_path / "missing"), str(tmp_path / "data"))["passed"]
+    # retention: all but the newest two run directories of a suite go
+    runs = tmp_path / "runs"
+    for i in range(4):
+        d = runs / f"long-train-{i}"
+        d.mkdir(parents=True)
+        os.utime(d, (1000 + i, 1000 + i))
+    (runs / "resume-gate-0").mkdir()
+    assert W.prune_old_runs(str(runs), "long-train", 2) == ["long-train-0", "long-train-1"]
+    assert sorted(os.listdir(runs)) == ["long-train-2", "long-train-3", "resume-gate-0"]
+    probe = W.env_probe()
+    assert probe["checks"]["package_is_this_tree"]["ok"] and probe["checks"]["subprocess_config_isomorphic"]["ok"]
+
+
+def test_wsd_sft_suite_with_host_side_kills(tmp_path, capsys):
+    """``harness run wsd-sft``: the three-phase run is SIGKILLed from outside once per phase and restarted; its banners and
+    per-phase trajectories equal a clean run's, and the run directory retention keeps only the newest runs."""
+    rc = cli_main(["run", "wsd-sft", "--artifacts", str(tmp_path / "runs")])
+    res = RS.extract_result(capsys.readouterr().out)
+    assert rc == 0 and res["status"] == "passed", res
+    assert all(p["passed"] and p["complete"] and p["max_abs_loss_diff"] == 0.0 for p in res["metrics"]["phases"].values())
+    log = open(os.path.join(res["details"]["run_dir"], "ours", "ours.log")).read()
+    assert log.count("[PHASE]") >= 6          # three phases, re-announced after each of the three kills
