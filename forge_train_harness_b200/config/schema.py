@@ -177,7 +177,11 @@ class TrainConfig:
     hash_output: str | None = None
     loss_tag: str = "LOSS"
     metrics_jsonl: str | None = None
-    recompute: bool = False
+    recompute: bool = False          # drop the SwiGLU intermediate of every layer and rebuild it in backward
+    # Activation recompute of whole layers: the LAST n layers of every model chunk keep only their input and are run again
+    # in the backward pass (-1 = every layer); the first layers keep their activations (ref/reference/model_pure_mup_mtp.py:
+    # 363-391, --recompute-num-layers).  Trades one extra forward of those layers for their activation memory.
+    recompute_num_layers: int = 0
 
 
 @dataclass(frozen=True)

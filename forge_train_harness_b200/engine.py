@@ -89,6 +89,7 @@ class Trainer:
                        for c in chunks]
         for c in self.chunks:
             c.recompute = t.recompute
+            c.recompute_num_layers = t.recompute_num_layers
         fused = None
         want_dp = os.environ.get("FORGE_FUSED_DP", "1")
         if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 and want_dp != "0":
@@ -100,7 +101,7 @@ class Trainer:
         self.grad_accum = cfg.grad_accum(topo.dp)
         self.source = build_source(cfg.data, m, t.micro_batch_size, topo.dp_rank, topo.dp, t.seed)
         self.prefetch = None
-        self.with_mtp = bool(m.mtp_num_layers) and topo.pp == 1
+        self.with_mtp = bool(m.mtp_num_layers)   # under PP the branch lives on the last stage (with its own copy of the embedding)
         self.stager = BatchStager(t.micro_batch_size, m.seq_length, self.device, self.with_mtp,
                                   dev_slots=self.grad_accum if topo.pp > 1 else 1)
         self.step = t.start_step  # completed steps (absolute)
@@ -234,7 +235,7 @@ class Trainer:
             return
         if topo.tp > 1 and self.tpc.fused is None:
             return                       # library collectives inside the layer loop: left eager
-        if self.with_mtp or self.cfg.model.qk_norm:
+        if self.with_mtp or self.cfg.model.qk_norm or t.recompute_num_layers:
             return
         for c in self.chunks:
             c.enable_graphs()

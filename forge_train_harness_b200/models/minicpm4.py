@@ -42,6 +42,7 @@ class LayerCache:
     gu: torch.Tensor = None
     inter: torch.Tensor = None
     m: torch.Tensor = None  # FC2 output, pending residual
+    dropped: bool = False  # whole-layer recompute: only ``x`` was kept, the rest is rebuilt in the backward pass
 
 
 @dataclass
@@ -67,6 +68,7 @@ class ModelChunk:
         self.ds_mtp = cfg.depth_scale(cfg.mtp_num_layers)
         self.capture = capture  # optional hook: capture(kind, fqn, tensor)
         self.recompute = False
+        self.recompute_num_layers = 0  # last n layers of the chunk keep only their input (-1: all)
         self.on_grads_final = None  # callable(prefix): every parameter under `prefix` has its final gradient of the step
         self._free_slots: list = []   # in-flight micro-batch slots released by finished backward passes
         self._n_slots = 0
@@ -228,10 +230,14 @@ class ModelChunk:
         """The chunk's layer loop.  Returns ``(x, pending)``: on a head chunk the last FC2 output is still to be added (the
         final norm fuses that add); otherwise the add is done here and ``pending`` is None."""
         pending = None
-        for li in self.spec.layers:
+        n = len(self.spec.layers)
+        n_rc = n if self.recompute_num_layers < 0 else min(max(self.recompute_num_layers, 0), n)
+        for idx, li in enumerate(self.spec.layers):
             c = self._layer_fwd(f"layers.{li}.", x, pending, self.ds, S, cache.slot)
-            cache.layers.append(c)
             x, pending = c.h, c.m
+            if idx >= n - n_rc:
+                c = LayerCache(x=c.x, dropped=True)   # the layer's input is all the backward pass needs to run it again
+            cache.layers.append(c)
         if not self.spec.has_head and pending is not None:
             x, pending = self.ops.residual_add(x, pending, self.ds), None
         return x, pending
@@ -239,6 +245,9 @@ class ModelChunk:
     def _layers_bwd(self, g, cache: ChunkCache, S):
         done = self.on_grads_final
         for li, c in zip(reversed(self.spec.layers), reversed(cache.layers)):
+            if c.dropped:
+                # c.x already contains the previous layer's residual, so the layer runs from it with nothing pending
+                c = self._layer_fwd(f"layers.{li}.", c.x, None, self.ds, S, cache.slot)
             g = self._layer_bwd(f"layers.{li}.", c, g, self.ds, S)
             if done is not None:
                 done(f"layers.{li}.")
@@ -325,8 +334,10 @@ class ModelChunk:
     # ------------------------------------------------------------------
     def _mtp_fwd(self, batch, cache: ChunkCache, S):
         cfg, ops, st, tp = self.cfg, self.ops, self.store, self.tp
-        if tp.size > 1:
-            raise NotImplementedError("the MTP branch runs with tensor_parallel_size = 1")
+        # Under tensor / sequence parallelism the branch needs nothing of its own: the embedding and the extra layer go
+        # through the same TP-aware paths as the main stack, the two input norms and eagle_fc act row-wise on whatever rows
+        # this rank holds (eagle_fc is a replicated weight whose row-partial gradient is summed with the other replicated
+        # weights), and the shared LM head is the vocabulary-parallel one.
         m: dict = {}
         m["ids"] = batch["mtp_ids"]
         emb = self._embed(m["ids"])

@@ -66,12 +66,13 @@ class ParamStore:
         layers = {li for c in chunks for li in c.layers}
         has_emb = any(c.has_embedding for c in chunks)
         has_head = any(c.has_head for c in chunks)
-        if cfg.mtp_num_layers and pp > 1:
-            raise ValueError("the MTP head is supported with pipeline_parallel_size = 1 only")
+        # The last stage needs the embedding table too when the LM head is tied to it or when the MTP branch embeds its own
+        # input tokens; it then holds a second copy whose gradient is summed with the first stage's.
+        shares_embedding = cfg.tie_embeddings or bool(cfg.mtp_num_layers)
         self.specs: list[P.ParamSpec] = []
         for s in P.full_param_specs(cfg):
             if s.layer == -1:
-                keep = has_emb or (cfg.tie_embeddings and has_head)
+                keep = has_emb or (shares_embedding and has_head)
             elif s.layer == 10 ** 6:
                 keep = has_head
             else:
@@ -80,7 +81,7 @@ class ParamStore:
                 self.specs.append(s)
         # A tied LM head on a last stage that does not also hold the embedding is a second copy
         # of tok_embeddings.weight; its gradient is summed with the first stage's (embed group).
-        self.tied_copy = cfg.tie_embeddings and has_head and not has_emb
+        self.tied_copy = shares_embedding and has_head and not has_emb
         self.spec_by_name = {s.name: s for s in self.specs}
         self.shapes = {s.name: P.local_shape(s, cfg, tp, tp_rank) for s in self.specs}
 

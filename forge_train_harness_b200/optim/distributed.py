@@ -116,7 +116,7 @@ class DistributedOptimizer:
             for s in st.specs:
                 if s.kind == "qkv":
                     dist.all_reduce(st.g(s.name)[r0:r1], group=topo.kv_group)
-        if st.cfg.tie_embeddings and topo.pp > 1 and topo.embed_group is not None and \
+        if (st.cfg.tie_embeddings or st.cfg.mtp_num_layers) and topo.pp > 1 and topo.embed_group is not None and \
                 "tok_embeddings.weight" in st.grads and (topo.is_first_stage or topo.is_last_stage):
             dist.all_reduce(st.g("tok_embeddings.weight"), group=topo.embed_group)
 

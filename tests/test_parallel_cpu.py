@@ -87,6 +87,37 @@ def test_tp2_qk_norm_weights_stay_replicated(sp):
     assert (res[0][1] - 1.0).abs().max() > 1e-3  # the norm weights did move
 
 
+def _mtp_cfg(**par):
+    import dataclasses
+    cfg = base_cfg(steps=3, **par)
+    return dataclasses.replace(cfg, model=dataclasses.replace(cfg.model, tie_embeddings=False, mtp_num_layers=1, mtp_loss_weight=0.3))
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2_with_mtp_branch(sp):
+    """The Eagle / MTP branch under tensor (and sequence) parallelism: same losses as one process."""
+    cfg = _mtp_cfg(tensor_parallel_size=2, sequence_parallel=sp)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg), res[0])
+
+
+def test_pp2_with_mtp_branch_on_the_last_stage():
+    """Pipeline parallelism with MTP: the last stage holds its own copy of the (untied) embedding for the branch's input
+    tokens, and the two copies' gradients are summed, so the run matches one process."""
+    cfg = _mtp_cfg(pipeline_parallel_size=2, gbs=8)
+    res = run_ranks(2, _train, cfg)
+    check(single(cfg), res[0])
+
+
+@pytest.mark.parametrize("n", [1, 3, -1])
+def test_last_n_layers_recompute_is_exact(n):
+    """Layers whose activations are dropped and rebuilt in the backward pass give bitwise the same step."""
+    cfg = base_cfg(steps=3)
+    ref = single(cfg)
+    got = single(cfg.replace(train={"recompute_num_layers": n}))
+    assert ref == got
+
+
 def test_tp4_kv_replication_sp():
     cfg = base_cfg(tensor_parallel_size=4, sequence_parallel=True)
     res = run_ranks(4, _train, cfg)
