@@ -2,15 +2,23 @@
 
 Two on-disk formats:
 
-* ``megatron_dist`` (default) — Megatron-style directory layout: ``<root>/latest_checkpointed_iteration.txt``
-  and ``<root>/iter_<N:07d>/mp_rank_<tp:02d>[_<pp:03d>]/model_optim_rng.pt`` written by DP rank 0 of every
-  model-parallel rank, plus ``metadata.json`` with the parallel layout.  Tensors are stored per FQN as the
-  local TP shard (model weights in the compute dtype; optimizer ``master`` / ``exp_avg`` / ``exp_avg_sq`` in
-  fp32, assembled over the ZeRO-1 DP shards), and the shard <-> full index map is a pure function of
-  (model config, tp, rank), so a checkpoint saved at one TP x PP x DP layout loads at any other.  The file
-  also carries the step, RNG states, the LR-relevant step counter and the DATA CURSOR (the reference stores
-  no data position and replays batches on resume, train_loop.py:1489-1505, 1776-1783).  Publishing is atomic:
-  write into ``iter_<N>.tmp``, fsync, rename, then replace the tracker file.
+* ``megatron_dist`` (default) — Megatron-style directory layout with a DISTRIBUTED payload:
+
+      <root>/latest_checkpointed_iteration.txt
+      <root>/iter_<N:07d>/metadata.json
+      <root>/iter_<N:07d>/mp_rank_<tp:02d>[_<pp:03d>]/model_optim_rng.pt      written by DP rank 0 of the model-parallel rank
+      <root>/iter_<N:07d>/mp_rank_<tp:02d>[_<pp:03d>]/distrib_optim_dp<d:03d>.pt   written by EVERY DP rank (ZeRO-1 shard)
+      <root>/iter_<N:07d>/mp_rank_<tp:02d>[_<pp:03d>]/layout.json
+
+  ``model_optim_rng.pt`` holds the local TP shard of every weight under its FQN (compute dtype), the step, the optimizer step
+  counter and the data cursor.  ``distrib_optim_dp<d>.pt`` holds that DP rank's OWN slice of the fp32 master / exp_avg /
+  exp_avg_sq (nothing is gathered: a rank writes what it has), its slice table, its RNG states and its data cursor.
+  ``metadata.json`` records the parallel layout and, per model-parallel rank, the flat offset / size / local shape of every
+  tensor and the bucket table, so a loader at ANY other TP x PP x DP layout can work out which slices of which files hold the
+  rows it needs and read only those (files are opened memory-mapped).  Loading at the same layout reads one shard file per
+  rank.  Publishing is atomic: write into ``iter_<N>.tmp``, fsync, rename, then replace the tracker file.  The reference
+  stores no data position and replays batches on resume (train_loop.py:1489-1505, 1776-1783).
+  ``ckpt/export_megatron.py`` rewrites such a checkpoint under Megatron-LM state-dict names.
 * ``legacy`` — the reference engine's ``<root>/step_<N>/training_state.pt``: rank 0 ``torch.save`` of lists in
   parameter order ``{fp32_master, exp_avgs, exp_avg_sqs, state_steps, step, rng_*}`` (train_loop.py:1354-1406);
   load picks the newest ``*training_state.pt`` by mtime (train_loop.py:1409-1486).  TP = PP = 1 only.
@@ -29,8 +37,10 @@ import torch
 import torch.distributed as dist
 
 from ..models import params as P
+from ..optim.distributed import shard_ranges
 
 TRACKER = "latest_checkpointed_iteration.txt"
+STATE_KEYS = ("master", "exp_avg", "exp_avg_sq")
 
 
 def _barrier():
@@ -50,11 +60,12 @@ def _fsync_write(path: str, obj) -> None:
 
 
 def _per_param_optimizer_state(tr) -> dict:
+    """Full per-parameter optimizer state on every rank (gathers over DP): used by the legacy single-file codec only."""
     full = tr.opt.gather_full_state()
     out = {}
     for name, (o, n) in tr.store.offsets.items():
         shp = tr.store.shapes[name]
-        out[name] = {k: full[k][o:o + n].view(shp).cpu().clone() for k in ("master", "exp_avg", "exp_avg_sq")}
+        out[name] = {k: full[k][o:o + n].view(shp).cpu().clone() for k in STATE_KEYS}
     return out
 
 
@@ -62,7 +73,7 @@ def save(tr, root: str) -> str:
     fmt = tr.cfg.ckpt.format
     if fmt == "legacy":
         return _save_legacy(tr, root)
-    topo, step = tr.topo, tr.step
+    topo, step, opt, store = tr.topo, tr.step, tr.opt, tr.store
     final = os.path.join(root, f"iter_{step:07d}")
     tmp = final + ".tmp"
     if tr.rank == 0:
@@ -71,25 +82,37 @@ def save(tr, root: str) -> str:
             shutil.rmtree(tmp)
         os.makedirs(tmp)
     _barrier()
-    opt_state = _per_param_optimizer_state(tr)  # collective over the DP group
+    d = os.path.join(tmp, _mp_dir(topo.tp_rank, topo.pp_rank, topo.pp))
+    os.makedirs(d, exist_ok=True)
+    # every rank that owns optimizer state writes exactly that (a ZeRO-1 shard, or the whole state on DP rank 0 otherwise)
+    if opt.sharded or topo.dp_rank == 0:
+        _fsync_write(os.path.join(d, f"distrib_optim_dp{opt.dpr:03d}.pt"), {
+            "master": opt.master.detach().cpu(), "exp_avg": opt.m.detach().cpu(), "exp_avg_sq": opt.v.detach().cpu(),
+            "ranges": [list(r) for r in opt.my_ranges], "dp_rank": opt.dpr, "dp_world": opt.dpw,
+            "rng_state": tr.rng_state(), "data_state": tr.data_state(), "optimizer_step": opt.step_count})
     if topo.dp_rank == 0:
-        d = os.path.join(tmp, _mp_dir(topo.tp_rank, topo.pp_rank, topo.pp))
-        os.makedirs(d, exist_ok=True)
         _fsync_write(os.path.join(d, "model_optim_rng.pt"), {
-            "model": {k: v.detach().cpu().clone() for k, v in tr.store.params.items()},
-            "optimizer": opt_state,
-            "optimizer_step": tr.opt.step_count,
+            "model": {k: v.detach().cpu().clone() for k, v in store.params.items()},
+            "optimizer_step": opt.step_count,
             "iteration": step,
-            "rng_state": [tr.rng_state()],
             "data_state": tr.data_state(),
             "checkpoint_version": 3.0,
             "args": {k: dataclasses.asdict(getattr(tr.cfg, k)) for k in ("model", "optim", "parallel")},
         })
+        with open(os.path.join(d, "layout.json"), "w") as f:
+            json.dump({"tp_rank": topo.tp_rank, "pp_rank": topo.pp_rank, "numel": store.numel,
+                       "buckets": [[b.start, b.end] for b in store.buckets], "dp_shards": opt.dpw,
+                       "params": {n: [o, c, list(store.shapes[n])] for n, (o, c) in store.offsets.items()}}, f)
+            f.flush()
+            os.fsync(f.fileno())
     _barrier()
     if tr.rank == 0:
-        meta = {"format": "megatron_dist", "iteration": step, "tp": topo.tp, "pp": topo.pp, "dp": topo.dp,
-                "vpp": tr.cfg.parallel.virtual_pipeline_stages, "sharded_optimizer": tr.opt.sharded,
-                "model": dataclasses.asdict(tr.cfg.model), "dtype": tr.cfg.train.dtype}
+        mp = {}
+        for ld in sorted(glob.glob(os.path.join(tmp, "mp_rank_*", "layout.json"))):
+            mp[os.path.basename(os.path.dirname(ld))] = json.load(open(ld))
+        meta = {"format": "megatron_dist", "version": 2, "iteration": step, "tp": topo.tp, "pp": topo.pp, "dp": topo.dp,
+                "vpp": tr.cfg.parallel.virtual_pipeline_stages, "layer_split": list(tr.cfg.parallel.pipeline_layer_split),
+                "sharded_optimizer": opt.sharded, "model": dataclasses.asdict(tr.cfg.model), "dtype": tr.cfg.train.dtype, "mp": mp}
         with open(os.path.join(tmp, "metadata.json"), "w") as f:
             json.dump(meta, f, indent=1)
             f.flush()
@@ -146,59 +169,174 @@ def _resolve(path: str) -> tuple[str, str]:
     raise FileNotFoundError(f"no checkpoint under {path}")
 
 
+class ShardReader:
+    """Random access to the optimizer state of a ``megatron_dist`` checkpoint by (model-parallel rank, flat range).
+    Shard files are opened memory-mapped and kept open, so only the pages a caller touches are read."""
+
+    def __init__(self, concrete: str, meta: dict):
+        self.dir, self.meta, self._files = concrete, meta, {}
+        self.bytes_requested = 0
+
+    def _shard(self, mp_name: str, d: int) -> dict:
+        key = (mp_name, d)
+        if key not in self._files:
+            path = os.path.join(self.dir, mp_name, f"distrib_optim_dp{d:03d}.pt")
+            try:
+                self._files[key] = torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+            except (RuntimeError, ValueError):   # a file not written in the zip format cannot be mapped
+                self._files[key] = torch.load(path, map_location="cpu", weights_only=False)
+        return self._files[key]
+
+    def flat_range(self, mp_name: str, key: str, start: int, count: int) -> torch.Tensor:
+        """Elements ``[start, start + count)`` of the flat state ``key`` of one model-parallel rank, assembled from the DP
+        shards that own them."""
+        lay = self.meta["mp"][mp_name]
+        out = torch.empty(count, dtype=torch.float32)
+        dpw = int(lay["dp_shards"])
+        for d in range(dpw):
+            for (r0, r1, so) in shard_ranges(lay["buckets"], dpw, d):
+                lo, hi = max(r0, start), min(r1, start + count)
+                if hi > lo:
+                    out[lo - start: hi - start] = self._shard(mp_name, d)[key][so + lo - r0: so + hi - r0]
+                    self.bytes_requested += (hi - lo) * 4
+        return out
+
+    def mp_ranks(self):
+        return {name: (int(l["tp_rank"]), int(l["pp_rank"])) for name, l in self.meta["mp"].items()}
+
+
+def full_param_state(reader: ShardReader, cfg, name: str, spec, keys=STATE_KEYS) -> dict:
+    """``{key: FULL logical fp32 tensor}`` of one parameter, assembled from every old TP shard that holds part of it."""
+    old_tp = reader.meta["tp"]
+    full = {k: torch.zeros(spec.full_shape, dtype=torch.float32) for k in keys}
+    found = False
+    for mp_name, (tp_r, _pp_r) in reader.mp_ranks().items():
+        ent = reader.meta["mp"][mp_name]["params"].get(name)
+        if ent is None:
+            continue
+        found = True
+        o, n, shp = ent
+        dim, idx = P.shard_rows(spec, cfg, old_tp, tp_r)
+        for k in keys:
+            src = reader.flat_range(mp_name, k, o, n).view(shp)
+            if idx is None:
+                full[k].copy_(src)
+            else:
+                full[k].index_copy_(dim, idx, src)
+    if not found:
+        raise KeyError(f"{name} not found in checkpoint {reader.dir}")
+    return full
+
+
+def local_param_state(reader: ShardReader, cfg, name: str, spec, new_tp: int, new_rank: int, keys=STATE_KEYS) -> dict:
+    """``{key: fp32 tensor}`` of the rows (or columns) of one parameter that TP rank ``new_rank`` of a ``new_tp``-way layout
+    holds, read from whichever old shards have them: old ranks without any needed row are not opened for this tensor, and
+    for tensors sharded along dim 0 only the needed row runs are read (each row is one contiguous run of the flat shard)."""
+    old_tp = reader.meta["tp"]
+    dim_n, idx_n = P.shard_rows(spec, cfg, new_tp, new_rank)
+    shape = list(spec.full_shape)
+    if idx_n is not None:
+        shape[dim_n] = idx_n.numel()
+    out = {k: torch.zeros(shape, dtype=torch.float32) for k in keys}
+    found = False
+    filled = None
+    for mp_name, (tp_r, _pp_r) in sorted(reader.mp_ranks().items()):
+        ent = reader.meta["mp"][mp_name]["params"].get(name)
+        if ent is None:
+            continue
+        found = True
+        o, n, shp = ent
+        dim_o, idx_o = P.shard_rows(spec, cfg, old_tp, tp_r)
+        if idx_o is None and idx_n is None:           # replicated on both sides: any one copy
+            for k in keys:
+                out[k].copy_(reader.flat_range(mp_name, k, o, n).view(shp))
+            break
+        dim = dim_o if idx_o is not None else dim_n
+        extent = spec.full_shape[dim]
+        full_o = idx_o if idx_o is not None else torch.arange(extent)
+        full_n = idx_n if idx_n is not None else torch.arange(extent)
+        inv = torch.full((extent,), -1, dtype=torch.long)
+        inv[full_n] = torch.arange(full_n.numel())
+        pos = inv[full_o]                               # new local position of every old local row (-1: not needed)
+        if filled is None:
+            filled = torch.zeros(full_n.numel(), dtype=torch.bool)
+        need = (pos >= 0)
+        need[need.clone()] &= ~filled[pos[need]]
+        if not bool(need.any()):
+            continue
+        old_rows = torch.nonzero(need).reshape(-1)
+        new_rows = pos[old_rows]
+        filled[new_rows] = True
+        if dim == 0:
+            row_elems = n // shp[0]
+            runs, start = [], 0
+            rows = old_rows.tolist()
+            for i in range(1, len(rows) + 1):
+                if i == len(rows) or rows[i] != rows[i - 1] + 1:
+                    runs.append((rows[start], rows[i - 1] + 1, start))
+                    start = i
+            for k in keys:
+                flat_out = out[k].view(shape[0], -1)
+                for a, b, at in runs:
+                    src = reader.flat_range(mp_name, k, o + a * row_elems, (b - a) * row_elems).view(b - a, -1)
+                    flat_out.index_copy_(0, new_rows[at:at + (b - a)], src)
+        else:
+            for k in keys:
+                src = reader.flat_range(mp_name, k, o, n).view(shp)
+                out[k].index_copy_(dim, new_rows, src.index_select(dim, old_rows))
+    if not found:
+        raise KeyError(f"{name} not found in checkpoint {reader.dir}")
+    if filled is not None and not bool(filled.all()):
+        raise KeyError(f"{name}: the checkpoint's shards do not cover every row this layout needs")
+    return out
+
+
 def load(tr, path: str, weights_only: bool = False) -> int:
     fmt, concrete = _resolve(path)
     if fmt == "legacy":
         return _load_legacy(tr, concrete, weights_only)
     meta = json.load(open(os.path.join(concrete, "metadata.json")))
-    old_tp, old_pp = meta["tp"], meta["pp"]
-    files = {}
-    for d in sorted(glob.glob(os.path.join(concrete, "mp_rank_*"))):
-        parts = os.path.basename(d).split("_")
-        tp_r = int(parts[2])
-        pp_r = int(parts[3]) if len(parts) > 3 else 0
-        files[(tp_r, pp_r)] = os.path.join(d, "model_optim_rng.pt")
-    if len(files) != old_tp * old_pp:
-        raise FileNotFoundError(f"checkpoint {concrete} has {len(files)} model-parallel shards, expected {old_tp * old_pp}")
-    topo, store, cfg = tr.topo, tr.store, tr.cfg.model
-    same = (old_tp == topo.tp and old_pp == topo.pp and meta.get("vpp", 1) == tr.cfg.parallel.virtual_pipeline_stages)
-    common = None
+    if meta.get("version", 1) < 2:
+        raise ValueError(f"{concrete} was written by an older layout of this format (no per-rank optimizer shards)")
+    topo, store, cfg, opt = tr.topo, tr.store, tr.cfg.model, tr.opt
+    n_mp = len(meta["mp"])
+    if n_mp != meta["tp"] * meta["pp"]:
+        raise FileNotFoundError(f"checkpoint {concrete} has {n_mp} model-parallel shards, expected {meta['tp'] * meta['pp']}")
+    same = (meta["tp"] == topo.tp and meta["pp"] == topo.pp and meta.get("vpp", 1) == tr.cfg.parallel.virtual_pipeline_stages
+            and list(meta.get("layer_split", [])) == list(tr.cfg.parallel.pipeline_layer_split)
+            and int(meta["dp"] if meta["sharded_optimizer"] else 1) == opt.dpw and bool(meta["sharded_optimizer"]) == bool(opt.sharded))
+    my_mp = _mp_dir(topo.tp_rank, topo.pp_rank, topo.pp)
+    keys = ("master",) if weights_only else STATE_KEYS
+    own = None
     if same:
-        sd = torch.load(files[(topo.tp_rank, topo.pp_rank)], map_location="cpu", weights_only=False)
-        common = sd
-        shards = {name: {k: sd["optimizer"][name][k] for k in ("master", "exp_avg", "exp_avg_sq")} for name in store.params}
+        # one file per rank: this rank's own shard, exactly as it was written
+        own = torch.load(os.path.join(concrete, my_mp, f"distrib_optim_dp{opt.dpr:03d}.pt"), map_location="cpu", weights_only=False)
+        opt.master.copy_(own["master"])
+        if not weights_only:
+            opt.m.copy_(own["exp_avg"])
+            opt.v.copy_(own["exp_avg_sq"])
+            opt.step_count = int(own["optimizer_step"])
+        opt.sync_params_from_master()
+        common = {"iteration": meta["iteration"], "optimizer_step": own["optimizer_step"], "data_state": own.get("data_state")}
     else:
-        loaded = {k: torch.load(f, map_location="cpu", weights_only=False) for k, f in files.items()}
-        common = loaded[(0, 0)] if (0, 0) in loaded else next(iter(loaded.values()))
-        shards = {}
+        reader = ShardReader(concrete, meta)
         for name in store.params:
             spec = store.spec_by_name[name]
-            full = {k: torch.zeros(spec.full_shape, dtype=torch.float32) for k in ("master", "exp_avg", "exp_avg_sq")}
-            found = False
-            for (tp_r, pp_r), sd in loaded.items():
-                if name not in sd["optimizer"]:
-                    continue
-                found = True
-                dim, idx = P.shard_rows(spec, cfg, old_tp, tp_r)
-                for k in full:
-                    src = sd["optimizer"][name][k]
-                    if idx is None:
-                        full[k].copy_(src)
-                    else:
-                        full[k].index_copy_(dim, idx, src)
-            if not found:
-                raise KeyError(f"{name} not found in checkpoint {concrete}")
-            dim, idx = P.shard_rows(spec, cfg, topo.tp, topo.tp_rank)
-            shards[name] = {k: (v if idx is None else v.index_select(dim, idx)) for k, v in full.items()}
-    flat = {k: torch.zeros(store.numel, dtype=torch.float32, device=store.device) for k in ("master", "exp_avg", "exp_avg_sq")}
-    for name, (o, n) in store.offsets.items():
-        for k in flat:
-            flat[k][o:o + n].copy_(shards[name][k].reshape(-1))
-    tr.opt.scatter_full_state(flat, common["optimizer_step"], weights_only=weights_only)
+            local = local_param_state(reader, cfg, name, spec, topo.tp, topo.tp_rank, keys)
+            o, n = store.offsets[name]
+            for k in keys:
+                opt.set_flat_range(k, o, local[k].reshape(-1).to(opt.master.device))
+        any_mp = sorted(meta["mp"])[0]
+        first = reader._shard(any_mp, 0)
+        common = {"iteration": meta["iteration"], "optimizer_step": first["optimizer_step"], "data_state": first.get("data_state")}
+        if not weights_only:
+            opt.step_count = int(common["optimizer_step"])
+        opt.sync_params_from_master()
+        tr.last_load_bytes = reader.bytes_requested
     if not weights_only:
         tr.step = int(common["iteration"])
-        if same and common.get("rng_state"):
-            tr.set_rng_state(common["rng_state"][0])
+        if own is not None and own.get("rng_state"):
+            tr.set_rng_state(own["rng_state"])
         ds = common.get("data_state")
         if ds is not None:
             tr.source.load_state_dict(ds)

@@ -35,6 +35,18 @@ def _intersect(a0, a1, b0, b1):
     return (lo, hi) if hi > lo else None
 
 
+def shard_ranges(buckets, dp_world: int, dp_rank: int) -> list[tuple[int, int, int]]:
+    """``[(flat_start, flat_end, shard_offset)]``, one per bucket: the slice of the flat buffer DP rank ``dp_rank`` owns and where
+    it sits in that rank's shard.  ``buckets`` are ``(start, end)`` pairs (or objects with those attributes)."""
+    out = []
+    for b in buckets:
+        start, end = (b.start, b.end) if hasattr(b, "start") else (int(b[0]), int(b[1]))
+        lr_ = (end - start) // dp_world
+        s0 = start + dp_rank * lr_
+        out.append((s0, s0 + lr_, start // dp_world))
+    return out
+
+
 class DistributedOptimizer:
     def __init__(self, store: ParamStore, topo: Topology, optim_cfg, ops, *, sharded: bool,
                  sequence_parallel: bool = False, fused_backend=None):
@@ -52,11 +64,7 @@ class DistributedOptimizer:
         self.step_count = 0
         cfg = store.cfg
         # my flat ranges, one per bucket: (flat_start, flat_end, shard_off)
-        self.my_ranges = []
-        for b in store.buckets:
-            lr_ = (b.end - b.start) // self.dpw
-            s0 = b.start + self.dpr * lr_
-            self.my_ranges.append((s0, s0 + lr_, b.start // self.dpw))
+        self.my_ranges = shard_ranges(store.buckets, self.dpw, self.dpr)
         # Adam segments: param ∩ my range
         self.segs = []
         for spec in store.specs:
@@ -240,6 +248,16 @@ class DistributedOptimizer:
             self.v.copy_(sd["exp_avg_sq"])
             self.step_count = int(sd["step"])
         self.sync_params_from_master()
+
+    def set_flat_range(self, key: str, flat_start: int, values: torch.Tensor) -> None:
+        """Write ``values`` (fp32, 1-D) as elements ``[flat_start, flat_start + len)`` of the FLAT state ``key``
+        (``master`` | ``exp_avg`` | ``exp_avg_sq``); only the part this rank's shard owns is kept."""
+        t = {"master": self.master, "exp_avg": self.m, "exp_avg_sq": self.v}[key]
+        n = values.numel()
+        for (r0, r1, so) in self.my_ranges:
+            it = _intersect(flat_start, flat_start + n, r0, r1)
+            if it:
+                t[so + it[0] - r0: so + it[1] - r0].copy_(values[it[0] - flat_start: it[1] - flat_start])
 
     # full (unsharded) views for layout-independent checkpoints ---------------
     def gather_full_state(self) -> dict[str, torch.Tensor]:

@@ -1,4 +1,5 @@
 """Save -> resume equivalence (bitwise), legacy codec, resharding across TP/PP/DP layouts, crash tolerance."""
+import json
 import os
 
 import pytest
@@ -142,3 +143,54 @@ def test_megatron_binary_cursor_moves_between_dp_degrees(tmp_path):
     same = MegatronBinary(prefix, S, mbs, 1, 2, seed)
     same.load_state_dict(dict(st, epoch=1))        # same layout: any epoch restores directly
     assert same.epoch == 1 and same.pos == st["pos"]
+
+
+def _load_layout_stats(rank, world, cfg, path, n):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True)
+    ckpt.load(tr, path)
+    out = [float(tr.train_step()["loss"]) for _ in range(n)]
+    stats = (getattr(tr, "last_load_bytes", 0), int(tr.opt.master.numel()) * 4 * 3)
+    tr.close()
+    return out, stats
+
+
+def test_distributed_payload_reshards_tp2pp2dp2_to_tp4_and_dp4_and_exports(tmp_path):
+    """Every DP rank writes its own optimizer shard; another layout reads only the slices it needs (here: at most a few
+    times its own shard, not the whole checkpoint), continues with the same losses, and the exporter rewrites the
+    checkpoint under Megatron names at a chosen TP x PP."""
+    a = base_cfg(tensor_parallel_size=2, pipeline_parallel_size=2, sequence_parallel=True, use_distributed_optimizer=True, gbs=16,
+                 ddp_bucket_elems=20000)
+    full = run_ranks(8, _save_layout, a.replace(train={"num_steps": 5}), str(tmp_path / "full"), 5)[0]
+    first = run_ranks(8, _save_layout, a, str(tmp_path / "ck"), 3)[0]
+    it = tmp_path / "ck" / "iter_0000003"
+    shards = sorted(p.name for p in (it / "mp_rank_00_000").iterdir())
+    assert shards == ["distrib_optim_dp000.pt", "distrib_optim_dp001.pt", "layout.json", "model_optim_rng.pt"]
+    one = torch.load(it / "mp_rank_00_000" / "distrib_optim_dp001.pt", weights_only=False)
+    assert one["dp_rank"] == 1 and one["dp_world"] == 2 and "rng_state" in one and one["master"].dim() == 1
+    meta = json.load(open(it / "metadata.json"))
+    assert meta["version"] == 2 and set(meta["mp"]) == {"mp_rank_00_000", "mp_rank_01_000", "mp_rank_00_001", "mp_rank_01_001"}
+    total_bytes = sum(l["numel"] for l in meta["mp"].values()) * 4 * 3
+    b = base_cfg(tensor_parallel_size=4, sequence_parallel=True, gbs=16)
+    res = run_ranks(4, _load_layout_stats, b, str(tmp_path / "ck"), 2)
+    for x, y in zip(full, first + res[0][0]):
+        assert abs(x - y) / abs(x) < 2e-4
+    for _, (asked, own) in res:
+        assert 0 < asked < 0.6 * total_bytes      # a TP-4 rank needs its rows of every tensor, not the whole checkpoint
+    c = base_cfg(use_distributed_optimizer=True, gbs=16, ddp_bucket_elems=20000)
+    res4 = run_ranks(4, _load_layout_stats, c, str(tmp_path / "ck"), 2)
+    for x, y in zip(full, first + res4[0][0]):
+        assert abs(x - y) / abs(x) < 2e-4
+    # exporter: Megatron names, TP 2 x PP 2, shapes of the local shards
+    from forge_train_harness_b200.ckpt.export_megatron import export, megatron_name
+    out = export(str(tmp_path / "ck"), str(tmp_path / "mg"), tp=2, pp=2, impl="te", dtype="fp32")
+    sd = torch.load(os.path.join(out, "mp_rank_01_001", "model_optim_rng.pt"), weights_only=False)
+    m = a.model
+    names = set(sd["model"])
+    assert "decoder.final_layernorm.weight" in names and "output_layer.weight" in names and "embedding.word_embeddings.weight" not in names
+    assert sd["model"]["decoder.layers.0.self_attention.linear_qkv.weight"].shape == (m.qkv_dim // 2, m.hidden_size)
+    assert sd["model"]["decoder.layers.1.mlp.linear_fc1.weight"].shape == (2 * m.ffn_hidden_size // 2, m.hidden_size)
+    assert sd["model"]["decoder.layers.0.mlp.linear_fc2.weight"].shape == (m.hidden_size, m.ffn_hidden_size // 2)
+    assert sd["args"]["tensor_model_parallel_size"] == 2 and sd["iteration"] == 3
+    s0 = torch.load(os.path.join(out, "mp_rank_00_000", "model_optim_rng.pt"), weights_only=False)
+    assert "embedding.word_embeddings.weight" in s0["model"] and "decoder.layers.1.self_attention.linear_proj.weight" in s0["model"]
+    assert megatron_name("layers.3.ffn_norm.weight", 1, "local") == "decoder.layers.1.pre_mlp_layernorm.weight"
