@@ -173,12 +173,18 @@ def family_key(key: str) -> str:
     return k
 
 
-def diff_tensors(baseline: dict, candidate: dict, *, family: str, rel_tol: float, fit_scale: bool = False) -> dict:
+def diff_tensors(baseline: dict, candidate: dict, *, family: str, rel_tol: float, fit_scale: bool = False,
+                 max_tol: float | None = None, scales: dict | None = None) -> dict:
     """Tolerance-mode alignment of two tensor captures.  Keys are reduced to ``<family>.<fqn>`` (the first occurrence of a
-    key wins: step, rank, micro-batch and call index are dropped), tensors are flattened to rows, and for every key both
-    sides have, ``max |a - b| / rms(b)`` must stay below ``rel_tol``.  ``fit_scale`` first removes the best common scalar
-    per key (gradients w.r.t. a module output depend on where a stack applies its residual scale); the fitted scalars are
-    reported.  No overlap, or a shape mismatch, fails."""
+    key wins: step, rank, micro-batch and call index are dropped) and tensors are flattened.  For every key both sides have,
+    the relative L2 error ``||a - b|| / ||b||`` must stay below ``rel_tol`` and the largest element error, relative to the
+    reference's RMS, below ``max_tol`` (default ``25 x rel_tol``: a bf16 rounding of an entry several times the RMS is a
+    few percent of the RMS by itself, so the L2 figure is the tight one).  ``scales`` multiplies named candidate keys by a
+    known factor (a capture point that sits on the other side of a constant scale); ``fit_scale`` removes the best common
+    scalar per key instead (gradients w.r.t. a module output depend on where a stack applies its residual scale) and
+    reports it.  No overlap, or a size mismatch, fails."""
+    max_tol = 25.0 * rel_tol if max_tol is None else max_tol
+
     def reduce(d):
         out = {}
         for k, v in d.items():
@@ -195,18 +201,20 @@ def diff_tensors(baseline: dict, candidate: dict, *, family: str, rel_tol: float
             bad.append(k)
             rows[k] = {"error": f"sizes {tuple(c[k].shape)} vs {tuple(b[k].shape)}"}
             continue
-        scale = 1.0
+        scale = float((scales or {}).get(k, 1.0))
         if fit_scale:
             den = float((x * x).sum())
             scale = float((x * y).sum()) / den if den > 0 else 1.0
-        rms = float(y.pow(2).mean().sqrt()) or 1.0
-        err = float((x * scale - y).abs().max()) / rms
-        rows[k] = {"max_rel_err": err, "scale": scale}
-        worst = max(worst, err)
-        if not err <= rel_tol:
+        norm = float(y.pow(2).sum().sqrt()) or 1.0
+        rms = norm / max(y.numel(), 1) ** 0.5
+        d = x * scale - y
+        l2, mx = float(d.pow(2).sum().sqrt()) / norm, float(d.abs().max()) / (rms or 1.0)
+        rows[k] = {"rel_l2": l2, "max_rel_err": mx, "scale": scale}
+        worst = max(worst, l2)
+        if not (l2 <= rel_tol and mx <= max_tol):
             bad.append(k)
     return {"passed": bool(common) and not bad, "overlap": len(common), "mismatched": bad, "worst_rel_err": worst,
-            "rel_tol": rel_tol, "missing_in_candidate": sorted(set(b) - set(c)), "per_key": rows}
+            "rel_tol": rel_tol, "max_tol": max_tol, "missing_in_candidate": sorted(set(b) - set(c)), "per_key": rows}
 
 
 def diff_captures(baseline: dict, candidate: dict, *, prefix: str = "", require_baseline_complete: bool = False) -> dict:

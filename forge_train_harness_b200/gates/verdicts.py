@@ -122,10 +122,11 @@ def align(ref_dump: str, our_dump: str, family: str, backward: bool = False) -> 
     return r
 
 
-def align_tolerance(ref_file: str, our_file: str, family: str, rel_tol: float, fit_scale: bool = False) -> dict:
+def align_tolerance(ref_file: str, our_file: str, family: str, rel_tol: float, fit_scale: bool = False,
+                    scales: dict | None = None) -> dict:
     """forward-/backward-align against a stack whose kernels differ: both files are ``torch.save`` dicts of captured tensors
     (``baseline/ref_capture_bridge.py`` on the reference side, ``CaptureSession(mode="tensor")`` on this side); every key of
-    ``family`` (``fwd`` | ``bwd`` | ``grad`` | ``loss``) both sides have must agree to ``rel_tol`` of the reference's RMS."""
+    ``family`` (``fwd`` | ``bwd`` | ``grad`` | ``loss``) both sides have must agree to a relative L2 error of ``rel_tol`` (and 25 x that for the largest element, relative to the reference's RMS)."""
     import torch
     ours: dict = {}
     import glob
@@ -133,11 +134,12 @@ def align_tolerance(ref_file: str, our_file: str, family: str, rel_tol: float, f
     for fn in files:
         ours.update(torch.load(fn, map_location="cpu", weights_only=True))
     ref = torch.load(ref_file, map_location="cpu", weights_only=True)
-    r = cap.diff_tensors(ref, ours, family=family, rel_tol=rel_tol, fit_scale=fit_scale)
-    worst = sorted(((v.get("max_rel_err", float("inf")), k) for k, v in r["per_key"].items()), reverse=True)[:5]
+    r = cap.diff_tensors(ref, ours, family=family, rel_tol=rel_tol, fit_scale=fit_scale, scales=scales)
+    worst = sorted(((v.get("rel_l2", float("inf")), k) for k, v in r["per_key"].items()), reverse=True)[:5]
     return {"passed": r["passed"], "checks_total": r["overlap"], "within_tolerance": r["overlap"] - len(r["mismatched"]),
             "worst_rel_err": r["worst_rel_err"], "rel_tol": rel_tol, "mismatched": r["mismatched"][:20],
-            "worst_keys": [{"key": k, "max_rel_err": e} for e, k in worst], "family": family}
+            "worst_keys": [{"key": k, "rel_l2": e, "max_rel_err": r["per_key"][k].get("max_rel_err")} for e, k in worst],
+            "family": family}
 
 
 def resume(text: str, window: tuple[int, int], returncode: int | None = None) -> dict:

@@ -66,8 +66,10 @@ def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) ->
         r = {"passed": r["passed"], "checks_total": r["overlap"], "bitwise_match": r["overlap"] - len(r["mismatched"]),
              "hash_capture_level": gate.get("hash_capture_level", 2), "mismatched": r["mismatched"][:20]}
     elif kind == "align_tolerance":
+        sc = os.path.join(run_dir, "ours", "scales.json")   # known constant factors between the two sides' capture points
         r = V.align_tolerance(os.path.join(run_dir, "ours", "ref_capture.pt"), os.path.join(run_dir, "ours", "ours_capture.pt"),
-                              gate.get("family", "fwd"), gate.get("rel_tol", 3e-2), gate.get("fit_scale", False))
+                              gate.get("family", "fwd"), gate.get("rel_tol", 1e-2), gate.get("fit_scale", False),
+                              json.load(open(sc)) if os.path.isfile(sc) else None)
     elif kind == "op_long":
         from . import stage2
         r = stage2.op_long(gate["op"], os.path.join(ROOT_DIR, gate["config"]), int(gate.get("steps", 200)),

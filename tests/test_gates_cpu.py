@@ -249,3 +249,28 @@ def test_hf_stream_packer_is_deterministic_sharded_and_resumable(tmp_path, monke
         take(0, 1, 1)
     with pytest.raises(RuntimeError, match="modelbest_sdk"):
         build_modelbest("x")
+
+
+def test_tolerance_alignment_of_tensor_captures(tmp_path):
+    """forward-/backward-align in tolerance mode: relative L2 per key, known scales, fitted scales, missing overlap."""
+    import torch
+    from forge_train_harness_b200.gates.capture import CaptureSession, diff_tensors, family_key
+    assert family_key("step_3.rank0.mb1.fwd.layers.0.wqkv#0") == "fwd.layers.0.wqkv"
+    assert family_key("step_0.rank0.grad.layers.1.w2.weight.preallreduce") == "grad.layers.1.w2.weight"
+    assert family_key("step_0.rank0.grad.x.weight.postallreduce") == "grad.x.weight.postallreduce"
+    g = torch.Generator().manual_seed(0)
+    ref = {"fwd.a": torch.randn(64, 32, generator=g), "fwd.emb": torch.randn(16, 8, generator=g), "bwd.a": torch.randn(64, 32, generator=g)}
+    sess = CaptureSession(str(tmp_path / "ours.pt"), level=2, rank=0, mode="tensor")
+    sess.begin_step(0)
+    sess.module_hook("fwd", "a", (ref["fwd.a"] * (1 + 2e-3 * torch.randn(64, 32, generator=g))).to(torch.bfloat16))
+    sess.module_hook("fwd", "emb", ref["fwd.emb"] * 12.0)
+    sess.module_hook("bwd", "a", ref["bwd.a"] * 0.37)
+    sess.dump()
+    torch.save(ref, tmp_path / "ref.pt")
+    ok = V.align_tolerance(str(tmp_path / "ref.pt"), str(tmp_path / "ours.pt"), "fwd", 1e-2, scales={"fwd.emb": 1 / 12.0})
+    assert ok["passed"] and ok["checks_total"] == 2 and ok["worst_rel_err"] < 6e-3
+    assert not V.align_tolerance(str(tmp_path / "ref.pt"), str(tmp_path / "ours.pt"), "fwd", 1e-2)["passed"]   # the x12 shows
+    assert not V.align_tolerance(str(tmp_path / "ref.pt"), str(tmp_path / "ours.pt"), "bwd", 1e-2)["passed"]
+    fit = V.align_tolerance(str(tmp_path / "ref.pt"), str(tmp_path / "ours.pt"), "bwd", 1e-2, fit_scale=True)
+    assert fit["passed"] and fit["worst_rel_err"] < 1e-6
+    assert not diff_tensors(ref, {}, family="fwd", rel_tol=1.0)["passed"]                                        # no overlap
