@@ -139,8 +139,16 @@ class ParallelConfig:
     # even split leaves the last stage the slowest: e.g. (7, 6, 6, 5) for 24 layers on pp = 2 x 2 virtual stages
     # (Megatron: --decoder-first/last-pipeline-num-layers).
     pipeline_layer_split: tuple = ()
+    # "global": the clip norm is the L2 norm of the whole model's gradient (every model-parallel shard once), Megatron's rule.
+    # "tp_local": every TP rank clips by the norm of ITS OWN shards (replicated weights counted on every rank), which is what
+    # the hand-written DP x TP reference does (ref/reference/train_minicpm4_8b_tp.py:321) and what its dptp gate compares.
+    clip_norm_scope: str = "global"
 
     def __post_init__(self):
+        if self.clip_norm_scope not in ("global", "tp_local"):
+            raise ValueError("clip_norm_scope must be 'global' or 'tp_local'")
+        if self.clip_norm_scope == "tp_local" and self.pipeline_parallel_size > 1:
+            raise ValueError("clip_norm_scope = 'tp_local' mirrors a reference without pipeline parallelism")
         object.__setattr__(self, "pipeline_layer_split", tuple(int(x) for x in self.pipeline_layer_split))
         if self.fp8 not in ("off", "mxfp8"):
             raise ValueError("fp8 must be 'off' or 'mxfp8'")

@@ -96,7 +96,8 @@ class Trainer:
             from .parallel import fused_dp
             fused = fused_dp.try_create(self.store, topo, required=want_dp == "require")
         self.opt = DistributedOptimizer(self.store, topo, cfg.optim, self.ops, sharded=par.use_distributed_optimizer,
-                                        sequence_parallel=par.sequence_parallel, fused_backend=fused)
+                                        sequence_parallel=par.sequence_parallel, fused_backend=fused,
+                                        clip_norm_scope=par.clip_norm_scope)
         self.links = PipeLinks(topo)
         self.grad_accum = cfg.grad_accum(topo.dp)
         self.source = build_source(cfg.data, m, t.micro_batch_size, topo.dp_rank, topo.dp, t.seed)
@@ -108,6 +109,9 @@ class Trainer:
         self.peaks = load_peaks()
         self.flops_per_token = m.flops_per_token(self.with_mtp)
         self._graph = None
+        self._graph_last = None       # the last micro-batch of a step, with the DP bucket pulls forked off its backward
+        self._graph_last_stats = None
+        self._graph_last_buckets = 0
         self._graph_stats = None
         self._graph_failed = False
         self.graph_launches = 0  # sm_100a kernels recorded in the captured micro-batch graph
@@ -182,6 +186,37 @@ class Trainer:
             raise RuntimeError(f"step {self.step}: sm_100a kernel reported status {code} "
                                f"({STATUS_NAMES.get(code, 'unknown')}); the step's results are not valid")
 
+    def _fwd_bwd_overlapped(self, batch: dict):
+        """The last micro-batch of a step: every gradient bucket goes to the DP reduction as soon as the backward has passed
+        its parameters, so the collective (library path) or the peer-memory pulls (fused path) run under the rest of it."""
+        self.opt.begin_overlap()
+        self.chunks[0].on_grads_final = self.opt.grads_final
+        try:
+            stats = self._fwd_bwd(batch)
+        finally:
+            self.chunks[0].on_grads_final = None
+        if self.opt.fused is not None:
+            self.opt.fused.join_overlap()
+        return stats
+
+    def _capture_last_graph(self, batch: dict):
+        """Second graph, sharing the first one's memory pool (they never run at the same time).  The gradient buffer is
+        restored afterwards: the capture itself launches nothing, but the first replay must see this step's sums."""
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self._graph.pool()):
+                self._graph_last_stats = self._fwd_bwd_overlapped(batch)
+            self._graph_last_buckets = self.opt.fused.buckets_done
+            self.opt.fused.overlapped_total -= self._graph_last_buckets   # counted at replay
+            self.opt.fused.buckets_done = 0
+            self._graph_last = g
+        except Exception as e:  # keep training with the plain graph and the pulls after the backward
+            self._graph_last = None
+            self.cfg = self.cfg.replace(parallel={"overlap_grad_reduce": False})
+            if not self.quiet and self.rank == 0:
+                print(f"[warn] capture of the overlapped last micro-batch failed, pulling after the backward: {e}", file=sys.stderr, flush=True)
+            torch.cuda.synchronize()
+
     def _try_capture_graph(self, batch: dict):
         """Capture forward + loss + backward of ONE micro-batch (train_loop.py:1926-2125)."""
         try:
@@ -252,24 +287,32 @@ class Trainer:
             if self.capture is not None:
                 self.capture.begin_microbatch(mb)
             batch = self.stager.stage(self.prefetch.get())
+            last = mb == self.grad_accum - 1
+            overlap = last and self.cfg.parallel.overlap_grad_reduce and self.opt.overlap_eligible()
             if self._use_graph():
                 if self._graph is None:
                     self._try_capture_graph(batch)
                 if self._graph is not None:
+                    if overlap and self.opt.fused is not None:
+                        # the last micro-batch has its own graph: same kernels, plus the bucket pulls on a forked stream
+                        if self._graph_last is None:
+                            self._capture_last_graph(batch)
+                        if self._graph_last is not None:
+                            self.opt.begin_overlap()
+                            self._graph_last.replay()
+                            self.graph_replays += 1
+                            self.stats += self._graph_last_stats
+                            self.opt.fused.buckets_done = self._graph_last_buckets
+                            self.opt.fused.overlapped_total += self._graph_last_buckets
+                            continue
                     self._graph.replay()
                     self.graph_replays += 1
                     self.stats += self._graph_stats
                     continue
-            last = mb == self.grad_accum - 1
-            if last and self.cfg.parallel.overlap_grad_reduce and self.opt.overlap_eligible():
+            if overlap:
                 # eager last micro-batch: each gradient bucket is handed to the DP reduction as soon as the backward has
                 # passed its parameters, so the collective runs under the rest of the backward
-                self.opt.begin_overlap()
-                self.chunks[0].on_grads_final = self.opt.grads_final
-                try:
-                    self.stats += self._fwd_bwd(batch)
-                finally:
-                    self.chunks[0].on_grads_final = None
+                self.stats += self._fwd_bwd_overlapped(batch)
                 continue
             self.stats += self._fwd_bwd(batch)
 
@@ -285,10 +328,24 @@ class Trainer:
             rows //= topo.tp
         shape = (rows, m.hidden_size)
         caches = {}
-        for kind, v, i in sched:
+
+        def needs_recv(kind, v):
+            ch = self.chunks[v]
+            return (kind == "F" and not ch.spec.has_embedding) or (kind == "B" and not ch.spec.has_head)
+
+        def post(k):
+            kind, v, _ = sched[k]
+            if needs_recv(kind, v):
+                return (self.links.post_recv_act if kind == "F" else self.links.post_recv_grad)(shape, self.dtype, self.device)
+            return None
+        # Receives are posted one action ahead.  On gloo (CPU) a posted receive is matched by peer sends in posting order
+        # exactly as on NCCL, so the same code runs on both.
+        posted = post(0) if sched else None
+        for k, (kind, v, i) in enumerate(sched):
+            nxt = post(k + 1) if k + 1 < len(sched) else None
             ch = self.chunks[v]
             if kind == "F":
-                x_in = None if ch.spec.has_embedding else self.links.recv_act(shape, self.dtype, self.device)
+                x_in = self.links.wait_recv(posted) if posted is not None else None
                 out, cache = ch.forward(batches[i], x_in)
                 caches[(v, i)] = cache
                 if ch.spec.has_head:
@@ -296,10 +353,11 @@ class Trainer:
                 else:
                     self.links.send_act(out)
             else:
-                g_out = None if ch.spec.has_head else self.links.recv_grad(shape, self.dtype, self.device)
+                g_out = self.links.wait_recv(posted) if posted is not None else None
                 g_in = ch.run_backward(batches[i], caches.pop((v, i)), g_out)
                 if g_in is not None:
                     self.links.send_grad(g_in)
+            posted = nxt
         self.links.drain()
 
     # ------------------------------------------------------------------
@@ -353,7 +411,9 @@ class Trainer:
         """Which implementation of each communication / launch path this trainer runs (reported by the benchmark and the
         training log, so that a fallback to the library collectives is never silent)."""
         return {"ops": self.ops.name, "fused_dp": self.opt.fused is not None, "fused_tp": self.tpc.fused is not None,
-                "cuda_graph": self._graph is not None or self._layer_graphs, "tp": self.topo.tp, "pp": self.topo.pp, "dp": self.topo.dp}
+                "cuda_graph": self._graph is not None or self._layer_graphs, "tp": self.topo.tp, "pp": self.topo.pp, "dp": self.topo.dp,
+                "dp_buckets_overlapped_with_backward": getattr(self.opt.fused, "overlapped_total", 0) if self.opt.fused is not None
+                else getattr(self.opt, "overlapped_buckets", 0), "dp_buckets": len(self.store.buckets)}
 
     def weights_changed(self):
         """Tell op tables that keep derived copies of the weights (the MXFP8 quantised ones) that the bf16 parameters moved."""

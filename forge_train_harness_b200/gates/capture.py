@@ -39,7 +39,11 @@ def hash_tensor(t: torch.Tensor) -> dict:
 
 
 class StagingRing:
-    """Fixed pinned-memory ring + copy stream: ``stage(t)`` returns a CPU view valid until the slot is reused."""
+    """Fixed pinned-memory ring + copy stream.  ``stage(t)`` returns a CPU view valid until the slot is reused (it waits for
+    the copy).  ``submit(key, t, sink)`` is the asynchronous form the capture session uses: the device -> host copy is
+    enqueued on the copy stream and a WORKER THREAD waits for it, hashes the bytes and stores the record, so the training
+    thread never blocks on a hash (blake2b runs at ~1 GB/s per core, which is what made level-2 capture cost most of a
+    step when it ran inline); the training thread only waits when every slot of the ring is still being hashed."""
 
     def __init__(self, nbytes: int = 256 << 20, slots: int = 4, device=None):
         self.cuda = torch.cuda.is_available() and device is not None and torch.device(device).type == "cuda"
@@ -48,6 +52,60 @@ class StagingRing:
         self.events = [None] * slots
         self.turn = 0
         self.stream = torch.cuda.Stream() if self.cuda else None
+        import queue
+        import threading
+        self._free = threading.Semaphore(slots)
+        self._q: "queue.Queue" = queue.Queue()
+        self._err = None
+        self._worker = threading.Thread(target=self._run, daemon=True)
+        self._worker.start()
+
+    def _run(self):
+        while True:
+            item = self._q.get()
+            if item is None:
+                self._q.task_done()
+                return
+            key, view, ev, sink, slot_held = item
+            try:
+                if ev is not None:
+                    ev.synchronize()
+                sink[key] = hash_tensor(view)
+            except BaseException as e:  # surfaced by flush()
+                self._err = e
+            finally:
+                if slot_held:
+                    self._free.release()
+                self._q.task_done()
+
+    def submit(self, key: str, t: torch.Tensor, sink: dict) -> None:
+        """Record ``hash_tensor(t)`` under ``key`` in ``sink`` without blocking on the copy or the hash."""
+        nb = t.numel() * t.element_size()
+        if not self.cuda or t.device.type != "cuda" or nb > self.bufs[0].numel():
+            host = t.detach().to("cpu", copy=True)   # CPU tensors (and oversized ones) are snapshotted, then hashed off-thread
+            self._q.put((key, host, None, sink, False))
+            return
+        self._free.acquire()                          # a slot whose previous content has been hashed
+        k = self.turn
+        self.turn = (self.turn + 1) % self.slots
+        dst = self.bufs[k][:nb].view(t.dtype).view(t.shape)
+        # a device-side snapshot first (an HBM copy on the training stream): several captured tensors are later updated in
+        # place (logits become their gradient, RoPE rotates QKV), and the PCIe copy below runs behind the training stream
+        snap = t.detach().clone()
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            dst.copy_(snap, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        snap.record_stream(self.stream)
+        self._q.put((key, dst, ev, sink, True))
+
+    def flush(self) -> None:
+        """Wait until every submitted tensor has been hashed; re-raises a worker failure."""
+        self._q.join()
+        if self._err is not None:
+            err, self._err = self._err, None
+            raise err
 
     def stage(self, t: torch.Tensor) -> torch.Tensor:
         if not self.cuda or t.device.type != "cuda":
@@ -99,7 +157,10 @@ class CaptureSession:
         if self.mode == "tensor":
             self.records[key] = t.detach().to("cpu", copy=True)
             return
-        self.records[key] = hash_tensor(self.ring.stage(t) if self.ring else t)
+        if self.ring is not None:
+            self.ring.submit(key, t, self.records)   # hashed by the ring's worker thread; dump() waits for it
+        else:
+            self.records[key] = hash_tensor(t)
 
     # -- capture points ---------------------------------------------------------
     def module_hook(self, kind: str, fqn: str, t: torch.Tensor):
@@ -130,6 +191,8 @@ class CaptureSession:
 
     # -- output -----------------------------------------------------------------
     def dump(self):
+        if self.ring is not None:
+            self.ring.flush()
         if self.level < 1 or not self.out:
             return
         path = f"{self.out}.rank{self.rank}"

@@ -87,6 +87,48 @@ def product_env(prod: dict, port_allocator=None) -> list[str]:
     return lines
 
 
+def load_axes(root: str) -> dict:
+    """``{"model": {name: table}, "optim": {...}, "data": {...}}`` from ``<root>/{model,optim,data}/<name>.toml`` — the axis
+    directories a gate picks one file of each from (harness/config_runtime.py:191-234 validates the same three axes)."""
+    import os
+    out = {}
+    for axis in ("model", "optim", "data"):
+        d = os.path.join(root, axis)
+        out[axis] = {}
+        if not os.path.isdir(d):
+            continue
+        for fn in sorted(os.listdir(d)):
+            if fn.endswith(".toml"):
+                doc = load_toml(os.path.join(d, fn))
+                if axis not in doc:
+                    raise ValueError(f"{os.path.join(d, fn)} has no [{axis}] table")
+                out[axis][fn[:-5]] = doc[axis]
+    return out
+
+
+RUNTIME = "<runtime>"
+
+
+def resolve_deploy(product: dict, runtime_values: dict) -> dict:
+    """Freeze-time fill of the ``<runtime>`` sentinels of a rendered product (tools/resolve_deploy.py): values only the
+    execution host knows (data paths, checkpoint roots, ports).  Every sentinel must get a value; an unknown key in
+    ``runtime_values`` is an error too, so a typo cannot silently leave a sentinel behind."""
+    out = {t: dict(product.get(t, {})) for t in ("cli", "env")}
+    used = set()
+    for t in out:
+        for k, v in out[t].items():
+            if v == RUNTIME:
+                key = k if k in runtime_values else k.lower() if k.lower() in runtime_values else k.upper()
+                if key not in runtime_values:
+                    raise KeyError(f"product key {k!r} is <runtime> and no value was given for it")
+                out[t][k] = runtime_values[key]
+                used.add(key)
+    extra = set(runtime_values) - used
+    if extra:
+        raise KeyError(f"runtime values {sorted(extra)} match no <runtime> sentinel of the product")
+    return out
+
+
 def load_toml(path: str) -> dict:
     with open(path, "rb") as f:
         return tomllib.load(f)

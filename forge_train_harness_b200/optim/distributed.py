@@ -49,13 +49,14 @@ def shard_ranges(buckets, dp_world: int, dp_rank: int) -> list[tuple[int, int, i
 
 class DistributedOptimizer:
     def __init__(self, store: ParamStore, topo: Topology, optim_cfg, ops, *, sharded: bool,
-                 sequence_parallel: bool = False, fused_backend=None):
+                 sequence_parallel: bool = False, fused_backend=None, clip_norm_scope: str = "global"):
         self.store, self.topo, self.oc, self.ops = store, topo, optim_cfg, ops
         self.sharded = bool(sharded and topo.dp > 1)
         self.dpw = topo.dp if self.sharded else 1
         self.dpr = topo.dp_rank if self.sharded else 0
         self.sp = sequence_parallel and topo.tp > 1
         self.fused = fused_backend
+        self.tp_local_norm = clip_norm_scope == "tp_local"
         dev = store.device
         n_shard = store.numel // self.dpw
         self.master = torch.zeros(n_shard, dtype=torch.float32, device=dev)
@@ -131,15 +132,18 @@ class DistributedOptimizer:
     # -- bucket-by-bucket overlap of the DP reduction with the last micro-batch's backward -------------------------
     def overlap_eligible(self) -> bool:
         """Buckets can be reduced while the backward still runs when nothing has to be summed over model-parallel ranks
-        first (no TP / PP) and the library path is in use (the peer-memory path reduces after its own flag barrier)."""
+        first (no TP / PP); both the library path (asynchronous collectives) and the peer-memory path (side-stream pulls
+        behind a flag barrier) do it."""
         t = self.topo
-        return t.dp > 1 and t.tp == 1 and t.pp == 1 and self.fused is None
+        return t.dp > 1 and t.tp == 1 and t.pp == 1
 
     def begin_overlap(self) -> None:
         self._done_names: set = set()
         self._launched = 0
         self._works: list = []
         self.overlapped_buckets = 0
+        if self.fused is not None:
+            self.fused.begin_overlap()
 
     def grads_final(self, prefix: str) -> None:
         """Called by the backward when every parameter whose name starts with ``prefix`` has its final gradient of this
@@ -150,6 +154,11 @@ class DistributedOptimizer:
         while self._launched < len(st.buckets) and all(n in self._done_names for n in st.buckets[self._launched].names):
             b = st.buckets[self._launched]
             buf = st.flat_grad[b.start:b.end]
+            if self.fused is not None:
+                self.fused.bucket_ready(self, self._launched)
+                self._launched += 1
+                self.overlapped_buckets += 1
+                continue
             if self.sharded and buf.device.type != "cpu":
                 r0, r1, _ = self.my_ranges[self._launched]
                 w = dist.reduce_scatter_tensor(st.flat_grad[r0:r1], buf, group=topo.dp_group, async_op=True)
@@ -197,7 +206,7 @@ class DistributedOptimizer:
         tot = torch.zeros((), dtype=torch.float32, device=st.device)
         for (r0, r1, _) in self.my_ranges:
             tot = tot + self.ops.sumsq(st.flat_grad[r0:r1])
-            for (d0, d1) in self.dup_ranges:
+            for (d0, d1) in ([] if self.tp_local_norm else self.dup_ranges):
                 it = _intersect(d0, d1, r0, r1)
                 if it:
                     tot = tot - self.ops.sumsq(st.flat_grad[it[0]:it[1]])
@@ -211,11 +220,18 @@ class DistributedOptimizer:
         self.step_count += 1
         self.reduce_model_parallel_grads()
         if self.fused is not None:
+            self._works, self._launched = [], 0
             sq = self.fused.reduce_scatter_sumsq(self)
         else:
             self._reduce_grads()
             sq = self._local_sumsq()
-        if topo.world_size > 1:
+        if self.tp_local_norm:
+            # this TP rank's own shards only (replicated weights included): sum the DP slices of a ZeRO-1 shard, nothing else
+            if self.sharded:
+                sq = sq.reshape(1).clone()
+                dist.all_reduce(sq, group=topo.dp_group)
+                sq = sq[0]
+        elif topo.world_size > 1:
             sq = sq.reshape(1).clone()
             dist.all_reduce(sq)
             sq = sq[0]

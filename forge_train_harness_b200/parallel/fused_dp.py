@@ -11,9 +11,11 @@ memory) with two kernels over symmetric memory:
    separate collective at all and the next forward's first GEMM simply finds its weights in place.
 
 Ordering between ranks is three flag barriers per step (gradients complete -> pull; pulls done -> buffers reusable;
-pushes done -> parameters readable), each a bounded device-side wait.  With gradient accumulation the collectives run once
-per step after the last micro-batch; they are not interleaved with the backward (at 16 micro-batches per step the whole
-exchange is < 0.5 % of the step).  Roofline: bytes over NVLink per rank = (dp-1)/dp * 4P (pull) + (dp-1)/dp * 2P (push).
+pushes done -> parameters readable), each a bounded device-side wait.  With gradient accumulation the pulls belong to the
+LAST micro-batch of the step, and they overlap its backward bucket by bucket: the flat gradient buffer is laid out in
+backward order, so as soon as the backward has passed every parameter of a bucket, ``bucket_ready`` forks a side stream
+that waits (flag barrier with a device-numbered epoch, so the fork can live inside a captured CUDA graph) until every rank
+has finished that bucket and then pulls this rank's slice of it, while the main stream goes on with the next layers.  Roofline: bytes over NVLink per rank = (dp-1)/dp * 4P (pull) + (dp-1)/dp * 2P (push).
 """
 from __future__ import annotations
 
@@ -38,17 +40,44 @@ class FusedDP:
         self.sumsq = torch.zeros((), dtype=torch.float32, device=store.device)
         self._ops = Sm100Ops
         self._table = None
+        self.side = torch.cuda.Stream(device=store.device)
+        self.buckets_done = 0      # buckets of this step already pulled while the backward was still running
+        self.overlapped_total = 0  # over the whole run (reported by tests / the benchmark)
+
+    # -- bucket-by-bucket overlap with the last micro-batch's backward -------------------------------------------------
+    def begin_overlap(self) -> None:
+        self.sumsq.zero_()
+        self.buckets_done = 0
+
+    def bucket_ready(self, opt, idx: int) -> None:
+        """Every gradient of bucket ``idx`` is final on THIS rank (main stream order).  On the side stream: wait until that
+        holds on every rank, then pull and sum this rank's slice of the bucket (plus its share of the clip norm)."""
+        from ..ops.cuda_ops import _C
+        self.side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.side):
+            self.barrier(3, device_epoch=True)
+            r0, r1, _ = opt.my_ranges[idx]
+            _C.dp_reduce_scatter(self.grad.ptrs, self.grad.mc_ptr, r0, r1 - r0, self.grad.rank, self.sumsq)
+        self.buckets_done += 1
+        self.overlapped_total += 1
+
+    def join_overlap(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.side)
 
     def reduce_scatter_sumsq(self, opt) -> torch.Tensor:
         from ..ops.cuda_ops import _C
-        self.barrier(0)  # every rank's gradients are complete
-        self.sumsq.zero_()
-        for (r0, r1, _) in opt.my_ranges:
-            _C.dp_reduce_scatter(self.grad.ptrs, self.grad.mc_ptr, r0, r1 - r0, self.grad.rank, self.sumsq)
+        rest = list(opt.my_ranges)[self.buckets_done:]
+        if self.buckets_done == 0:
+            self.sumsq.zero_()
+        if rest:
+            self.barrier(0)  # every rank's gradients are complete
+            for (r0, r1, _) in rest:
+                _C.dp_reduce_scatter(self.grad.ptrs, self.grad.mc_ptr, r0, r1 - r0, self.grad.rank, self.sumsq)
+        self.buckets_done = 0
         self.barrier(1)  # every pull is done: gradient buffers may be overwritten again
         sq = self.sumsq.clone()
         for (r0, r1, _) in opt.my_ranges:  # gradients that are replicas of another model-parallel rank's count once
-            for (d0, d1) in opt.dup_ranges:
+            for (d0, d1) in ([] if getattr(opt, "tp_local_norm", False) else opt.dup_ranges):
                 lo, hi = max(d0, r0), min(d1, r1)
                 if hi > lo:
                     sq = sq - opt.ops.sumsq(self.store.flat_grad[lo:hi])

@@ -9,7 +9,8 @@ then one-forward-one-backward, then the remaining backwards.
 
 Because the backward is hand-derived, a schedule is just a list of ``("F"|"B", chunk, microbatch)``.
 
-Transport: activations and gradients travel by ``isend`` / ``irecv`` over NCCL (gloo on CPU).  Every
+Transport: activations and gradients travel by ``isend`` / ``irecv`` over NCCL (gloo on CPU); receives are posted one
+schedule action ahead of their consumer and waited for on the stream, so the transfer overlaps the current action's compute.  Every
 directed edge of the pipeline ring — activations p -> p+1 and gradients p+1 -> p — gets its OWN
 two-rank process group, hence its own communicator and stream: a send that waits for its receiver
 blocks only that edge, never the opposite direction, so the schedule needs no hand-paired
@@ -78,18 +79,31 @@ class PipeLinks:
     def send_act(self, t):
         self._pending.append((dist.isend(t, self.topo.next_stage_rank, group=self.fwd_to_next), t))
 
-    def recv_act(self, shape, dtype, device):
+    def post_recv_act(self, shape, dtype, device):
+        """Post the receive now, wait later (``wait_recv``): posting it one schedule action ahead lets the transfer run
+        under the current action's kernels instead of starting when its consumer is about to be enqueued."""
         t = torch.empty(shape, dtype=dtype, device=device)
-        dist.irecv(t, self.topo.prev_stage_rank, group=self.fwd_from_prev).wait()
+        return dist.irecv(t, self.topo.prev_stage_rank, group=self.fwd_from_prev), t
+
+    def post_recv_grad(self, shape, dtype, device):
+        t = torch.empty(shape, dtype=dtype, device=device)
+        return dist.irecv(t, self.topo.next_stage_rank, group=self.bwd_from_next), t
+
+    @staticmethod
+    def wait_recv(posted):
+        """With NCCL this makes the CURRENT STREAM wait for the transfer (the host does not block); with gloo it blocks."""
+        work, t = posted
+        work.wait()
         return t
+
+    def recv_act(self, shape, dtype, device):
+        return self.wait_recv(self.post_recv_act(shape, dtype, device))
 
     def send_grad(self, t):
         self._pending.append((dist.isend(t, self.topo.prev_stage_rank, group=self.bwd_to_prev), t))
 
     def recv_grad(self, shape, dtype, device):
-        t = torch.empty(shape, dtype=dtype, device=device)
-        dist.irecv(t, self.topo.next_stage_rank, group=self.bwd_from_next).wait()
-        return t
+        return self.wait_recv(self.post_recv_grad(shape, dtype, device))
 
     def drain(self):
         for w, _ in self._pending:

@@ -48,9 +48,10 @@ class PeerBarrier:
         self.epoch_dev = torch.zeros(lanes, dtype=torch.int32, device=device)
         self.device_epochs = False
 
-    def __call__(self, lane: int = 0):
+    def __call__(self, lane: int = 0, device_epoch: bool | None = None):
+        """``device_epoch`` overrides the object's default for this call; a lane must stick to one numbering."""
         from ..ops.cuda_ops import _C
-        if self.device_epochs:
+        if self.device_epochs if device_epoch is None else device_epoch:
             _C.peer_barrier(self.buf.ptrs, self.buf.rank, 0, lane, self.limit_s, self.epoch_dev)
             return
         self.epoch[lane] += 1

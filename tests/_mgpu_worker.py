@@ -16,6 +16,7 @@ def main():
     mode = sys.argv[1]
     init_distributed()
     par = {"dp_zero": dict(use_distributed_optimizer=True, ddp_bucket_elems=300_000),
+           "dp_zero_late": dict(use_distributed_optimizer=True, ddp_bucket_elems=300_000, overlap_grad_reduce=False),
            "dp_plain": dict(use_distributed_optimizer=False),
            "tp_sp": dict(tensor_parallel_size=int(os.environ.get("WORLD_SIZE", "1")), sequence_parallel=True),
            "pp": dict(pipeline_parallel_size=2),

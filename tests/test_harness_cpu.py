@@ -253,3 +253,29 @@ def test_wsd_sft_suite_with_host_side_kills(tmp_path, capsys):
     assert all(p["passed"] and p["complete"] and p["max_abs_loss_diff"] == 0.0 for p in res["metrics"]["phases"].values())
     log = open(os.path.join(res["details"]["run_dir"], "ours", "ours.log")).read()
     assert log.count("[PHASE]") >= 6          # three phases, re-announced after each of the three kills
+
+
+def test_axis_directories_gate_sources_and_resolve_deploy():
+    """Every gate source renders against every model x optim axis file; <runtime> sentinels are filled at freeze time."""
+    axes = render.load_axes(os.path.join(ROOT, "configs", "axes"))
+    assert {"minicpm4_0.5b", "minicpm4_8b", "tiny"} <= set(axes["model"]) and "pretrain_cosine" in axes["optim"]
+    reg = render.load_toml(os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    gdir = os.path.join(ROOT, "configs", "eval", "gate_config")
+    gates = sorted(f for f in os.listdir(gdir) if f.endswith(".toml"))
+    assert len(gates) >= 7
+    for g in gates:
+        for mname, model in axes["model"].items():
+            prods = render.render_gate(render.load_toml(os.path.join(gdir, g)), model, axes["optim"]["pretrain_cosine"], reg["env"])
+            ours = prods["ours"]
+            assert ours["cli"]["num_layers"] >= 1 and ours["env"]["NUM_PROCS"] == ours["cli"].get("world_size", 1), (g, mname)
+            assert ours["cli"]["grad_accum_steps"] * ours["cli"]["micro_batch_size"] * ours["env"]["NUM_PROCS"] == ours["cli"]["global_batch_size"]
+    dptp = render.render_gate(render.load_toml(os.path.join(gdir, "dptp.toml")), axes["model"]["minicpm4_8b"],
+                              axes["optim"]["pretrain_cosine"], reg["env"])["ours"]
+    assert dptp["cli"]["num_layers"] == 4 and dptp["cli"]["tensor_parallel_size"] == 2 and dptp["cli"]["lr_warmup_iters"] == 0
+    prod = {"cli": dict(dptp["cli"], data_path=render.RUNTIME), "env": {"MASTER_PORT": render.RUNTIME}}
+    frozen = render.resolve_deploy(prod, {"data_path": "/data/corpus", "MASTER_PORT": 29511})
+    assert frozen["cli"]["data_path"] == "/data/corpus" and frozen["env"]["MASTER_PORT"] == 29511
+    with pytest.raises(KeyError, match="no value was given"):
+        render.resolve_deploy(prod, {"data_path": "/data/corpus"})
+    with pytest.raises(KeyError, match="match no <runtime>"):
+        render.resolve_deploy(prod, {"data_path": "x", "MASTER_PORT": 1, "typo": 2})

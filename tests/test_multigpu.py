@@ -34,6 +34,20 @@ needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs"
 
 
 @needs2
+def test_fused_dp_bucket_pulls_overlap_the_backward_eager_and_in_the_graph():
+    """The peer-memory reduce-scatter runs bucket by bucket behind the last micro-batch's backward (side stream, device-
+    numbered flag barrier), eagerly and inside the captured graph; same numbers as pulling after the backward."""
+    late = run("dp_zero_late", 2)
+    eager = run("dp_zero", 2)
+    graph = run("dp_zero:graph", 2)
+    assert late["paths"]["dp_buckets_overlapped_with_backward"] == 0
+    assert eager["paths"]["dp_buckets_overlapped_with_backward"] > 0 and eager["paths"]["dp_buckets"] > 2
+    assert graph["paths"]["dp_buckets_overlapped_with_backward"] > 0 and graph["paths"]["cuda_graph"]
+    close(late, eager, 1e-3)
+    close(late, graph, 1e-3)
+
+
+@needs2
 def test_fused_dp_matches_nccl_and_single_gpu():
     single = run("single", 1)
     nccl = run("dp_zero", 2, {"FORGE_FUSED_DP": "0"})
