@@ -34,7 +34,8 @@ extern "C" {
 // Sharing: all calls on a device use the same scratch array and the array keeps whatever the last call left in it.  The
 // kernels overwrite every element they later read, so no clearing is needed between calls; but two calls that can run at
 // the same time on one GPU (different streams without an ordering between them, or two host threads) race on it.  Order
-// them on one stream or with events.
+// them on one stream or with events.  (The one-time address look-up itself may be done by two host threads at once on
+// their first calls: both store the same value into the per-device slot, an unsynchronised but idempotent write.)
 //
 // Returns 0 on success; on failure a negative code, and if `err` is not NULL a zero-terminated message of at most
 // `err_len` bytes.

@@ -18,7 +18,10 @@ BANNED = ["megatron", "deepspeed", "torch.nn.Module", "torch.optim", "torch.auto
 PROXY = ["baseline._ref", "baseline/_ref", "training_engine_tensor", "train_pure_mup_mtp", "model_pure_mup_mtp"]
 PROXY += [p for p in os.environ.get("FORGE_REFERENCE_ROOTS", "").split(os.pathsep) if p]   # checkout paths of the reference, if any
 ENGINE_DIRS = ["models", "ops", "optim", "parallel", "data", "ckpt", "engine.py", "train.py"]
-ALLOW = {"ops/torch_ops.py": {"torch.nn.Module"}, "data/sources.py": {"megatron"}}  # the corpus FORMAT is called Megatron binary
+# the corpus FORMAT is called Megatron binary, and the exporter writes checkpoints under Megatron-LM's state-dict names:
+# both name a file format, neither imports the framework
+ALLOW = {"ops/torch_ops.py": {"torch.nn.Module"}, "data/sources.py": {"megatron"}, "data/prepare.py": {"megatron"},
+         "ckpt/export_megatron.py": {"megatron"}}
 
 
 def _code_only(src: str) -> str:

@@ -274,3 +274,21 @@ def test_tolerance_alignment_of_tensor_captures(tmp_path):
     fit = V.align_tolerance(str(tmp_path / "ref.pt"), str(tmp_path / "ours.pt"), "bwd", 1e-2, fit_scale=True)
     assert fit["passed"] and fit["worst_rel_err"] < 1e-6
     assert not diff_tensors(ref, {}, family="fwd", rel_tol=1.0)["passed"]                                        # no overlap
+
+
+def test_prepare_corpus_matches_the_streaming_encode_contract(tmp_path):
+    import json
+    import numpy as np
+    from forge_train_harness_b200.data import prepare
+    from forge_train_harness_b200.data.sources import MegatronBinary
+    f = tmp_path / "qa.jsonl"
+    with open(f, "w") as fh:
+        for j in range(20):
+            fh.write(json.dumps({"question": f"q{j}", "answer": f"a{j}"}) + "\n")
+        fh.write(json.dumps({"question": "", "answer": ""}) + "\n")
+    assert prepare.main([str(f), "--out", str(tmp_path / "c"), "--tokenizer", "bytes", "--template", "gsm8k_qa"]) == 0
+    src = MegatronBinary(str(tmp_path / "c"), 8, 1, 0, 1, 0)
+    flat = np.concatenate([w for w in src.windows])
+    assert int((flat == 256).sum()) >= 10 and flat.max() <= 256          # one EOS per document, byte ids otherwise
+    text = bytes(int(x) for x in flat[:9]).decode()
+    assert text.startswith("Question")
