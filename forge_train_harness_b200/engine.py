@@ -117,6 +117,7 @@ class Trainer:
         self.graph_launches = 0  # sm_100a kernels recorded in the captured micro-batch graph
         self.graph_replays = 0
         self._layer_graphs = False  # TP / PP runs: the chunks' layer loops are replayed from CUDA graphs (after one eager step)
+        self._layer_graph_steps = 0  # steps run since the layer graphs were enabled (the first of them captures)
         self.stats = torch.zeros(4, dtype=torch.float64, device=self.device)
         self.launch_count = 0
         self.last = {}
@@ -338,11 +339,16 @@ class Trainer:
             if needs_recv(kind, v):
                 return (self.links.post_recv_act if kind == "F" else self.links.post_recv_grad)(shape, self.dtype, self.device)
             return None
-        # Receives are posted one action ahead.  On gloo (CPU) a posted receive is matched by peer sends in posting order
-        # exactly as on NCCL, so the same code runs on both.
+        # Receives may be posted one action ahead, so that the transfer runs under the current action's kernels.  Never
+        # while CUDA graphs are still being captured: a capture begins with a device-wide synchronize, which would wait
+        # for the posted receive, whose sender is a peer waiting in its own synchronize for THIS rank's next send.  The
+        # look-ahead is the default on the CPU / gloo path; on NCCL it is opt-in (FORGE_PP_PREFETCH=1) and starts with the
+        # first step after the one that captured the layer graphs.
+        ahead = (self.device.type != "cuda") or (os.environ.get("FORGE_PP_PREFETCH", "0") == "1"
+                                                 and (not self._layer_graphs or self._layer_graph_steps >= 1))
         posted = post(0) if sched else None
         for k, (kind, v, i) in enumerate(sched):
-            nxt = post(k + 1) if k + 1 < len(sched) else None
+            nxt = post(k + 1) if (ahead and k + 1 < len(sched)) else None
             ch = self.chunks[v]
             if kind == "F":
                 x_in = self.links.wait_recv(posted) if posted is not None else None
@@ -357,7 +363,7 @@ class Trainer:
                 g_in = ch.run_backward(batches[i], caches.pop((v, i)), g_out)
                 if g_in is not None:
                     self.links.send_grad(g_in)
-            posted = nxt
+            posted = nxt if ahead else (post(k + 1) if k + 1 < len(sched) else None)
         self.links.drain()
 
     # ------------------------------------------------------------------
@@ -401,6 +407,8 @@ class Trainer:
             self.capture.grads("post", self.store, scale=inv_tokens)
             self.capture.loss_scalar("post", stats)
         self.step = step_abs
+        if self._layer_graphs:
+            self._layer_graph_steps += 1
         self._maybe_enable_layer_graphs()
         self.last = {"loss": loss, "grad_norm": norm, "tokens": stats[1], "lr": lr}
         if verify:

@@ -9,8 +9,10 @@ then one-forward-one-backward, then the remaining backwards.
 
 Because the backward is hand-derived, a schedule is just a list of ``("F"|"B", chunk, microbatch)``.
 
-Transport: activations and gradients travel by ``isend`` / ``irecv`` over NCCL (gloo on CPU); receives are posted one
-schedule action ahead of their consumer and waited for on the stream, so the transfer overlaps the current action's compute.  Every
+Transport: activations and gradients travel by ``isend`` / ``irecv`` over NCCL (gloo on CPU) and are waited for on the stream
+(the host does not block on NCCL).  A receive can be posted one schedule action ahead of its consumer, so that the transfer
+overlaps the current action's compute (default on gloo, ``FORGE_PP_PREFETCH=1`` on NCCL; never during a CUDA-graph capture
+step: see ``engine.py``).  Every
 directed edge of the pipeline ring — activations p -> p+1 and gradients p+1 -> p — gets its OWN
 two-rank process group, hence its own communicator and stream: a send that waits for its receiver
 blocks only that edge, never the opposite direction, so the schedule needs no hand-paired

@@ -299,3 +299,15 @@ def test_adamw_distribution_and_repeatability(ops):
     assert_close_stats(mm, m64, mean=2e-7, p95=6e-7, mx=1e-5, bias=5e-8, what="exp_avg")
     assert_close_stats(vv, v64, mean=2e-6, p95=6e-6, mx=1e-4, bias=1e-6, what="exp_avg_sq")
     assert torch.equal(p, ma.to(torch.bfloat16))
+
+
+def test_attention_in_kernel_timelines(ops):
+    """The clock64 stamps of the attention kernels, read by the timeline tool: every phase of a step has a positive median
+    and the phases add up to the step; with no buffer set the kernels skip the stamps (every other test runs that way)."""
+    from forge_train_harness_b200.utils.attn_timeline import backward_timeline, forward_timeline
+    f = forward_timeline(S=2048, B=1)
+    b = backward_timeline(S=2048, B=1)
+    for part in list(f.values()) + list(b.values()):
+        assert part is not None and part["steps"] >= 8 and part["total"] > 500
+        phases = [v for k, v in part.items() if k not in ("total", "steps")]
+        assert all(v >= 0 for v in phases) and abs(sum(phases) - part["total"]) <= 0.25 * part["total"]
