@@ -180,6 +180,9 @@ class TrainConfig:
     init_weights_only: bool = False
     phase_name: str | None = None
     forge_init_ones: bool = True
+    # "reference": every full tensor drawn from one CPU generator in the reference's parameter order (bit-identical start
+    # for the gates; minutes of host time at 8B).  "device": each shard drawn on its GPU (throughput runs).
+    init_mode: str = "reference"
     cuda_graph: bool = True
     hash_capture_level: int = 0
     hash_output: str | None = None

@@ -144,8 +144,10 @@ class Trainer:
             self.store.load_canonical_state(torch.load(canon, map_location="cpu", weights_only=True))
         elif init_mode == "device":
             self.store.init_device(t.seed, t.forge_init_ones)
-        else:
+        elif init_mode == "reference":
             self.store.init_reference(t.seed, t.forge_init_ones)
+        else:
+            raise ValueError(f"init_mode must be 'reference' or 'device', not {init_mode!r}")
 
     def start_data(self):
         if self.prefetch is None:
@@ -469,7 +471,7 @@ def run_training_loop(cfg: RunConfig, *, trainer: Trainer | None = None, loss_ta
     out = out or sys.stdout
     t0_wall = time.time()
     created = init_distributed()
-    tr = trainer or Trainer(cfg)
+    tr = trainer or Trainer(cfg, init_mode=cfg.train.init_mode)
     t, oc, m = cfg.train, cfg.optim, cfg.model
     tag = loss_tag or t.loss_tag
     rank0 = tr.rank == 0

@@ -4,6 +4,9 @@
     python -m forge_train_harness_b200.harness guard | anti-proxy | unit | info | doctor | echo-config <toml> | render <gate.toml> ...
     python -m forge_train_harness_b200.harness budget <suite> | env-probe | resources provision|verify | prefetch <prefix> <dir> | sync push <dest>
     python -m forge_train_harness_b200.harness op-inventory | op-status | op-long <op> --config <toml> [--steps N --window A B --nproc N]
+    python -m forge_train_harness_b200.harness lease claim|release|rebind|list ... | job <suite> --outer S [--poll] | loop run|report ...
+
+``FORGE_EVAL_FAMILY`` picks the suite registry (dense_training | dense_training_1b | dense_training_8b | dense_training_qwen3).
 
 Local suites (``guard``, ``anti-proxy``, ``unit``) run in-process / as a pytest child; gate suites go request -> dispatcher ->
 result JSON between the result markers.  Timeout precedence: ``--timeout`` > ``HARNESS_RUN_TIMEOUT_S`` > the registry value.
@@ -30,12 +33,29 @@ def _timeout(cli_value, registry_value):
     return float(env) if env else float(registry_value)
 
 
+def _registry_default() -> str:
+    """Suite registry of the active eval family: ``FORGE_EVAL_FAMILY`` = dense_training (0.5B, default) | dense_training_1b |
+    dense_training_8b | dense_training_qwen3 (config/eval/<family>/<family>.toml in the reference)."""
+    fam = os.environ.get("FORGE_EVAL_FAMILY", "dense_training")
+    return os.path.join(ROOT, "configs", "eval", fam + ".toml")
+
+
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv[:1] == ["lease"]:      # GPU lease registry, short-lived GPU jobs and the development loop keep their own parsers
+        from . import lease
+        return lease.main(argv[1:])
+    if argv[:1] == ["job"]:
+        from . import jobs
+        return jobs.main(argv[1:])
+    if argv[:1] == ["loop"]:
+        from . import loop
+        return loop.main(argv[1:])
     ap = argparse.ArgumentParser(prog="harness")
     sub = ap.add_subparsers(dest="cmd", required=True)
     r = sub.add_parser("run")
     r.add_argument("suite")
-    r.add_argument("--registry", default=os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    r.add_argument("--registry", default=_registry_default())
     r.add_argument("--timeout", type=float, default=0.0)
     r.add_argument("--arg", action="append", default=[])
     r.add_argument("--artifacts", default=os.path.join(ROOT, ".artifacts", "runs"))
@@ -43,7 +63,7 @@ def main(argv=None) -> int:
         sub.add_parser(name)
     b = sub.add_parser("budget")
     b.add_argument("suite")
-    b.add_argument("--registry", default=os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    b.add_argument("--registry", default=_registry_default())
     b.add_argument("--json", action="store_true")
     rs = sub.add_parser("resources")
     rs.add_argument("action", choices=["provision", "verify"])
@@ -68,7 +88,7 @@ def main(argv=None) -> int:
     rn.add_argument("gate")
     rn.add_argument("--model", required=True)
     rn.add_argument("--optim", required=True)
-    rn.add_argument("--registry", default=os.path.join(ROOT, "configs", "eval", "dense_training.toml"))
+    rn.add_argument("--registry", default=_registry_default())
     a = ap.parse_args(argv)
 
     if a.cmd == "guard":
