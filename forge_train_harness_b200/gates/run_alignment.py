@@ -10,7 +10,8 @@ this name runs DP = 2, 200 steps, global batch 80, window [101, 201) (config/eva
 ``--nproc 2 --steps 200 --mbs 4 --accum 10 --window 101 201 --ref engine``.
 
 The three steps of the reference's gate executor (evals/dispatcher.py:253-331): (1) run the reference side — its unmodified
-pure-PyTorch L0 trainer (ref/reference/train_pure_mup_mtp.py) from ``baseline/_ref`` as a child process; (2) run this
+pure-PyTorch L0 trainer (ref/reference/train_pure_mup_mtp.py, or ref/reference/train_qwen3_dense.py for a Qwen3 ``--model``)
+from ``baseline/_ref`` as a child process; (2) run this
 engine through its public entry point (``python -m forge_train_harness_b200.train``) as a child process; (3) a verdict
 that only reads the two logs: mean |ours - ref| / |ref| over the step window below ``--threshold`` (the ``long-train``
 rule, evals/verdicts/long_train.py:177-220) plus a first-step tolerance check (single-card alignment).
@@ -60,7 +61,8 @@ def main(argv=None):
     m = preset(a.model)
     if a.layers:
         m = dataclasses.replace(m, num_layers=a.layers)
-    m = dataclasses.replace(m, tie_embeddings=False, mtp_num_layers=0)  # the reference trainer's only mode
+    qwen = m.qk_norm and not m.use_mup      # the Qwen3 family has its own L0 trainer (tied head, no MTP, no muP)
+    m = dataclasses.replace(m, mtp_num_layers=0) if qwen else dataclasses.replace(m, tie_embeddings=False, mtp_num_layers=0)
     out = os.path.abspath(a.out)
     os.makedirs(out, exist_ok=True)
     gbs = a.mbs * a.accum * a.nproc
@@ -109,13 +111,14 @@ def main(argv=None):
     env["PYTHONPATH"] = os.pathsep.join([REF, os.path.join(REF, "ref", "reference"), env.get("PYTHONPATH", "")])
     env["FORGE_DATA_TOML"] = os.path.join(out, "data.toml")
     ref_cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.nproc}", "--master-addr", "127.0.0.1",
-               "--master-port", str(port), os.path.join(REF, "ref", "reference", "train_pure_mup_mtp.py"),
+               "--master-port", str(port), os.path.join(REF, "ref", "reference", "train_qwen3_dense.py" if qwen else "train_pure_mup_mtp.py"),
                "--data-path-file", os.path.join(out, "data_path.txt"), "--data-config", os.path.join(out, "data.toml"),
                "--train-iters", str(a.steps), "--micro-batch-size", str(a.mbs), "--global-batch-size", str(gbs),
                "--lr", str(a.lr), "--min-lr", str(a.lr * 0.1), "--lr-warmup-iters", "10", "--lr-decay-iters", "100000",
                "--weight-decay", "0.1", "--adam-beta1", "0.9", "--adam-beta2", "0.95", "--clip-grad", "1.0", "--seed", "1234",
-               "--init-method-std", str(m.init_method_std), "--init-ones", "1", "--eagle-num-layers", "0",
-               "--out-dir", os.path.join(out, "ref_out"), "--no-deterministic"]
+               "--init-method-std", str(m.init_method_std), "--out-dir", os.path.join(out, "ref_out"), "--no-deterministic"]
+    if not qwen:
+        ref_cmd += ["--init-ones", "1", "--eagle-num-layers", "0"]
     if a.ref == "engine":
         ref_cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.nproc}", "--master-addr",
                    "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "baseline", "ref_engine_driver.py"),

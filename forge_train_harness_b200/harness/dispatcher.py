@@ -80,6 +80,16 @@ def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) ->
         r = V.resume_startup(rd(our_log), gate.get("resume_startup_budget_s", 18.0))
     elif kind == "wsd_sft":
         r = V.wsd_sft(rd(ref_log), rd(our_log))
+    elif kind == "exit_code":
+        # the runner judged itself (it exited 0, or run_suite would not have come here); its last JSON line, if any, is kept
+        r = {"passed": ours_rc == 0}
+        for ln in reversed(rd(our_log).strip().splitlines()[-20:]):
+            if ln.startswith("{"):
+                try:
+                    r.update({k: v for k, v in json.loads(ln).items() if k != "passed"})
+                    break
+                except json.JSONDecodeError:
+                    continue
     elif kind == "production":
         r = V.production(os.path.join(run_dir, gate.get("ckpt_subdir", os.path.join("ours", "ckpt"))), gate["expected_steps"])
     else:

@@ -194,6 +194,13 @@ def iter_full_init(cfg: ModelConfig, seed: int, init_ones: bool = True, wanted: 
     for spec in full_param_specs(cfg):
         if spec.init == "norm":
             t = torch.full(spec.full_shape, 1.0 if init_ones else 0.97, dtype=torch.float32)
+        elif spec.kind == "qkv" and cfg.qk_norm and not cfg.use_mup:
+            # the Qwen3 reference keeps q / k / v as three matrices and draws them one after the other, heads in plain order
+            # (model_qwen3.py:112-115, 232-249); same draws here, then interleaved per KV group into the fused layout
+            nkv, g, d, H = cfg.num_query_groups, cfg.q_per_kv, cfg.head_dim, spec.full_shape[1]
+            q, k, v = (torch.randn((rows, H), generator=gen, dtype=torch.float32).mul_(init_std(spec, cfg))
+                       for rows in (nkv * g * d, nkv * d, nkv * d))
+            t = torch.cat([q.view(nkv, g, d, H), k.view(nkv, 1, d, H), v.view(nkv, 1, d, H)], 1).reshape(spec.full_shape)
         else:
             t = torch.randn(spec.full_shape, generator=gen, dtype=torch.float32).mul_(init_std(spec, cfg))
         yield spec, (t if wanted is None or spec.name in wanted else None)

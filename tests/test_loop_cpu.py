@@ -218,3 +218,28 @@ def test_loop_config_file_and_cli(tmp_path):
     assert order[0] == "alignment" and order[-1] == "production"
     for m in order:
         assert loop.suites_of_milestone(shipped.registry, m), m
+
+
+def test_every_eval_family_registry_is_routable():
+    """Four families (0.5B, 1B, 8B, Qwen3), each with a milestone order that its suites cover and verdict kinds the dispatcher knows."""
+    import inspect
+    import tomllib
+
+    from forge_train_harness_b200.harness import dispatcher
+    kinds = set(__import__("re").findall(r'kind == "([a-z_]+)"', inspect.getsource(dispatcher._verdict)))
+    for fam in ("dense_training", "dense_training_1b", "dense_training_8b", "dense_training_qwen3"):
+        path = os.path.join(loop.ROOT, "configs", "eval", fam + ".toml")
+        doc = tomllib.load(open(path, "rb"))
+        assert doc["family"]["name"] == fam
+        order = loop.milestone_order(path)
+        for m in order:
+            assert loop.suites_of_milestone(path, m), (fam, m)
+        for name, gate in doc["evals"].items():
+            assert gate["verdict"] in kinds, (fam, name, gate["verdict"])
+            assert gate.get("stage") in ("stage1", "stage2"), (fam, name)
+            ms = gate.get("milestone", "")
+            assert gate["stage"] == "stage2" or ms.split(".")[0] in order, (fam, name, ms)
+    d8 = tomllib.load(open(os.path.join(loop.ROOT, "configs", "eval", "dense_training_8b.toml"), "rb"))
+    assert "hf-oracle" in d8["evals"] and "dptp" in d8["evals"] and "--model" in d8["evals"]["long-train"]["ours_cmd"]
+    dq = tomllib.load(open(os.path.join(loop.ROOT, "configs", "eval", "dense_training_qwen3.toml"), "rb"))
+    assert "qwen3_0.6b" in dq["evals"]["long-train"]["ours_cmd"] and "dptp" not in dq["evals"]

@@ -200,3 +200,25 @@ def test_minicpm_mup_mtp_matches_the_reference_model(ref_minicpm):
             bad[name] = err
     assert not bad, bad
     tr.close()
+
+
+def test_reference_order_init_is_bit_identical_for_both_model_families(ref_qwen3):
+    """``init_reference`` must reproduce the reference's own ``init_weights`` (same generator, same draw order): it is what lets
+    a gate start both sides from equal weights without exchanging a file."""
+    from forge_train_harness_b200.ckpt.hf_names import split_qkv
+    from forge_train_harness_b200.models import params as P
+    ref = ref_qwen3.Qwen3Dense().float()
+    ref.init_weights(init_std=0.02, seed=1234)
+    sd = dict(ref.named_parameters())
+    m = dataclasses.replace(fth.preset("qwen3_0.6b"), num_layers=2, hidden_size=128, ffn_hidden_size=256, num_attention_heads=4,
+                            num_query_groups=2, head_dim=64, seq_length=64, padded_vocab_size=512, max_position_embeddings=64)
+    n = 0
+    for spec, t in P.iter_full_init(m, 1234, True):
+        if spec.name.endswith("wqkv.weight"):
+            li = spec.name.split(".")[1]
+            for part, nm in zip(split_qkv(t, m), ("wq", "wk", "wv")):
+                assert torch.equal(part, sd[f"layers.{li}.{nm}.weight"].data), (spec.name, nm)
+        else:
+            assert torch.equal(t, sd[spec.name].data), spec.name
+        n += 1
+    assert n == len(P.full_param_specs(m))
