@@ -24,6 +24,7 @@ CLI::
 
     python -m forge_train_harness_b200.harness.loop run --config configs/loop.toml [--loop-id ID] [--max-rounds N] [--reset-state]
     python -m forge_train_harness_b200.harness.loop report <loop_dir> [--json out.json] [--md out.md]
+    python -m forge_train_harness_b200.harness.loop fork --config configs/loop.toml --src-loop-id ID --at-milestone NAME [--workspace DIR]
     python -m forge_train_harness_b200.harness.loop should-retry <rc>
 """
 from __future__ import annotations
@@ -212,6 +213,17 @@ class Loop:
         with open(os.path.join(self.dir, "events.jsonl"), "a", encoding="utf-8") as f:
             f.write(json.dumps(row) + "\n")
         return row
+
+    def backfill_mfu_events(self) -> int:
+        """One ``mfu_record`` event per row of ``mfu_history.jsonl`` not yet seen (rows land there from gate runs, possibly
+        on another host and synced back; a cursor file makes this idempotent — tools/mfu_backfill_events.py)."""
+        rows = mfu.load(os.path.join(self.dir, "mfu_history.jsonl"))
+        seen = int(self._read("mfu.cursor", "0"))
+        for r in rows[seen:]:
+            self.event("mfu_record", suite=r.get("suite"), mfu_avg=r.get("mfu_avg"), loss_passed=r.get("loss_passed"), sample_ts=r.get("ts"))
+        if len(rows) != seen:
+            self._write("mfu.cursor", str(len(rows)))
+        return len(rows) - seen
 
     # -- git helpers (the workspace's history is the trajectory)
     def _git(self, *args: str) -> str:
@@ -420,6 +432,7 @@ class Loop:
                     self._advance_by_gates(rnd, lease_env)
                 else:
                     self._advance_declared(rnd, review_passed, ctx["review_file"])
+                self.backfill_mfu_events()
                 self.event("round_finished", round=rnd, status="ok", attempts=attempts, duration_s=time.time() - t0,
                            review="PASS" if review_passed else "FAIL", commits=commits, milestone_after=self.milestone)
                 if self._read("stage1.status") == "finished":
@@ -443,6 +456,71 @@ class Loop:
             self.event("loop_exit", rc=rc_final, cause=self.exit_cause, milestone=self.milestone)
             for s, h in prev_handlers.items():
                 signal.signal(s, h)
+
+
+# ---- fork a loop at a passed milestone -----------------------------------------------------------------------------------------
+def fork(cfg: LoopConfig, src_loop_id: str, at_milestone: str, new_loop_id: str | None = None, at_sha: str = "",
+         workspace_dst: str | None = None) -> dict:
+    """New loop whose state equals the source loop's at the moment ``at_milestone`` was accepted, so a normal ``run
+    --loop-id`` continues from the NEXT milestone (tools/fork_loop.py).  The anchor commit comes from the source's
+    ``milestone_advanced`` event, else from the one commit that declares the milestone; several declarations without an event
+    are ambiguous and need ``at_sha``.  The source loop is not touched; with ``workspace_dst`` the workspace history up to
+    the anchor is cloned there (``git clone`` + ``reset --hard``) for the new loop to work in."""
+    src = Loop(cfg, loop_id=src_loop_id)
+    order = src.order
+    if at_milestone not in order:
+        raise ValueError(f"{at_milestone!r} is not in the milestone order {order}")
+    decl = re.compile(rf"^MILESTONE_STATUS:[ \t]+{re.escape(at_milestone)}[ \t]+PASS[ \t]*$", re.M)
+
+    def declares(sha: str) -> bool:
+        return bool(sha) and bool(decl.search(src._git("show", "-s", "--format=%B", sha)))
+
+    events = []
+    ep = os.path.join(src.dir, "events.jsonl")
+    if os.path.isfile(ep):
+        for ln in open(ep, encoding="utf-8"):
+            try:
+                events.append(json.loads(ln))
+            except json.JSONDecodeError:
+                continue
+    anchor, rnd, source = "", 0, ""
+    if at_sha:
+        full = src._git("rev-parse", at_sha).strip()
+        if not declares(full):
+            raise ValueError(f"{at_sha} does not exist in the workspace or does not declare 'MILESTONE_STATUS: {at_milestone} PASS'")
+        anchor, source = full, "explicit-sha"
+    else:
+        hits = [e for e in events if e.get("subtype") == "milestone_advanced" and e.get("from") == at_milestone and declares(e.get("commit", ""))]
+        if hits:
+            anchor, rnd, source = hits[-1]["commit"], int(hits[-1].get("round", 0)), "event"
+        else:
+            shas = [h for h in src._git("log", "--format=%H").split() if declares(h)]
+            if len(shas) != 1:
+                raise ValueError(f"{len(shas)} commits declare {at_milestone!r} and no event names one: pass at_sha")
+            anchor, source = shas[0], "git-fallback"
+    nxt = order[min(order.index(at_milestone) + 1, len(order) - 1)]
+    ws = cfg.workspace
+    if workspace_dst:
+        if os.path.exists(workspace_dst) and os.listdir(workspace_dst):
+            raise ValueError(f"{workspace_dst} exists and is not empty")
+        subprocess.run(["git", "clone", "-q", cfg.workspace, workspace_dst], check=True, timeout=600)
+        subprocess.run(["git", "-C", workspace_dst, "reset", "-q", "--hard", anchor], check=True, timeout=120)
+        ws = workspace_dst
+    import dataclasses as _dc
+    new = Loop(_dc.replace(cfg, workspace=ws), loop_id=new_loop_id)
+    if os.path.exists(os.path.join(new.dir, "events.jsonl")):
+        raise ValueError(f"loop {new.loop_id} already exists")
+    new._write("stage1.milestone", nxt)
+    new._write("stage1.status", "in-progress")
+    new._write("stage1.round", str(rnd))
+    src_hist = os.path.join(src.dir, "mfu_history.jsonl")
+    if os.path.isfile(src_hist):
+        import shutil
+        shutil.copyfile(src_hist, os.path.join(new.dir, "mfu_history.jsonl"))
+    info = {"src_loop_id": src_loop_id, "loop_id": new.loop_id, "anchor": anchor, "anchor_source": source, "passed": at_milestone,
+            "next_milestone": nxt, "round": rnd, "workspace": ws}
+    new.event("loop_forked", **info)
+    return info
 
 
 # ---- offline report -----------------------------------------------------------------------------------------------------------
@@ -542,6 +620,13 @@ def main(argv=None) -> int:
     rp.add_argument("loop_dir")
     rp.add_argument("--json", default="")
     rp.add_argument("--md", default="")
+    fk = sub.add_parser("fork")
+    fk.add_argument("--config", required=True)
+    fk.add_argument("--src-loop-id", required=True)
+    fk.add_argument("--at-milestone", required=True)
+    fk.add_argument("--at-sha", default="")
+    fk.add_argument("--new-loop-id", default="")
+    fk.add_argument("--workspace", default="", help="clone the workspace at the anchor commit into this empty directory")
     sr = sub.add_parser("should-retry")
     sr.add_argument("rc", type=int)
     ms = sub.add_parser("stage-milestones")
@@ -551,6 +636,15 @@ def main(argv=None) -> int:
         return 0 if should_retry(a.rc) else 1
     if a.cmd == "stage-milestones":
         print("\n".join(milestone_order(a.registry)))
+        return 0
+    if a.cmd == "fork":
+        try:
+            info = fork(LoopConfig.load(a.config), a.src_loop_id, a.at_milestone, a.new_loop_id or None, a.at_sha, a.workspace or None)
+        except ValueError as e:
+            print(f"fork: {e}", file=sys.stderr)
+            return 1
+        print(json.dumps(info, indent=1))
+        print(f"continue with: python -m forge_train_harness_b200.harness.loop run --config {a.config} --loop-id {info['loop_id']}", file=sys.stderr)
         return 0
     if a.cmd == "report":
         rep = report(a.loop_dir)

@@ -243,3 +243,32 @@ def test_every_eval_family_registry_is_routable():
     assert "hf-oracle" in d8["evals"] and "dptp" in d8["evals"] and "--model" in d8["evals"]["long-train"]["ours_cmd"]
     dq = tomllib.load(open(os.path.join(loop.ROOT, "configs", "eval", "dense_training_qwen3.toml"), "rb"))
     assert "qwen3_0.6b" in dq["evals"]["long-train"]["ours_cmd"] and "dptp" not in dq["evals"]
+
+
+def test_fork_continues_from_the_milestone_after_the_anchor(tmp_path):
+    ws, reg = _workspace(tmp_path)
+    cfg = _cfg(tmp_path, ws, reg, {1: "declare", 2: "declare"})
+    lp = loop.Loop(cfg, loop_id="src")
+    assert lp.run(max_rounds=2) == 0 and lp.milestone == "long-horizon"
+    mfu.record(os.path.join(lp.dir, "mfu_history.jsonl"), "long-train", 40.0, True)
+    assert lp.backfill_mfu_events() == 1 and lp.backfill_mfu_events() == 0  # cursor: each row becomes one event, once
+    assert [e["mfu_avg"] for e in _events(lp) if e["subtype"] == "mfu_record"] == [40.0]
+    # fork at the first milestone: anchor = the commit that declared it (from the event), state = the milestone after it
+    info = loop.fork(cfg, "src", "alignment", new_loop_id="forked", workspace_dst=str(tmp_path / "ws2"))
+    assert info["anchor_source"] == "event" and info["next_milestone"] == "bitwise-singlecard" and info["round"] == 1
+    head2 = subprocess.run(["git", "-C", str(tmp_path / "ws2"), "rev-parse", "HEAD"], capture_output=True, text=True).stdout.strip()
+    assert head2 == info["anchor"] and head2 != lp.head()  # history cut at the anchor; the source keeps its later commits
+    import dataclasses
+    lp2 = loop.Loop(dataclasses.replace(cfg, workspace=str(tmp_path / "ws2")), loop_id="forked")
+    assert lp2.milestone == "bitwise-singlecard" and os.path.isfile(os.path.join(lp2.dir, "mfu_history.jsonl"))
+    assert lp2.run(max_rounds=1) == 0  # round counter continues: this is round 2, whose script entry declares
+    assert [e["round"] for e in _events(lp2) if e["subtype"] == "round_started"] == [2] and lp2.milestone == "long-horizon"
+    with pytest.raises(ValueError, match="already exists"):
+        loop.fork(cfg, "src", "alignment", new_loop_id="forked")
+    with pytest.raises(ValueError, match="not in the milestone order"):
+        loop.fork(cfg, "src", "nonsense")
+    # without events the one declaring commit is found in the history; an undeclared sha is refused
+    os.unlink(os.path.join(lp.dir, "events.jsonl"))
+    assert loop.fork(cfg, "src", "bitwise-singlecard", new_loop_id="f3")["anchor_source"] == "git-fallback"
+    with pytest.raises(ValueError, match="does not"):
+        loop.fork(cfg, "src", "alignment", new_loop_id="f4", at_sha=lp.head())
