@@ -4,7 +4,7 @@
     python -m forge_train_harness_b200.harness guard | anti-proxy | unit | info | doctor | echo-config <toml> | render <gate.toml> ...
     python -m forge_train_harness_b200.harness budget <suite> | env-probe | resources provision|verify | prefetch <prefix> <dir> | sync push <dest>
     python -m forge_train_harness_b200.harness op-inventory | op-status | op-long <op> --config <toml> [--steps N --window A B --nproc N]
-    python -m forge_train_harness_b200.harness lease claim|release|rebind|list ... | job <suite> --outer S [--poll] | loop run|report ...
+    python -m forge_train_harness_b200.harness lease claim|release|rebind|list ... | job <suite> --outer S [--poll] | loop run|report|fork ... | tools canonical|recipe-env|data-check|capture-batch ...
 
 ``FORGE_EVAL_FAMILY`` picks the suite registry (dense_training | dense_training_1b | dense_training_8b | dense_training_qwen3).
 
@@ -51,6 +51,9 @@ def main(argv=None) -> int:
     if argv[:1] == ["loop"]:
         from . import loop
         return loop.main(argv[1:])
+    if argv[:1] == ["tools"]:      # canonical | recipe-env | data-check | capture-batch
+        from . import tools
+        return tools.main(argv[1:])
     ap = argparse.ArgumentParser(prog="harness")
     sub = ap.add_subparsers(dest="cmd", required=True)
     r = sub.add_parser("run")
