@@ -173,9 +173,80 @@ def op_long(name: str, config: str, steps: int = 200, window: tuple[int, int] = 
 
 
 def _record(name: str, res: dict) -> None:
+    """Last result per op, plus a running count of consecutive failed ``op-long`` runs (reset by a pass)."""
     os.makedirs(_results_dir(), exist_ok=True)
-    with open(os.path.join(_results_dir(), f"{name}.json"), "w") as f:
-        json.dump({k: v for k, v in res.items() if k != "step_diffs"}, f, indent=1)
+    path = os.path.join(_results_dir(), f"{name}.json")
+    fails = 0
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                fails = int(json.load(f).get("consecutive_failures", 0))
+        except (json.JSONDecodeError, ValueError, OSError):
+            fails = 0
+    fails = 0 if res.get("passed") else fails + 1
+    with open(path, "w") as f:
+        json.dump(dict({k: v for k, v in res.items() if k != "step_diffs"}, consecutive_failures=fails), f, indent=1)
+
+
+def op_long_failures(name: str) -> int:
+    path = os.path.join(_results_dir(), f"{name}.json")
+    try:
+        with open(path) as f:
+            return int(json.load(f).get("consecutive_failures", 0))
+    except (FileNotFoundError, json.JSONDecodeError, ValueError):
+        return 0
+
+
+def fan_out(worker_argv: list[str], ops: list[str] | None = None, max_concurrent: int | None = None,
+            max_failures: int | None = None, timeout_s: float = 4 * 3600.0, log_dir: str | None = None) -> dict:
+    """One worker process per operator, at most ``[automation].max_concurrent`` at a time (the reference's stage-2 main agent
+    fans its sub-agents out the same way, tools/stage2_config.py, config [automation.stage2]).  ``worker_argv`` is a command
+    template; ``{op}`` is replaced by the operator's name and ``OP_NAME`` is exported.  Operators whose last
+    ``[automation].max_op_long_failures`` op-long runs all failed are skipped as ``exhausted`` — the safety net that stops a
+    worker from burning GPU time on the same broken kernel round after round.  Workers share the GPU through ``gpu_lock``."""
+    reg = load_registry()
+    auto = reg.get("automation", {})
+    max_concurrent = int(max_concurrent if max_concurrent is not None else auto.get("max_concurrent", 6))
+    max_failures = int(max_failures if max_failures is not None else auto.get("max_op_long_failures", 3))
+    names = list(ops) if ops else sorted(reg.get("ops", {}))
+    unknown = [n for n in names if n not in reg.get("ops", {})]
+    if unknown:
+        raise KeyError(f"unknown operators: {unknown}")
+    log_dir = log_dir or os.path.join(ROOT, ".artifacts", "stage2", "workers")
+    os.makedirs(log_dir, exist_ok=True)
+    result = {n: {"state": "exhausted", "failures": op_long_failures(n)} for n in names if op_long_failures(n) >= max_failures}
+    todo = [n for n in names if n not in result]
+    running: dict[str, tuple] = {}
+    import time
+    peak = 0
+    while todo or running:
+        while todo and len(running) < max(1, max_concurrent):
+            n = todo.pop(0)
+            lg = open(os.path.join(log_dir, f"{n}.log"), "ab")
+            p = subprocess.Popen([a.replace("{op}", n) for a in worker_argv], cwd=ROOT, env=dict(os.environ, OP_NAME=n),
+                                 stdin=subprocess.DEVNULL, stdout=lg, stderr=subprocess.STDOUT, start_new_session=True)
+            running[n] = (p, lg, time.monotonic())
+            peak = max(peak, len(running))
+        for n, (p, lg, t0) in list(running.items()):
+            rc = p.poll()
+            if rc is None and time.monotonic() - t0 > timeout_s:
+                with contextlib.suppress(ProcessLookupError):
+                    os.killpg(p.pid, 15)   # the exact group this worker was started in
+                try:
+                    rc = p.wait(timeout=10)
+                except subprocess.TimeoutExpired:
+                    with contextlib.suppress(ProcessLookupError):
+                        os.killpg(p.pid, 9)
+                    rc = p.wait()
+                rc = 124
+            if rc is not None:
+                lg.close()
+                result[n] = {"state": "done" if rc == 0 else "failed", "rc": rc, "failures": op_long_failures(n)}
+                del running[n]
+        if running:
+            time.sleep(0.05)
+    return {"passed": all(r["state"] == "done" for r in result.values()), "max_concurrent": max_concurrent, "peak_running": peak,
+            "ops": result}
 
 
 def as_result(suite: str, r: dict) -> dict:

@@ -279,3 +279,30 @@ def test_axis_directories_gate_sources_and_resolve_deploy():
         render.resolve_deploy(prod, {"data_path": "/data/corpus"})
     with pytest.raises(KeyError, match="match no <runtime>"):
         render.resolve_deploy(prod, {"data_path": "x", "MASTER_PORT": 1, "typo": 2})
+
+
+def test_stage2_fan_out_bounds_concurrency_and_skips_exhausted_ops(tmp_path, monkeypatch):
+    """[automation].max_concurrent workers at a time; an op whose last max_op_long_failures op-long runs failed is skipped."""
+    from forge_train_harness_b200.harness import stage2
+    monkeypatch.setattr(stage2, "_results_dir", lambda: str(tmp_path / "op_long"))
+    ops = sorted(stage2.load_registry()["ops"])[:5]
+    for _ in range(3):
+        stage2._record(ops[0], {"passed": False})
+    stage2._record(ops[1], {"passed": False})
+    stage2._record(ops[1], {"passed": True})        # a pass resets the count
+    assert stage2.op_long_failures(ops[0]) == 3 and stage2.op_long_failures(ops[1]) == 0
+    marks = tmp_path / "marks"
+    marks.mkdir()
+    worker = tmp_path / "w.py"
+    worker.write_text("import os, sys, time\nd = sys.argv[2]\nopen(os.path.join(d, sys.argv[1] + '.start'), 'w').close()\n"
+                      "time.sleep(0.4)\nn = len([f for f in os.listdir(d) if f.endswith('.start')]) - len([f for f in os.listdir(d) if f.endswith('.end')])\n"
+                      "open(os.path.join(d, sys.argv[1] + '.end'), 'w').write(str(n))\nsys.exit(3 if sys.argv[1] == os.environ['FAIL_OP'] else 0)\n")
+    monkeypatch.setenv("FAIL_OP", ops[2])
+    res = stage2.fan_out([sys.executable, str(worker), "{op}", str(marks)], ops=ops, max_concurrent=2, max_failures=3,
+                         log_dir=str(tmp_path / "logs"))
+    assert res["ops"][ops[0]]["state"] == "exhausted" and not os.path.exists(marks / (ops[0] + ".start"))
+    assert res["ops"][ops[2]] == {"state": "failed", "rc": 3, "failures": 0} and res["ops"][ops[1]]["state"] == "done"
+    assert res["peak_running"] == 2 and not res["passed"]
+    assert max(int(open(marks / f).read()) for f in os.listdir(marks) if f.endswith(".end")) <= 2   # never more than 2 alive
+    with pytest.raises(KeyError):
+        stage2.fan_out(["true"], ops=["no_such_op"])
