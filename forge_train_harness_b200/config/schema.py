@@ -183,6 +183,7 @@ class TrainConfig:
     # "reference": every full tensor drawn from one CPU generator in the reference's parameter order (bit-identical start
     # for the gates; minutes of host time at 8B).  "device": each shard drawn on its GPU (throughput runs).
     init_mode: str = "reference"
+    debug_checks: bool = False       # validate token ids / labels against the vocabulary every micro-batch (also FORGE_DEBUG_CHECKS=1)
     cuda_graph: bool = True
     hash_capture_level: int = 0
     hash_output: str | None = None

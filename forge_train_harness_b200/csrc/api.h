@@ -17,6 +17,8 @@ int fth_rope(void* qkv, const float* table, int M, int S, int n_kv, int g, int d
 int fth_swiglu_fwd(const void* gu, void* out, int M, int F, cudaStream_t stream);
 int fth_swiglu_bwd(const void* dinter, const void* gu, void* dgu, int M, int F, cudaStream_t stream);
 int fth_residual_add(const void* h, const void* a, float scale, void* out, size_t n, cudaStream_t stream);
+// debug input check: ids outside [lo, hi) set status 7 and record the first bad position in where[0] (atomicMin)
+int fth_check_ids(const int* ids, size_t n, int lo, int hi, int* status, int* where, cudaStream_t stream);
 int fth_embedding_fwd(const int* ids, const void* w, void* out, int M, int H, int vocab_start, int vocab_local, float scale,
                       cudaStream_t stream);
 int fth_embedding_bwd(const void* dout, const int* ids, float* main_grad, int M, int H, int vocab_start, int vocab_local,

@@ -136,6 +136,24 @@ at::Tensor residual_add(const at::Tensor& h, const at::Tensor& a, double scale) 
   return out;
 }
 
+at::Tensor g_bad_pos;  // first position a debug input check found out of range (INT_MAX = none)
+
+// Debug input check (off the hot path unless asked for): every id must lie in [lo, hi).  Nothing is read back here; a bad id
+// shows up as status 7 at the step's status check, and bad_index_position() says where.
+void check_ids(const at::Tensor& ids, int64_t lo, int64_t hi) {
+  need_i32(ids, "ids");
+  if (!g_bad_pos.defined()) g_bad_pos = at::full({1}, 0x7fffffff, at::TensorOptions().dtype(at::kInt).device(at::kCUDA));
+  check(fth_check_ids(ids.data_ptr<int>(), (size_t)ids.numel(), (int)lo, (int)hi, status_ptr(), g_bad_pos.data_ptr<int>(),
+                      cur_stream()), "check_ids");
+}
+
+int64_t bad_index_position(bool reset) {
+  if (!g_bad_pos.defined()) return -1;
+  int v = g_bad_pos.cpu().item<int>();
+  if (reset && v != 0x7fffffff) g_bad_pos.fill_(0x7fffffff);
+  return v == 0x7fffffff ? -1 : v;
+}
+
 at::Tensor embedding_fwd(const at::Tensor& ids, const at::Tensor& w, double scale, int64_t vocab_start) {
   need_i32(ids, "ids");
   need_bf16(w, "weight");
@@ -420,6 +438,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("residual_add", &residual_add);
+  m.def("check_ids", &check_ids);
+  m.def("bad_index_position", &bad_index_position);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("embedding_bwd_det", &embedding_bwd_det);

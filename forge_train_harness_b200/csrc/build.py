@@ -65,9 +65,11 @@ def build(verbose: bool = False) -> str:
     objs.append(bobj)
     if _newer(objs, SO):
         libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
-        _run(["g++", "-shared", "-o", SO] + objs + ["-L", libdir, "-L", os.path.join(cuda_home, "lib64"),
+        tmp = SO + f".tmp{os.getpid()}"   # link beside the target, then rename: a reader never sees a half-written library
+        _run(["g++", "-shared", "-o", tmp] + objs + ["-L", libdir, "-L", os.path.join(cuda_home, "lib64"),
              "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart",
              f"-Wl,-rpath,{libdir}"], log)
+        os.replace(tmp, SO)
     with open(os.path.join(OBJ, "build.log"), "w") as f:
         f.write("\n".join(log))
     if verbose:

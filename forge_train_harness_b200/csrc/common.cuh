@@ -17,6 +17,7 @@ enum StatusCode : int {
   kTimeoutTmemEmpty = 4,   // MMA issuer waited for an accumulator that was never drained
   kTimeoutPeerFlag = 5,    // a flag another GPU should have written never changed
   kTimeoutGeneric = 6,
+  kBadIndex = 7,           // an input check found an index outside its valid range (debug checks; no wait involved)
 };
 
 constexpr long long kSpinLimitCycles = 4000000000LL;  // ~2 s at B200 clocks

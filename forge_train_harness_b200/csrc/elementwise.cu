@@ -294,6 +294,20 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfl
   }
 }
 
+// Debug input check: the embedding and cross-entropy kernels treat an id outside the local vocabulary range as "another
+// rank's token" and skip it, which is right under vocabulary parallelism and hides a corrupt batch without it.  This kernel
+// looks at the GLOBAL range: an id outside [lo, hi) sets status kBadIndex and records the first offending position
+// (atomicMin) in where[0]; it touches nothing else.
+__global__ void check_ids_kernel(const int* __restrict__ ids, size_t n, int lo, int hi, int* status, int* where) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    int v = ids[i];
+    if (v < lo || v >= hi) {
+      report_status(status, kBadIndex);
+      if (where != nullptr) atomicMin(where, (int)(i < 0x7fffffff ? i : 0x7fffffff));
+    }
+  }
+}
+
 __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const int* __restrict__ ids,
                                      float* __restrict__ main_grad, int M, int H, int vocab_start, int vocab_local,
                                      float scale) {
@@ -645,6 +659,13 @@ int fth_embedding_fwd(const int* ids, const void* w, void* out, int M, int H, in
   int grid = (int)min((total + 255) / 256, (size_t)num_sms() * 16);
   embedding_fwd_kernel<<<grid, 256, 0, stream>>>(ids, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, H, vocab_start,
                                                  vocab_local, scale);
+  return 0;
+}
+
+int fth_check_ids(const int* ids, size_t n, int lo, int hi, int* status, int* where, cudaStream_t stream) {
+  if (n == 0) return 0;
+  int grid = (int)min((n + 255) / 256, (size_t)num_sms() * 4);
+  check_ids_kernel<<<grid, 256, 0, stream>>>(ids, n, lo, hi, status, where);
   return 0;
 }
 

@@ -90,6 +90,7 @@ class Trainer:
         for c in self.chunks:
             c.recompute = t.recompute
             c.recompute_num_layers = t.recompute_num_layers
+            c.debug_checks = t.debug_checks or os.environ.get("FORGE_DEBUG_CHECKS", "0") == "1"
         fused = None
         want_dp = os.environ.get("FORGE_FUSED_DP", "1")
         if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 and want_dp != "0":
@@ -186,8 +187,12 @@ class Trainer:
         code = self._read_status()
         if code:
             from .ops.status import STATUS_NAMES
+            where = ""
+            if code == 7:
+                from .ops.cuda_ops import Sm100Ops
+                where = f" [first bad position in its tensor: {Sm100Ops.bad_index_position()}]"
             raise RuntimeError(f"step {self.step}: sm_100a kernel reported status {code} "
-                               f"({STATUS_NAMES.get(code, 'unknown')}); the step's results are not valid")
+                               f"({STATUS_NAMES.get(code, 'unknown')}){where}; the step's results are not valid")
 
     def _fwd_bwd_overlapped(self, batch: dict):
         """The last micro-batch of a step: every gradient bucket goes to the DP reduction as soon as the backward has passed

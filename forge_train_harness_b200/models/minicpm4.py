@@ -67,6 +67,9 @@ class ModelChunk:
         self.ds = cfg.depth_scale(0)
         self.ds_mtp = cfg.depth_scale(cfg.mtp_num_layers)
         self.capture = capture  # optional hook: capture(kind, fqn, tensor)
+        # debug input checks (train.debug_checks / FORGE_DEBUG_CHECKS=1): token ids and labels must lie in the GLOBAL vocabulary
+        # range; the kernels themselves only skip ids outside the LOCAL range, which is legitimate under vocabulary parallelism
+        self.debug_checks = False
         self.recompute = False
         self.recompute_num_layers = 0  # last n layers of the chunk keep only their input (-1: all)
         self.on_grads_final = None  # callable(prefix): every parameter under `prefix` has its final gradient of the step
@@ -85,6 +88,8 @@ class ModelChunk:
     def _embed(self, ids):
         ops, geo, tp = self.ops, self.geo, self.tp
         w = self.store.p("tok_embeddings.weight")
+        if self.debug_checks:
+            ops.check_ids(ids, 0, self.cfg.padded_vocab_size)
         e = ops.embedding_fwd(ids, w, self.cfg.emb_scale, geo.vocab_start, tp.size > 1)
         if tp.size > 1:
             e = tp.row_output_fwd(e)
@@ -179,6 +184,8 @@ class ModelChunk:
         alpha = 1.0 / cfg.width_mult
         logits = ops.linear_fwd(nff, st.p(st.head_weight_name()), alpha)
         self._cap("fwd", "output", logits)
+        if self.debug_checks:
+            ops.check_ids(labels, 0, cfg.padded_vocab_size)
         nll = ops.cross_entropy_fwd_bwd(logits, labels, mask, grad_scale, geo.vocab_start,
                                         tp.group if tp.size > 1 else None)
         cache_out.update(x_last=x, rstd_f=rstd, nf=nf, nff=nff, dlogits=logits)

@@ -44,6 +44,8 @@ class RoutedOps:
             self.versions[n] = ver
         self.name = default
         self._impls = impls
+        # not a versioned op: the debug input check of whichever implementation runs the model
+        self.check_ids = getattr(impls.get(default), "check_ids", TorchOps.check_ids)
 
     def set_deterministic(self, on: bool) -> None:
         """Forwarded to every implementation that has a deterministic mode (fixed summation orders instead of atomics)."""

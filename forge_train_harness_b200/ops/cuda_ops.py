@@ -45,6 +45,16 @@ def check_status(reset: bool = True) -> None:
 class Sm100Ops:
     name = "sm100"
 
+    # ---- debug input checks ---------------------------------------------
+    @staticmethod
+    def check_ids(ids, lo, hi):
+        """Every id in [lo, hi), else status 7 at the next status read (no host sync here: usable inside a CUDA graph)."""
+        _C.check_ids(ids, int(lo), int(hi))
+
+    @staticmethod
+    def bad_index_position(reset=True):
+        return int(_C.bad_index_position(bool(reset)))
+
     # ---- embedding -------------------------------------------------------
     @staticmethod
     def embedding_fwd(ids, weight, scale, vocab_start=0, sharded=False):

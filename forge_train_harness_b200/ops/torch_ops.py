@@ -42,6 +42,14 @@ class TorchOps:
         return out.to(weight.dtype)
 
     @staticmethod
+    def check_ids(ids, lo, hi):
+        """Debug input check, host side: raises at once (the CUDA version reports through the status word)."""
+        bad = ((ids < lo) | (ids >= hi)).nonzero()
+        if bad.numel():
+            pos = int(bad[0, 0])
+            raise ValueError(f"index {int(ids.reshape(-1)[pos])} at position {pos} lies outside [{lo}, {hi})")
+
+    @staticmethod
     def embedding_bwd(dout, ids, main_grad, scale, vocab_start=0):
         local = ids.long() - vocab_start
         ok = (local >= 0) & (local < main_grad.shape[0])

@@ -107,3 +107,27 @@ def test_kernel_status_stops_the_step_before_it_is_logged_or_saved(tmp_path):
     with pytest.raises(RuntimeError, match="accumulator never committed"):
         tr.train_step(verify=True)
     tr.close()
+
+
+def test_debug_checks_catch_a_corrupt_batch():
+    """``train.debug_checks``: a token id or a label outside the vocabulary stops the step with its position, instead of being
+    skipped like another vocabulary shard's token."""
+    import pytest
+    cfg = tiny_cfg(debug_checks=True).replace(model={"seq_length": 32, "padded_vocab_size": 512})
+    tr = fth.Trainer(cfg, device="cpu")
+    tr.start_data()
+    batch = tr.stager.stage(tr.prefetch.get())
+    tr._fwd_bwd({k: (v.clone() if hasattr(v, "clone") else v) for k, v in batch.items()})   # a clean batch passes
+    bad = {k: (v.clone() if hasattr(v, "clone") else v) for k, v in batch.items()}
+    bad["ids"][7] = 512
+    with pytest.raises(ValueError, match=r"index 512 at position 7 lies outside \[0, 512\)"):
+        tr._fwd_bwd(bad)
+    bad = {k: (v.clone() if hasattr(v, "clone") else v) for k, v in batch.items()}
+    bad["labels"][3] = -1
+    with pytest.raises(ValueError, match="position 3"):
+        tr._fwd_bwd(bad)
+    tr.close()
+    # off by default: the same batch is accepted (the op skips the id), which is what vocabulary parallelism relies on
+    tr2 = fth.Trainer(tiny_cfg().replace(model={"seq_length": 32, "padded_vocab_size": 512}), device="cpu")
+    assert not tr2.chunks[0].debug_checks
+    tr2.close()

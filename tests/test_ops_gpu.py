@@ -290,3 +290,29 @@ def test_bounded_peer_wait_runs_out_and_reports_status(ops):
     torch.cuda.synchronize()
     check_status()
     assert torch.isfinite(y.float()).all()
+
+
+def test_debug_input_check_reports_a_bad_id_through_the_status_word(ops):
+    """An id outside the vocabulary is recorded (status 7 + first bad position) without touching memory; in-range ids, and an
+    id that is merely outside the LOCAL shard range, are not errors; the context keeps working."""
+    from forge_train_harness_b200.ops.cuda_ops import _C, Sm100Ops, check_status
+    _C.read_status(True)
+    Sm100Ops.bad_index_position()
+    ids = torch.randint(0, 1000, (4096,), device="cuda", dtype=torch.int32)
+    Sm100Ops.check_ids(ids, 0, 1000)
+    torch.cuda.synchronize()
+    check_status()
+    assert Sm100Ops.bad_index_position() == -1
+    ids[1234] = 1000
+    ids[3000] = -5
+    Sm100Ops.check_ids(ids, 0, 1000)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="outside its valid range"):
+        check_status()
+    assert Sm100Ops.bad_index_position() == 1234 and Sm100Ops.bad_index_position() == -1   # first bad position; read resets
+    # the kernels themselves stay safe on such input: the embedding writes zeros for it and reads nothing out of range
+    w = rnd(1000, 256)
+    e = ops.embedding_fwd(ids, w, 1.0, 0, False)
+    torch.cuda.synchronize()
+    check_status()
+    assert float(e[1234].abs().max()) == 0.0 and float(e[3000].abs().max()) == 0.0 and torch.isfinite(e.float()).all()
