@@ -151,7 +151,7 @@ __global__ void adamw_push_kernel(float* __restrict__ master, float* __restrict_
   const float gs = *grad_scale;
   const float l = lr * sg.lr_mult;
   const float decay = 1.f - l * weight_decay * sg.wd;
-  const float step = l / bc1;
+  const float step = __fdiv_rn(l, bc1);
   float* w = master + sg.shard_off;
   float* mm = m + sg.shard_off;
   float* vv = v + sg.shard_off;
@@ -169,7 +169,7 @@ __global__ void adamw_push_kernel(float* __restrict__ master, float* __restrict_
       ww[k] *= decay;
       ma[k] += (gg - ma[k]) * (1.f - beta1);
       va[k] = va[k] * beta2 + gg * gg * (1.f - beta2);
-      ww[k] -= step * ma[k] / (sqrtf(va[k]) * rsqrt_bc2 + eps);
+      ww[k] -= __fdiv_rn(step * ma[k], __fsqrt_rn(va[k]) * rsqrt_bc2 + eps);  // IEEE sqrt / divide whatever the build's fast-math flag says
     }
     store8(w + i * 8, ww);
     store8(mm + i * 8, ma);
@@ -191,7 +191,7 @@ __global__ void adamw_push_kernel(float* __restrict__ master, float* __restrict_
     float gg = g[i] * gs, ww = w[i] * decay;
     float ma = mm[i] + (gg - mm[i]) * (1.f - beta1);
     float va = vv[i] * beta2 + gg * gg * (1.f - beta2);
-    ww -= step * ma / (sqrtf(va) * rsqrt_bc2 + eps);
+    ww -= __fdiv_rn(step * ma, __fsqrt_rn(va) * rsqrt_bc2 + eps);
     w[i] = ww; mm[i] = ma; vv[i] = va;
     const __nv_bfloat16 b = __float2bfloat16(ww);
     for (int r = 0; r < world; ++r) reinterpret_cast<__nv_bfloat16*>(params.p[r])[sg.flat_off + i] = b;

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(
       }
     }
     ss = row_sum<TPR>(ss, smem, slot, lane);
-    const float rstd = rsqrtf(ss / (float)H + eps);
+    const float rstd = __frsqrt_rn(__fdiv_rn(ss, (float)H) + eps);  // IEEE-rounded, one per row: independent of the fast-math flag
     if (ok && lane == 0) rstd_out[row] = rstd;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
@@ -472,7 +472,7 @@ __global__ void adamw_segments_kernel(float* __restrict__ master, float* __restr
   const float gs = *grad_scale;
   const float l = lr * sg.lr_mult;
   const float decay = 1.f - l * weight_decay * sg.wd;
-  const float step = l / bc1;
+  const float step = __fdiv_rn(l, bc1);
   float* w = master + sg.shard_off;
   float* mm = m + sg.shard_off;
   float* vv = v + sg.shard_off;
@@ -489,7 +489,7 @@ __global__ void adamw_segments_kernel(float* __restrict__ master, float* __restr
       ww[k] *= decay;
       ma[k] += (ga[k] - ma[k]) * (1.f - beta1);
       va[k] = va[k] * beta2 + ga[k] * ga[k] * (1.f - beta2);
-      ww[k] -= step * ma[k] / (sqrtf(va[k]) * rsqrt_bc2 + eps);
+      ww[k] -= __fdiv_rn(step * ma[k], __fsqrt_rn(va[k]) * rsqrt_bc2 + eps);  // IEEE sqrt / divide whatever the build's fast-math flag says
     }
     reinterpret_cast<float4*>(w)[i] = make_float4(ww[0], ww[1], ww[2], ww[3]);
     reinterpret_cast<float4*>(mm)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
@@ -505,7 +505,7 @@ __global__ void adamw_segments_kernel(float* __restrict__ master, float* __restr
     float gg = g[i] * gs, ww = w[i] * decay;
     float ma = mm[i] + (gg - mm[i]) * (1.f - beta1);
     float va = vv[i] * beta2 + gg * gg * (1.f - beta2);
-    ww -= step * ma / (sqrtf(va) * rsqrt_bc2 + eps);
+    ww -= __fdiv_rn(step * ma, __fsqrt_rn(va) * rsqrt_bc2 + eps);
     w[i] = ww; mm[i] = ma; vv[i] = va;
     if constexpr (sizeof(PT) == 2) p[i] = __float2bfloat16(ww); else p[i] = ww;
   }
