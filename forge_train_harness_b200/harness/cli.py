@@ -2,7 +2,7 @@
 
     python -m forge_train_harness_b200.harness run <suite> [--registry configs/eval/dense_training.toml] [--timeout S] [--arg k=v]
     python -m forge_train_harness_b200.harness guard | anti-proxy | unit | info | doctor | echo-config <toml> | render <gate.toml> ...
-    python -m forge_train_harness_b200.harness budget <suite> | env-probe | resources provision|verify | prefetch <prefix> <dir> | sync push <dest>
+    python -m forge_train_harness_b200.harness sweep [--stage stage1] [--max-gpus N] | budget <suite> | env-probe | resources provision|verify | prefetch <prefix> <dir> | sync push <dest>
     python -m forge_train_harness_b200.harness op-inventory | op-status | op-long <op> --config <toml> [--steps N --window A B --nproc N]
     python -m forge_train_harness_b200.harness lease claim|release|rebind|list ... | job <suite> --outer S [--poll] | loop run|report|fork ... | tools canonical|recipe-env|data-check|capture-batch ...
 
@@ -64,6 +64,12 @@ def main(argv=None) -> int:
     r.add_argument("--artifacts", default=os.path.join(ROOT, ".artifacts", "runs"))
     for name in ("guard", "anti-proxy", "unit", "info", "doctor", "env", "env-probe", "op-inventory", "op-status"):
         sub.add_parser(name)
+    sw = sub.add_parser("sweep", help="run every suite of a stage (optionally only those needing no GPU) and print one table")
+    sw.add_argument("--registry", default=_registry_default())
+    sw.add_argument("--stage", default="stage1")
+    sw.add_argument("--max-gpus", type=int, default=-1, help="skip suites that need more GPUs than this (-1: whatever is visible)")
+    sw.add_argument("--only", default="", help="comma-separated suite names")
+    sw.add_argument("--artifacts", default=os.path.join(ROOT, ".artifacts", "runs"))
     b = sub.add_parser("budget")
     b.add_argument("suite")
     b.add_argument("--registry", default=_registry_default())
@@ -172,6 +178,35 @@ def main(argv=None) -> int:
         for side in ("ref", "ours"):
             print(f"# ---- {side} product ----\n" + render.dumps_product(prods[side]))
         return 0
+    if a.cmd == "sweep":
+        # the reference's env/gate_sweep_torch.sh: every gate of the ladder in milestone order, one line each
+        reg = render.load_toml(a.registry)
+        have = a.max_gpus
+        if have < 0:
+            try:
+                import torch
+                have = torch.cuda.device_count()
+            except Exception:
+                have = 0
+        order = (reg.get(a.stage) or {}).get("milestone_order", [])
+        rank = {m: i for i, m in enumerate(order)}
+        names = [n for n, g in reg.get("evals", {}).items() if g.get("stage", "stage1") == a.stage]
+        if a.only:
+            names = [n for n in names if n in a.only.split(",")]
+        names.sort(key=lambda n: (rank.get(str(reg["evals"][n].get("milestone", "")).split(".")[0], 99), n))
+        rows, failed = [], 0
+        for n in names:
+            g = reg["evals"][n]
+            if int(g.get("gpu_count", 0)) > have and not (have == 0 and "tiny_cpu" in json.dumps(g)):
+                rows.append((n, g.get("milestone", "-"), "skipped", f"needs {g.get('gpu_count')} GPUs, {have} visible"))
+                continue
+            rc = main(["run", n, "--registry", a.registry, "--artifacts", a.artifacts])
+            failed += rc != 0
+            rows.append((n, g.get("milestone", "-"), "passed" if rc == 0 else "FAILED", ""))
+        print("\n| suite | milestone | status | note |\n|---|---|---|---|")
+        for r in rows:
+            print("| " + " | ".join(r) + " |")
+        return 1 if failed else 0
     # run <suite>
     reg = render.load_toml(a.registry)
     gate = reg.get("evals", {}).get(a.suite, {})

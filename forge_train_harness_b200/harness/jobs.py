@@ -304,7 +304,9 @@ def main(argv=None) -> int:
         return _supervise(argv[1])
     ap = argparse.ArgumentParser(prog="gpu_job")
     ap.add_argument("suite")
-    ap.add_argument("--outer", type=float, required=True, help="exec window in seconds, owned by the caller (harness budget)")
+    ap.add_argument("--outer", type=float, default=0.0,
+                    help="exec window in seconds, owned by the caller; default: the suite's `harness budget` plus a 120 s margin "
+                         "for start-up and result write-back (the sum the reference's tools/remote_run.sh passes)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--poll", action="store_true", help="poll the in-flight job of this suite; never submit")
     ap.add_argument("--poll-interval", type=float, default=30.0)
@@ -312,6 +314,12 @@ def main(argv=None) -> int:
     ap.add_argument("--entry", default="", help="shell line to run instead of `harness run <suite>`")
     ap.add_argument("extra", nargs="*")
     a = ap.parse_args(argv)
+    if a.outer <= 0:
+        r = subprocess.run([sys.executable, "-m", "forge_train_harness_b200.harness", "budget", a.suite], capture_output=True, text=True, cwd=ROOT)
+        if r.returncode != 0 or not r.stdout.strip().isdigit():
+            print(f"gpu_job: no budget for suite {a.suite!r}: {r.stderr.strip()}", file=sys.stderr)
+            return 64
+        a.outer = float(r.stdout.strip()) + 120.0
     sched = LocalScheduler()
     if a.poll:
         return poll_suite(sched, suite=a.suite, outer=a.outer, poll_interval_s=a.poll_interval)

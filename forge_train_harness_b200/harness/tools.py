@@ -3,6 +3,9 @@
 * ``canonical``  — write ``canonical_state_fp32.pt`` for a model shape: every full tensor from one seeded CPU generator in the
   reference's parameter order, the hand-off file both sides of a gate can start from (tools/bootstrap_canonical.py; the
   reference keeps two, ``ones/`` with norm weights 1 and ``no1/`` with 0.97, chosen by a gate's ``forge_init_ones``).
+* ``canonical-preflight`` — before a gate spends GPU time: the canonical file exists, holds exactly the model's parameters with
+  the right shapes in fp32, is finite, and (when a ``.sha256`` file sits beside it) has the recorded digest
+  (tools/canonical_preflight.sh, evals/canonical_preflight.py).
 * ``recipe-env`` — project a training recipe TOML into shell lines ``export VAR="${VAR:-value}"``: the environment wins, the
   recipe supplies defaults; an unknown top-level table is an error, so no key silently never reaches the shell
   (tools/train_recipe_to_env.py).
@@ -12,6 +15,7 @@
   workspace, so that profiling runs a fixed input and needs nothing from outside the tree (tools/capture_profile_batch.py).
 
     python -m forge_train_harness_b200.harness.tools canonical --model minicpm4_0.5b --out ckpt_root [--init-ones 0|1] [--layers N]
+    python -m forge_train_harness_b200.harness.tools canonical-preflight --model minicpm4_0.5b --file ckpt_root/ones/canonical_state_fp32.pt
     python -m forge_train_harness_b200.harness.tools recipe-env configs/eval/recipe_wsd_sft_tiny.toml
     python -m forge_train_harness_b200.harness.tools data-check --config run.toml [--dp 2] [--batches 16]
     python -m forge_train_harness_b200.harness.tools capture-batch --config run.toml --out profiles_in/captured_batch.pt
@@ -41,6 +45,41 @@ def write_canonical(model_cfg, out_root: str, seed: int = 1234, init_ones: bool 
     torch.save(state, tmp)
     os.replace(tmp, path)
     return path
+
+
+def canonical_preflight(model_cfg, path: str) -> dict:
+    import torch
+
+    from ..models import params as P
+    problems = []
+    if not os.path.isfile(path):
+        return {"passed": False, "problems": [f"{path} does not exist"]}
+    side = path + ".sha256"
+    digest = hashlib.sha256()
+    with open(path, "rb") as f:
+        for chunk in iter(lambda: f.read(1 << 24), b""):
+            digest.update(chunk)
+    if os.path.isfile(side):
+        want = open(side).read().split()[0].strip()
+        if want != digest.hexdigest():
+            problems.append(f"sha256 {digest.hexdigest()[:16]}... differs from the recorded {want[:16]}...")
+    state = torch.load(path, map_location="cpu", weights_only=True, mmap=True)
+    specs = {s.name: s for s in P.full_param_specs(model_cfg)}
+    for name in sorted(set(specs) - set(state)):
+        problems.append(f"missing {name}")
+    for name in sorted(set(state) - set(specs)):
+        problems.append(f"unexpected {name}")
+    for name, spec in specs.items():
+        t = state.get(name)
+        if t is None:
+            continue
+        if tuple(t.shape) != tuple(spec.full_shape):
+            problems.append(f"{name}: shape {tuple(t.shape)}, model wants {tuple(spec.full_shape)}")
+        elif t.dtype != torch.float32:
+            problems.append(f"{name}: dtype {t.dtype}, want float32")
+        elif not bool(torch.isfinite(t).all()):
+            problems.append(f"{name}: not finite")
+    return {"passed": not problems, "problems": problems[:20], "sha256": digest.hexdigest(), "tensors": len(state)}
 
 
 def recipe_env_lines(recipe: dict) -> list[str]:
@@ -110,6 +149,10 @@ def main(argv=None) -> int:
     c.add_argument("--seed", type=int, default=1234)
     c.add_argument("--init-ones", type=int, choices=[0, 1], required=True)
     c.add_argument("--layers", type=int, default=0)
+    cp = sub.add_parser("canonical-preflight")
+    cp.add_argument("--model", required=True)
+    cp.add_argument("--file", required=True)
+    cp.add_argument("--layers", type=int, default=0)
     r = sub.add_parser("recipe-env")
     r.add_argument("recipe")
     d = sub.add_parser("data-check")
@@ -127,6 +170,13 @@ def main(argv=None) -> int:
             m = dataclasses.replace(m, num_layers=a.layers)
         print(write_canonical(m, a.out, a.seed, bool(a.init_ones)))
         return 0
+    if a.cmd == "canonical-preflight":
+        m = schema.preset(a.model)
+        if a.layers:
+            m = dataclasses.replace(m, num_layers=a.layers)
+        res = canonical_preflight(m, a.file)
+        print(json.dumps(res, indent=1))
+        return 0 if res["passed"] else 1
     if a.cmd == "recipe-env":
         with open(a.recipe, "rb") as f:
             try:

@@ -86,3 +86,35 @@ def test_data_check_and_capture_batch(tmp_path):
         assert not tools.data_check(cfg, 1, 4)["passed"]
     finally:
         sources.MegatronBinary.__next__ = real
+
+
+def test_canonical_preflight_finds_what_would_waste_a_gate_run(tmp_path):
+    m = fth.preset("tiny")
+    path = tools.write_canonical(m, str(tmp_path), seed=3, init_ones=True)
+    ok = tools.canonical_preflight(m, path)
+    assert ok["passed"] and ok["tensors"] == len(list(fth.models.params.full_param_specs(m))) if hasattr(fth, "models") else ok["passed"]
+    open(path + ".sha256", "w").write(ok["sha256"] + "  canonical_state_fp32.pt\n")
+    assert tools.canonical_preflight(m, path)["passed"]
+    state = torch.load(path, weights_only=True)
+    state["layers.0.wo.weight"][0, 0] = float("nan")
+    state["layers.1.w2.weight"] = state["layers.1.w2.weight"][:, :-1].contiguous()
+    del state["norm.weight"]
+    torch.save(state, path)
+    bad = tools.canonical_preflight(m, path)
+    text = " ".join(bad["problems"])
+    assert not bad["passed"] and "sha256" in text and "missing norm.weight" in text and "not finite" in text and "layers.1.w2.weight: shape" in text
+    import dataclasses
+    assert not tools.canonical_preflight(dataclasses.replace(m, num_layers=3), str(tmp_path / "nope.pt"))["passed"]
+
+
+def test_gate_sweep_runs_the_cpu_suites_in_milestone_order(tmp_path):
+    from forge_train_harness_b200.harness.cli import main as cli_main
+    import contextlib, io
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        rc = cli_main(["sweep", "--only", "multistep,production-train,dptp", "--max-gpus", "0", "--artifacts", str(tmp_path / "runs")])
+    table = buf.getvalue().split("| suite | milestone | status | note |")[-1]
+    assert rc == 0, buf.getvalue()[-3000:]
+    lines = [ln for ln in table.splitlines() if ln.startswith("| ") and "---" not in ln]
+    assert [ln.split("|")[1].strip() for ln in lines] == ["multistep", "dptp", "production-train"]   # milestone order
+    assert "passed" in lines[0] and "skipped" in lines[1] and "needs 4 GPUs" in lines[1] and "passed" in lines[2]
