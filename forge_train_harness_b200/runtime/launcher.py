@@ -64,10 +64,34 @@ def wait_with_fast_fail(procs, poll_s: float = 0.5, grace_s: float = 30.0, sleep
     return failed
 
 
+def profile_wrap(argv: list[str], rank: int, env: dict) -> tuple[list[str], dict]:
+    """Profile snapshot behind ONE variable (evals/scripts/launch_dp.py:35-56): with ``NSYS_PROFILE=1`` rank 0 alone is
+    profiled, the other ranks run as they are.  Where an ``nsys`` executable exists (``NSYS_BIN`` or PATH) rank 0 is wrapped
+    in ``nsys profile`` writing ``$NSYS_OUTPUT`` (default ``profile_out/rank0``); where it does not, the same variable turns
+    on the engine's own one-step profiler (``utils/step_profile.py``: ``FORGE_PROFILE_STEP``, default step 5) — the per-kernel
+    summary is the same table either way."""
+    if env.get("NSYS_PROFILE", "0") != "1" or rank != 0:
+        return argv, env
+    import shutil
+    nsys = env.get("NSYS_BIN") or shutil.which("nsys")
+    env = dict(env)
+    if nsys:
+        out = env.get("NSYS_OUTPUT", os.path.join("profile_out", "rank0"))
+        os.makedirs(os.path.dirname(os.path.abspath(out)), exist_ok=True)
+        return [nsys, "profile", "--trace=cuda,nvtx", "--sample=none", "--cpuctxsw=none", "--force-overwrite=true",
+                "-o", out] + list(argv), env
+    env.setdefault("FORGE_PROFILE_STEP", "5")
+    env.setdefault("FORGE_PROFILE_RANK", "0")
+    env.setdefault("FORGE_PROFILE_DIR", os.path.dirname(env.get("NSYS_OUTPUT", "")) or "profile_out")
+    return argv, env
+
+
 def launch(argv: list[str], nproc: int, master_port="auto", env=None, stdout=None, stderr=None) -> int:
     port = free_port() if master_port in ("auto", None, 0) else int(master_port)
-    procs = [subprocess.Popen(argv, env=rank_env(r, nproc, port, env), stdout=stdout if r == 0 else subprocess.DEVNULL,
-                              stderr=stderr) for r in range(nproc)]
+    procs = []
+    for r in range(nproc):
+        cmd, renv = profile_wrap(list(argv), r, rank_env(r, nproc, port, env))
+        procs.append(subprocess.Popen(cmd, env=renv, stdout=stdout if r == 0 else subprocess.DEVNULL, stderr=stderr))
     return wait_with_fast_fail(procs)
 
 

@@ -94,3 +94,29 @@ def test_sigkill_mid_phase_then_restart_matches_clean_run(tmp_path):
     assert v["passed"], v
     assert V.production(os.path.join(main_root, "sft"), [10, 12])["passed"]
     assert not V.production(os.path.join(main_root, "sft"), [11])["passed"]
+
+
+def test_profile_snapshot_wraps_rank0_only_behind_one_variable(tmp_path):
+    """NSYS_PROFILE=1: rank 0 runs under the profiler executable when there is one, else the engine's own one-step profiler is
+    switched on for it; the other ranks are untouched (evals/scripts/launch_dp.py:35-56)."""
+    import stat
+    from forge_train_harness_b200.runtime import launcher
+    argv = [sys.executable, "-c", "pass"]
+    base = {"PATH": "/nonexistent", "NSYS_PROFILE": "1", "NSYS_OUTPUT": str(tmp_path / "prof" / "rank0")}
+    cmd, env = launcher.profile_wrap(argv, 1, dict(base))
+    assert cmd == argv and "FORGE_PROFILE_STEP" not in env                      # not rank 0: as it is
+    cmd, env = launcher.profile_wrap(argv, 0, dict(base))
+    assert cmd == argv and env["FORGE_PROFILE_STEP"] == "5" and env["FORGE_PROFILE_RANK"] == "0" and env["FORGE_PROFILE_DIR"] == str(tmp_path / "prof")
+    assert launcher.profile_wrap(argv, 0, {"PATH": "/nonexistent"}) == (argv, {"PATH": "/nonexistent"})  # variable unset: nothing
+    # with a profiler executable: rank 0's command line is wrapped, and the wrapped program still runs with its rank env
+    fake = tmp_path / "nsys"
+    fake.write_text("#!/bin/bash\nout=\"\"; while [ $# -gt 0 ]; do if [ \"$1\" = -o ]; then out=$2; shift 2; break; fi; shift; done\n"
+                    "echo \"wrapped rank=$RANK\" > \"$out.txt\"\nexec \"$@\"\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    marks = tmp_path / "marks"
+    marks.mkdir()
+    prog = [sys.executable, "-c", f"import os; open(os.path.join({str(marks)!r}, os.environ['RANK']), 'w').write('ran')"]
+    env = dict(os.environ, NSYS_PROFILE="1", NSYS_BIN=str(fake), NSYS_OUTPUT=str(tmp_path / "prof" / "rank0"))
+    assert launcher.launch(prog, 2, env=env) == 0
+    assert sorted(os.listdir(marks)) == ["0", "1"]
+    assert open(str(tmp_path / "prof" / "rank0") + ".txt").read().strip() == "wrapped rank=0"
