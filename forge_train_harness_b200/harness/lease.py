@@ -183,7 +183,7 @@ class LocalGpuProvider:
 
     @staticmethod
     def ordinals(handle: str) -> list[int]:
-        if handle == "gpu-none":
+        if handle.startswith("gpu-none"):   # a GPU-less gateway lease ("gpu-none@<loop>")
             return []
         if not handle.startswith("gpu-"):
             raise LeaseError(f"not a local GPU lease handle: {handle!r}")

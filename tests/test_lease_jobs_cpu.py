@@ -48,6 +48,21 @@ def test_local_claims_are_exclusive_idempotent_and_aligned(lease_root):
         a.wait(), b.wait()
 
 
+def test_gpu_less_gateway_leases_coexist_with_gpu_leases(lease_root):
+    a = _sleeper()
+    try:
+        p = lease.LocalGpuProvider(total_gpus=2, holder_pid=a.pid)
+        g1 = lease.claim("gpu", spec=lease.LeaseSpec(0), loop_id="gw1", provider=p)
+        g2 = lease.claim("gpu", spec=lease.LeaseSpec(0), loop_id="gw2", provider=p)
+        assert g1 == "gpu-none@gw1" and g2 == "gpu-none@gw2" and p.env(g1) == {"CUDA_VISIBLE_DEVICES": ""}
+        assert lease.claim("gpu", spec=lease.LeaseSpec(2), loop_id="worker", provider=p) == "gpu-0-1"   # gateways hold no ordinals
+        lease.release("gpu", loop_id="gw1", provider=p)
+        assert sorted(lease.holders("gpu")) == ["gpu-0-1", "gpu-none@gw2"]
+    finally:
+        a.kill()
+        a.wait()
+
+
 def test_dead_holder_is_reclaimed(lease_root):
     a = _sleeper()
     pa = lease.LocalGpuProvider(total_gpus=2, holder_pid=a.pid)
