@@ -13,6 +13,13 @@ int fth_rmsnorm_fwd(const void* x, const void* res, float res_scale, const void*
 int fth_rmsnorm_bwd_blocks(int M, int H);
 int fth_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                     float* dw_partial, float* dw_main_grad, int M, int H, float out_scale, cudaStream_t stream);
+// per-head q/k RMSNorm on the packed QKV layout (d = 64 or 128).  fwd writes a new tensor (v heads copied) + rstd [M, n_kv, g+1];
+// bwd is in place on dqkv and accumulates the two weight gradients; `partial` = fth_qk_norm_blocks() x 2 x d floats.
+int fth_qk_norm_blocks(int M, int n_kv, int g, int d);
+int fth_qk_norm_fwd(const void* qkv, const void* wq, const void* wk, void* out, float* rstd, int M, int n_kv, int g, int d,
+                    float eps, cudaStream_t stream);
+int fth_qk_norm_bwd(void* dqkv, const void* qkv_pre, const float* rstd, const void* wq, const void* wk, float* partial,
+                    float* dwq_main, float* dwk_main, int M, int n_kv, int g, int d, cudaStream_t stream);
 int fth_rope(void* qkv, const float* table, int M, int S, int n_kv, int g, int d, float sign, cudaStream_t stream);
 int fth_swiglu_fwd(const void* gu, void* out, int M, int F, cudaStream_t stream);
 int fth_swiglu_bwd(const void* dinter, const void* gu, void* dgu, int M, int F, cudaStream_t stream);

@@ -110,6 +110,41 @@ void rope_(at::Tensor& qkv, const at::Tensor& table, int64_t S, int64_t n_kv, in
                  cur_stream()), "rope");
 }
 
+// Per-head q/k RMSNorm (Qwen3 variant) on the packed QKV activation.  Returns (normalised copy, rstd [M, n_kv, g + 1]).
+std::vector<at::Tensor> qk_norm_fwd(const at::Tensor& qkv, const at::Tensor& wq, const at::Tensor& wk, double eps, int64_t n_kv,
+                                    int64_t g, int64_t d) {
+  need_bf16(qkv, "qkv");
+  need_bf16(wq, "q_norm weight");
+  need_bf16(wk, "k_norm weight");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.is_contiguous() && qkv.size(1) == n_kv * (g + 2) * d && wq.numel() == d && wk.numel() == d,
+              "qk_norm_fwd shape mismatch");
+  const int M = qkv.size(0);
+  at::Tensor out = at::empty_like(qkv);
+  at::Tensor rstd = at::empty({M, n_kv, g + 1}, qkv.options().dtype(at::kFloat));
+  check(fth_qk_norm_fwd(qkv.data_ptr(), wq.data_ptr(), wk.data_ptr(), out.data_ptr(), rstd.data_ptr<float>(), M, (int)n_kv, (int)g,
+                        (int)d, (float)eps, cur_stream()), "qk_norm_fwd");
+  return {out, rstd};
+}
+
+// In place on dqkv; accumulates into the two fp32 main-grad vectors.
+void qk_norm_bwd_(at::Tensor& dqkv, const at::Tensor& qkv_pre, const at::Tensor& rstd, const at::Tensor& wq, const at::Tensor& wk,
+                  at::Tensor& dwq_main, at::Tensor& dwk_main, int64_t n_kv, int64_t g, int64_t d) {
+  need_bf16(dqkv, "dqkv");
+  need_bf16(qkv_pre, "qkv_pre");
+  need_f32(rstd, "rstd");
+  need_f32(dwq_main, "q_norm main_grad");
+  need_f32(dwk_main, "k_norm main_grad");
+  const int M = dqkv.size(0);
+  TORCH_CHECK(dqkv.is_contiguous() && qkv_pre.is_contiguous() && dqkv.sizes() == qkv_pre.sizes() && dqkv.size(1) == n_kv * (g + 2) * d &&
+              rstd.numel() == (int64_t)M * n_kv * (g + 1) && dwq_main.numel() == d && dwk_main.numel() == d, "qk_norm_bwd shape mismatch");
+  const int nb = fth_qk_norm_blocks(M, (int)n_kv, (int)g, (int)d);
+  TORCH_CHECK(nb >= 0, "qk_norm: head_dim must be 64 or 128");
+  at::Tensor partial = at::empty({2 * (int64_t)std::max(nb, 1) * d}, rstd.options());
+  check(fth_qk_norm_bwd(dqkv.data_ptr(), qkv_pre.data_ptr(), rstd.data_ptr<float>(), wq.data_ptr(), wk.data_ptr(),
+                        partial.data_ptr<float>(), dwq_main.data_ptr<float>(), dwk_main.data_ptr<float>(), M, (int)n_kv, (int)g, (int)d,
+                        cur_stream()), "qk_norm_bwd");
+}
+
 at::Tensor swiglu_fwd(const at::Tensor& gu) {
   need_bf16(gu, "gate_up");
   const int M = gu.size(0), F = gu.size(1) / 2;
@@ -438,6 +473,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("residual_add", &residual_add);
+  m.def("qk_norm_fwd", &qk_norm_fwd);
+  m.def("qk_norm_bwd_", &qk_norm_bwd_);
   m.def("check_ids", &check_ids);
   m.def("bad_index_position", &bad_index_position);
   m.def("embedding_fwd", &embedding_fwd);

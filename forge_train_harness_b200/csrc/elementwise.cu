@@ -189,6 +189,109 @@ __global__ void colsum_add_kernel(const float* __restrict__ partial, float* __re
   }
 }
 
+// ---- per-head q/k RMSNorm (Qwen3 variant), on the packed kv-group-major QKV layout ------------------------------------------
+// A head vector of d = 64 / 128 bf16 is owned by d / 8 neighbouring lanes (8 or 16), each holding one 16-byte vector; the sum
+// of squares is combined with xor shuffles inside that lane group.  v heads pass through.  Every lane of a warp runs the
+// shuffles (lanes past the end, and lanes on a v head, feed zeros / ignore the result), so no shuffle sits in divergent code.
+__global__ void qk_norm_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                                   const __nv_bfloat16* __restrict__ wk, __nv_bfloat16* __restrict__ out,
+                                   float* __restrict__ rstd_out, int M, int n_kv, int g, int d, float eps) {
+  const int tph = d / 8, hpr = n_kv * (g + 2);
+  const size_t total = (size_t)M * hpr * tph, stride = (size_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it - lane < total; it += stride) {
+    const bool live = it < total;
+    const size_t slot = live ? it / tph : 0;
+    const int vec = (int)(it % tph);
+    const size_t row = slot / hpr;
+    const int hs = (int)(slot % hpr), hh = hs % (g + 2);
+    const size_t off = (row * hpr + hs) * (size_t)d + vec * 8;
+    float f[8];
+    if (live) load8(qkv + off, f);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    for (int o = tph / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!live) continue;
+    if (hh <= g) {
+      const float r = __frsqrt_rn(__fdiv_rn(ss, (float)d) + eps);
+      float w[8];
+      load8((hh < g ? wq : wk) + vec * 8, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * r * w[i];
+      if (vec == 0) rstd_out[(row * n_kv + hs / (g + 2)) * (size_t)(g + 1) + hh] = r;
+    }
+    store8(out + off, f);
+  }
+}
+
+// Backward, in place on dqkv: dx = rstd * (g*w - xhat * mean(g*w*xhat)) for q and k heads; v heads untouched.  Weight gradients:
+// every thread keeps its 8 columns' sums for q heads and for the k head in registers over all rows it visits (its column
+// position never changes: the grid stride is a multiple of the lane-group size), the block combines them in a fixed order
+// in shared memory and writes one partial row per block; colsum_add_kernel adds the partial rows into main_grad.
+__global__ void qk_norm_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv_pre,
+                                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ wq,
+                                   const __nv_bfloat16* __restrict__ wk, float* __restrict__ partial_q,
+                                   float* __restrict__ partial_k, int M, int n_kv, int g, int d) {
+  __shared__ float red[256][17];
+  const int tph = d / 8, hpr = n_kv * (g + 2);
+  const size_t total = (size_t)M * hpr * tph, stride = (size_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int vec = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) % tph);
+  float wqv[8], wkv[8], accq[8], acck[8];
+  load8(wq + vec * 8, wqv);
+  load8(wk + vec * 8, wkv);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) accq[i] = acck[i] = 0.f;
+  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it - lane < total; it += stride) {
+    const bool live = it < total;
+    const size_t slot = live ? it / tph : 0;
+    const size_t row = slot / hpr;
+    const int hs = (int)(slot % hpr), hh = hs % (g + 2);
+    const bool normed = live && hh <= g;
+    const size_t off = (row * hpr + hs) * (size_t)d + vec * 8;
+    float gq[8], x[8];
+    float r = 0.f, dot = 0.f;
+    if (normed) {
+      load8(dqkv + off, gq);
+      load8(qkv_pre + off, x);
+      r = rstd[(row * n_kv + hs / (g + 2)) * (size_t)(g + 1) + hh];
+      const bool is_q = hh < g;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[i] *= r;                       // xhat
+        const float dwc = gq[i] * x[i];  // weight-gradient contribution
+        accq[i] += is_q ? dwc : 0.f;
+        acck[i] += is_q ? 0.f : dwc;
+        gq[i] *= is_q ? wqv[i] : wkv[i];  // g * w
+        dot += gq[i] * x[i];
+      }
+    }
+    for (int o = tph / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (normed) {
+      const float mean = __fdiv_rn(dot, (float)d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gq[i] = r * (gq[i] - x[i] * mean);
+      store8(dqkv + off, gq);
+    }
+  }
+  // block combine: thread t holds columns vec(t)*8 .. +8; threads t, t + tph, t + 2 tph, ... share a column group
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { red[threadIdx.x][i] = accq[i]; red[threadIdx.x][8 + i] = acck[i]; }
+  __syncthreads();
+  if ((int)threadIdx.x < 2 * d) {
+    const int which = threadIdx.x / d, col = threadIdx.x % d;   // 0: q columns, 1: k columns
+    const int v0 = col / 8, e = col % 8;
+    float a = 0.f;
+    for (int t = v0; t < (int)blockDim.x; t += tph) a += red[t][which * 8 + e];
+    (which ? partial_k : partial_q)[(size_t)blockIdx.x * d + col] = a;
+  }
+}
+
 // In-place rotate-half RoPE on the q and k heads of the packed kv-group-major QKV activation.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ table, int M, int S,
                             int n_kv, int g, int d, float sign) {
@@ -614,6 +717,37 @@ int fth_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   FTH_ROW_DISPATCH_WIDE(rmsnorm_bwd_kernel, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
                    (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, M, H, out_scale);
   colsum_add_kernel<<<(H + 31) / 32, dim3(32, 32), 0, stream>>>(dw_partial, dw_main_grad, grid, H);
+  return 0;
+}
+
+int fth_qk_norm_blocks(int M, int n_kv, int g, int d) {
+  if (d != 64 && d != 128) return -1;
+  size_t total = (size_t)M * n_kv * (g + 2) * (d / 8);
+  return (int)min((total + 255) / 256, (size_t)num_sms() * 8);
+}
+
+int fth_qk_norm_fwd(const void* qkv, const void* wq, const void* wk, void* out, float* rstd, int M, int n_kv, int g, int d,
+                    float eps, cudaStream_t stream) {
+  const int grid = fth_qk_norm_blocks(M, n_kv, g, d);
+  if (grid < 0) return -1;
+  if (grid == 0) return 0;
+  qk_norm_fwd_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk,
+                                               (__nv_bfloat16*)out, rstd, M, n_kv, g, d, eps);
+  return 0;
+}
+
+// partial: fth_qk_norm_blocks(...) x 2 x d floats of scratch (q rows first, then k rows)
+int fth_qk_norm_bwd(void* dqkv, const void* qkv_pre, const float* rstd, const void* wq, const void* wk, float* partial,
+                    float* dwq_main, float* dwk_main, int M, int n_kv, int g, int d, cudaStream_t stream) {
+  const int grid = fth_qk_norm_blocks(M, n_kv, g, d);
+  if (grid < 0) return -1;
+  if (grid == 0) return 0;
+  float* pq = partial;
+  float* pk = partial + (size_t)grid * d;
+  qk_norm_bwd_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)dqkv, (const __nv_bfloat16*)qkv_pre, rstd,
+                                               (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk, pq, pk, M, n_kv, g, d);
+  colsum_add_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream>>>(pq, dwq_main, grid, d);
+  colsum_add_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream>>>(pk, dwk_main, grid, d);
   return 0;
 }
 

@@ -131,6 +131,18 @@ class Sm100Ops:
         _C.rope_(qkv, table, seq_len, n_kv, g, d, 1.0)
         return qkv
 
+    # ---- per-head q/k RMSNorm (Qwen3 variant) --------------------------------
+    @staticmethod
+    def qk_norm_fwd(qkv, wq, wk, eps, n_kv, g, d):
+        out, rstd = _C.qk_norm_fwd(qkv, wq, wk, float(eps), int(n_kv), int(g), int(d))
+        return out, rstd
+
+    @staticmethod
+    def qk_norm_bwd(dqkv, qkv_pre, rstd, wq, wk, dwq_main, dwk_main, n_kv, g, d):
+        """In place on ``dqkv`` (returned); the two weight gradients are accumulated into the fp32 main-grad vectors."""
+        _C.qk_norm_bwd_(dqkv, qkv_pre, rstd, wq, wk, dwq_main, dwk_main, int(n_kv), int(g), int(d))
+        return dqkv
+
     @staticmethod
     def rope_bwd_(dqkv, table, seq_len, n_kv, g, d):
         _C.rope_(dqkv, table, seq_len, n_kv, g, d, -1.0)

@@ -316,3 +316,37 @@ def test_debug_input_check_reports_a_bad_id_through_the_status_word(ops):
     torch.cuda.synchronize()
     check_status()
     assert float(e[1234].abs().max()) == 0.0 and float(e[3000].abs().max()) == 0.0 and torch.isfinite(e.float()).all()
+
+
+@pytest.mark.parametrize("nkv,g,d,M", [(8, 2, 128, 1000), (2, 8, 64, 777), (1, 1, 64, 5)])
+def test_qk_norm(ops, nkv, g, d, M):
+    """Per-head q/k RMSNorm on the packed QKV layout (Qwen3 variant) against the fp32 PyTorch op: forward, rstd, backward in
+    place, both weight gradients (accumulated), v heads untouched, and bitwise repeatable (no atomics)."""
+    torch.manual_seed(0)
+    qkv, dq = rnd(M, nkv * (g + 2) * d, scale=2.0), rnd(M, nkv * (g + 2) * d)
+    wq, wk = (1.0 + 0.3 * torch.randn(d, device="cuda")).bfloat16(), (1.0 + 0.3 * torch.randn(d, device="cuda")).bfloat16()
+    out, rstd = ops.qk_norm_fwd(qkv, wq, wk, 1e-6, nkv, g, d)
+    ref_out, ref_rstd = T.qk_norm_fwd(qkv.float(), wq.float(), wk.float(), 1e-6, nkv, g, d)
+    assert out.data_ptr() != qkv.data_ptr() and tuple(rstd.shape) == (M, nkv, g + 1)
+    assert (rstd - ref_rstd).abs().max() <= 1e-5 * ref_rstd.abs().max()
+    rel = (out.float() - ref_out).norm() / ref_out.norm()
+    assert rel < 3e-3, float(rel)                                   # one bf16 rounding of the output
+    v_in = qkv.view(M, nkv, g + 2, d)[:, :, g + 1]
+    assert torch.equal(out.view(M, nkv, g + 2, d)[:, :, g + 1], v_in)  # v heads pass through bit for bit
+    gq0, gk0 = torch.randn(d, device="cuda"), torch.randn(d, device="cuda")
+    gq, gk = gq0.clone(), gk0.clone()
+    rq, rk = gq0.clone(), gk0.clone()
+    ref_dx = T.qk_norm_bwd(dq.float(), qkv.float(), ref_rstd, wq.float(), wk.float(), rq, rk, nkv, g, d)
+    d_in = dq.clone()
+    got = ops.qk_norm_bwd(d_in, qkv, rstd, wq, wk, gq, gk, nkv, g, d)
+    assert got.data_ptr() == d_in.data_ptr()                        # in place
+    rel = (got.float() - ref_dx).norm() / ref_dx.norm()
+    assert rel < 3e-3, float(rel)
+    assert torch.equal(got.view(M, nkv, g + 2, d)[:, :, g + 1], dq.view(M, nkv, g + 2, d)[:, :, g + 1])
+    for a, b, start in ((gq, rq, gq0), (gk, rk, gk0)):
+        assert ((a - start) - (b - start)).norm() <= 2e-3 * (b - start).norm() + 1e-4, float(((a - start) - (b - start)).norm())
+    # run twice: identical bits
+    d2, gq2, gk2 = dq.clone(), gq0.clone(), gk0.clone()
+    ops.qk_norm_bwd(d2, qkv, rstd, wq, wk, gq2, gk2, nkv, g, d)
+    out2, rstd2 = ops.qk_norm_fwd(qkv, wq, wk, 1e-6, nkv, g, d)
+    assert torch.equal(d2, got) and torch.equal(gq2, gq) and torch.equal(gk2, gk) and torch.equal(out2, out) and torch.equal(rstd2, rstd)
