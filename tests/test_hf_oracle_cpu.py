@@ -49,3 +49,38 @@ def test_training_trajectory_matches_the_hf_oracle(tmp_path):
     assert res["passed"] and res["first_step"]["rel_diff"] < 1e-6 and res["trend"]["mean_rel_diff"] < 2e-4, res
     gn = res["grad_norm_first"]
     assert abs(gn["ref"] - gn["ours"]) / gn["ref"] < 1e-5
+
+
+def test_exported_checkpoint_loads_into_the_hf_model_and_gives_the_same_loss(tmp_path, monkeypatch):
+    """A trained checkpoint exported under HF names (``python -m forge_train_harness_b200.ckpt.hf_names``) is a drop-in state
+    dict of the bundled ``MiniCPMForCausalLM``: strict load, same loss on the same batch."""
+    why = hf_oracle.available()
+    if why:
+        pytest.skip(why)
+    from forge_train_harness_b200.ckpt import manager
+    monkeypatch.setenv("HF_MODULES_CACHE", str(tmp_path / "hf_modules"))
+    m = fth.ModelConfig(name="exp", num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=4, num_query_groups=2, head_dim=64,
+                        seq_length=64, padded_vocab_size=512, norm_epsilon=1e-6, tie_embeddings=False)
+    cfg = fth.RunConfig(model=m, optim=fth.OptimConfig(lr=2e-3, lr_schedule="constant"),
+                        train=fth.TrainConfig(num_steps=2, micro_batch_size=2, seed=3, dtype="fp32", cuda_graph=False),
+                        data=fth.DataConfig(prefetch_size=0))
+    tr = fth.Trainer(cfg, device="cpu")
+    tr.start_data()
+    tr.train_step()
+    tr.train_step()
+    manager.save(tr, str(tmp_path / "ckpt"))
+    out = tmp_path / "hf_state.pt"
+    r = subprocess.run([sys.executable, "-m", "forge_train_harness_b200.ckpt.hf_names", str(tmp_path / "ckpt"), str(out), "--dtype", "fp32"],
+                       cwd=ROOT, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    hf, _ = hf_oracle.build_model(m, 0, "cpu", torch.float32)
+    hf.load_state_dict(torch.load(out, weights_only=True), strict=True)
+    batch = tr.stager.stage(tr.prefetch.get())
+    batch = {k: (v.clone() if hasattr(v, "clone") else v) for k, v in batch.items()}
+    tr.store.zero_grad()
+    stats = tr._fwd_bwd(batch)
+    logits = hf(input_ids=batch["ids"].long().view(2, 64)).logits
+    nll = torch.nn.functional.cross_entropy(logits.view(-1, 512).float(), batch["labels"].long().view(-1), reduction="none")
+    ref = float((nll * batch["mask"].float().view(-1)).sum().detach())
+    assert abs(float(stats[0]) - ref) / ref < 2e-6, (float(stats[0]), ref)
+    tr.close()
