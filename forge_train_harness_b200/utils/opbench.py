@@ -137,6 +137,23 @@ def main(argv=None):
     if want("rope"):
         qkv, tab = r(M, cfg.qkv_dim), rope_table(S, d, cfg.rotary_base, dev)
         rec("rope", timeit(lambda: ops.rope_fwd_(qkv, tab, S, nkv, g, d), flush=flush), bytes_=2.0 * M * (cfg.q_dim + cfg.kv_dim) * 2)
+    if want("qknorm"):
+        # per-head q/k RMSNorm (Qwen3 variant): reads and writes the whole packed QKV forward; backward reads dqkv and the
+        # pre-norm copy of the q / k heads and rewrites the q / k heads of dqkv in place
+        from ..ops.torch_ops import TorchOps
+        qkv, dq = r(M, cfg.qkv_dim), r(M, cfg.qkv_dim)
+        wq, wk = r(d), r(d)
+        _, rstd = ops.qk_norm_fwd(qkv, wq, wk, 1e-6, nkv, g, d)
+        gq, gk = torch.zeros(d, device=dev), torch.zeros(d, device=dev)
+        qk_bytes = M * (cfg.q_dim + cfg.kv_dim) * 2
+        fns = {"qk_norm_fwd": lambda: ops.qk_norm_fwd(qkv, wq, wk, 1e-6, nkv, g, d),
+               "qk_norm_bwd": lambda: ops.qk_norm_bwd(dq, qkv, rstd, wq, wk, gq, gk, nkv, g, d),
+               "qk_norm_fwd_pytorch_ops": lambda: TorchOps.qk_norm_fwd(qkv, wq, wk, 1e-6, nkv, g, d),
+               "qk_norm_bwd_pytorch_ops": lambda: TorchOps.qk_norm_bwd(dq, qkv, rstd, wq, wk, gq, gk, nkv, g, d)}
+        by = {"qk_norm_fwd": 2.0 * M * cfg.qkv_dim * 2, "qk_norm_bwd": 3.0 * qk_bytes}
+        for k, t in timeit_many(fns, flush=flush).items():
+            rec(k, t, bytes_=by.get(k.replace("_pytorch_ops", ""), 0.0))
+        del qkv, dq
     if want("ce"):
         lg = r(M, V)
         lab = torch.randint(0, V, (M,), device=dev, dtype=torch.int32)
