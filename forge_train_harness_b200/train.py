@@ -33,6 +33,8 @@ def _apply_sets(cfg, sets):
             v = int(val)
         elif isinstance(cur, float):
             v = float(val)
+        elif isinstance(cur, (list, tuple)):   # e.g. parallel.pipeline_layer_split=17,15 ; "" or "none" empties it
+            v = tuple(int(x) for x in val.split(",") if x.strip()) if val not in ("", "none", "None") else ()
         else:
             v = None if val in ("", "none", "None") else val
         cfg = cfg.replace(**{table: {field: v}})
