@@ -20,6 +20,8 @@
 // GEMM CTA = 6 warps: warp 0 TMA producer (payload tiles by tensor map, scale chunks by 1-D bulk copy), warp 1 MMA
 // issuer and TMEM owner, warps 2-5 epilogue.  Tile 128 x 128 x 128, 5-stage ring, two accumulator stages.  Every
 // mbarrier wait is bounded.
+#include <cstdlib>
+
 #include <cuda.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -112,6 +114,81 @@ __global__ void mxfp8_quant_col_kernel(const __nv_bfloat16* __restrict__ x, long
     dst[0] = o[0];
     dst[1] = o[1];
     sf[sf_offset(c, rb, k_chunks)] = (uint8_t)e;
+  }
+}
+
+// Row orientation, coalesced form: four neighbouring lanes own one 32-element block, each one 16-byte vector of it, so a warp
+// reads 512 contiguous bytes per instruction and writes 256; the block's amax is combined with two xor shuffles.
+__global__ void mxfp8_quant_row4_kernel(const __nv_bfloat16* __restrict__ x, long long ld, uint8_t* __restrict__ q,
+                                        uint8_t* __restrict__ sf, int R, int C) {
+  const int vec_per_row = C / 8, k_chunks = (C / 32 + 3) / 4;
+  const long long total = (long long)R * vec_per_row, stride = (long long)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it - lane < total; it += stride) {
+    const bool live = it < total;
+    const int r = live ? (int)(it / vec_per_row) : 0, vr = live ? (int)(it % vec_per_row) : 0;
+    float v[8];
+    if (live) load8(x + (size_t)r * ld + vr * 8, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live) continue;
+    const uint32_t e = e8m0_of_amax(amax);
+    const float inv = inv_scale_of_e8m0(e);
+    uint2 o;
+    o.x = pack4_e4m3(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+    o.y = pack4_e4m3(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+    *reinterpret_cast<uint2*>(q + (size_t)r * C + vr * 8) = o;
+    if ((vr & 3) == 0) sf[sf_offset(r, vr >> 2, k_chunks)] = (uint8_t)e;
+  }
+}
+
+// Column orientation, coalesced form: a CTA stages a 32-row x 256-column patch in shared memory with 16-byte row loads
+// (512 contiguous bytes per row), then thread c reads column c of the patch, quantises its 32 values and writes one
+// 32-byte sector of q^T.
+constexpr int kColTile = 256;
+__global__ void mxfp8_quant_col_tile_kernel(const __nv_bfloat16* __restrict__ x, long long ld, uint8_t* __restrict__ qt,
+                                            uint8_t* __restrict__ sf, int R, int C) {
+  __shared__ __align__(16) __nv_bfloat16 patch[32][kColTile + 8];
+  const int row_blocks = R / 32, col_tiles = (C + kColTile - 1) / kColTile, k_chunks = (row_blocks + 3) / 4;
+  const long long total = (long long)row_blocks * col_tiles;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const int rb = (int)(t / col_tiles), c0 = (int)(t % col_tiles) * kColTile;
+    __syncthreads();   // the previous patch has been consumed
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int v = threadIdx.x + k * 256, row = v / (kColTile / 8), cv = v % (kColTile / 8);
+      const int col = c0 + cv * 8;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      if (col < C) w = *reinterpret_cast<const uint4*>(x + (size_t)(rb * 32 + row) * ld + col);
+      *reinterpret_cast<uint4*>(&patch[row][cv * 8]) = w;
+    }
+    __syncthreads();
+    const int c = c0 + threadIdx.x;
+    if (c < C) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __bfloat162float(patch[i][threadIdx.x]);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      const uint32_t e = e8m0_of_amax(amax);
+      const float inv = inv_scale_of_e8m0(e);
+      uint4 o[2];
+      uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ow[i] = pack4_e4m3(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+      uint4* dst = reinterpret_cast<uint4*>(qt + (size_t)c * R + rb * 32);
+      dst[0] = o[0];
+      dst[1] = o[1];
+      sf[sf_offset(c, rb, k_chunks)] = (uint8_t)e;
+    }
   }
 }
 
@@ -382,12 +459,28 @@ int fth_mxfp8_quant(const void* x, long long ld, void* q, void* sf, int R, int C
     long long total = (long long)R * (C / 32);
     int grid = (int)((total + 255) / 256);
     if (grid > mx_sm_count() * 16) grid = mx_sm_count() * 16;
-    mxfp8_quant_row_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    // coalesced form (4 lanes per block); FTH_MXFP8_QUANT_V1=1 selects the one-thread-per-block kernel (same bits)
+    static const bool v1 = getenv("FTH_MXFP8_QUANT_V1") != nullptr && getenv("FTH_MXFP8_QUANT_V1")[0] == '1';
+    if (v1) {
+      mxfp8_quant_row_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    } else {
+      long long vecs = (long long)R * (C / 8);
+      int g4 = (int)((vecs + 255) / 256);
+      if (g4 > mx_sm_count() * 16) g4 = mx_sm_count() * 16;
+      mxfp8_quant_row4_kernel<<<g4, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    }
   } else {
     if (R % 32 || R % 16) return -2;
     long long total = (long long)(R / 32) * ((C + 63) / 64);
     int grid = (int)(total < (long long)mx_sm_count() * 32 ? total : (long long)mx_sm_count() * 32);
-    mxfp8_quant_col_kernel<<<grid, 64, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    static const bool v1c = getenv("FTH_MXFP8_QUANT_V1") != nullptr && getenv("FTH_MXFP8_QUANT_V1")[0] == '1';
+    if (v1c || C % 8) {   // the tiled kernel loads 16-byte vectors along the columns
+      mxfp8_quant_col_kernel<<<grid, 64, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    } else {
+      long long tiles = (long long)(R / 32) * ((C + kColTile - 1) / kColTile);
+      int gt = (int)(tiles < (long long)mx_sm_count() * 8 ? tiles : (long long)mx_sm_count() * 8);
+      mxfp8_quant_col_tile_kernel<<<gt, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -224,9 +224,11 @@ def test_gemm_repeated_calls_and_views(ops):
 
 
 # ---- MXFP8 ----------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("R,C", [(128, 128), (256, 1024), (200, 160), (4096, 4096)])
+@pytest.mark.parametrize("R,C", [(128, 128), (256, 1024), (200, 160), (4096, 4096), (96, 320), (33, 32), (64, 584)])
 @pytest.mark.parametrize("colwise", [False, True])
 def test_mxfp8_quant_matches_format_statement(ops, R, C, colwise):
+    if not colwise and C % 32:
+        C = (C + 31) // 32 * 32          # row orientation: blocks of 32 along the columns
     from forge_train_harness_b200.ops import mxfp8 as mx
     if colwise and R % 32:
         R = (R + 31) // 32 * 32
@@ -236,6 +238,11 @@ def test_mxfp8_quant_matches_format_statement(ops, R, C, colwise):
     q0, sf0 = mx.quantize_ref(x, colwise)
     assert q.shape == q0.shape and torch.equal(sf.cpu(), sf0.cpu())
     assert torch.equal(q.cpu(), q0.cpu())
+    # a strided source (a column slice of a wider tensor) gives the same bits
+    wide = torch.zeros(R, C + 64, device="cuda", dtype=torch.bfloat16)
+    wide[:, 32:32 + C] = x
+    q2, sf2 = mx.quantize(wide[:, 32:32 + C], colwise)
+    assert torch.equal(q2, q) and torch.equal(sf2, sf)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (200, 264, 160), (1024, 4096, 4096), (130, 96, 32)])
