@@ -459,8 +459,10 @@ int fth_mxfp8_quant(const void* x, long long ld, void* q, void* sf, int R, int C
     long long total = (long long)R * (C / 32);
     int grid = (int)((total + 255) / 256);
     if (grid > mx_sm_count() * 16) grid = mx_sm_count() * 16;
-    // coalesced form (4 lanes per block); FTH_MXFP8_QUANT_V1=1 selects the one-thread-per-block kernel (same bits)
-    static const bool v1 = getenv("FTH_MXFP8_QUANT_V1") != nullptr && getenv("FTH_MXFP8_QUANT_V1")[0] == '1';
+    // coalesced form (4 lanes per block); FTH_MXFP8_QUANT_V1=1 (both orientations) or =row selects the one-thread-per-block
+    // kernel (same bits)
+    static const bool v1 = getenv("FTH_MXFP8_QUANT_V1") != nullptr &&
+                           (getenv("FTH_MXFP8_QUANT_V1")[0] == '1' || getenv("FTH_MXFP8_QUANT_V1")[0] == 'r');
     if (v1) {
       mxfp8_quant_row_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
     } else {
@@ -473,7 +475,8 @@ int fth_mxfp8_quant(const void* x, long long ld, void* q, void* sf, int R, int C
     if (R % 32 || R % 16) return -2;
     long long total = (long long)(R / 32) * ((C + 63) / 64);
     int grid = (int)(total < (long long)mx_sm_count() * 32 ? total : (long long)mx_sm_count() * 32);
-    static const bool v1c = getenv("FTH_MXFP8_QUANT_V1") != nullptr && getenv("FTH_MXFP8_QUANT_V1")[0] == '1';
+    static const bool v1c = getenv("FTH_MXFP8_QUANT_V1") != nullptr &&
+                            (getenv("FTH_MXFP8_QUANT_V1")[0] == '1' || getenv("FTH_MXFP8_QUANT_V1")[0] == 'c');
     if (v1c || C % 8) {   // the tiled kernel loads 16-byte vectors along the columns
       mxfp8_quant_col_kernel<<<grid, 64, 0, stream>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
     } else {
