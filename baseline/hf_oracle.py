@@ -56,10 +56,17 @@ def _compat():
 def build_model(m, seed: int, device: str = "cpu", dtype=None, attn_impl: str = "eager"):
     """HF ``MiniCPMForCausalLM`` with the geometry and muP constants of ``m`` (a ``ModelConfig``), random weights."""
     import torch
-    os.environ.setdefault("HF_MODULES_CACHE", os.path.join(ROOT, ".artifacts", "hf_modules"))
+    cache = os.environ.setdefault("HF_MODULES_CACHE", os.path.join(ROOT, ".artifacts", "hf_modules"))
     os.environ.setdefault("HF_HUB_OFFLINE", "1")
     os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
     _compat()
+    # transformers reads the cache location once, at import; if it was imported before this call the constants still point
+    # at the user's home directory, so they are re-pointed here: the copied modeling files stay inside this repository
+    import transformers.dynamic_module_utils as _dmu
+    import transformers.utils.hub as _hub
+    for mod in (_dmu, _hub):
+        if getattr(mod, "HF_MODULES_CACHE", cache) != cache:
+            mod.HF_MODULES_CACHE = cache
     from transformers import AutoConfig, AutoModelForCausalLM
     sys.path.insert(0, ROOT)
     from forge_train_harness_b200.ckpt.hf_names import hf_config_overrides
