@@ -219,6 +219,15 @@ class RunConfig:
     data: DataConfig = field(default_factory=DataConfig)
     ckpt: CkptConfig = field(default_factory=CkptConfig)
 
+    def __post_init__(self):
+        # cross-table checks that would otherwise only fail when the model is built on every rank
+        split = self.parallel.pipeline_layer_split
+        if split:
+            chunks = self.parallel.pipeline_parallel_size * max(1, self.parallel.virtual_pipeline_stages)
+            if len(split) != chunks or any(int(x) <= 0 for x in split) or sum(int(x) for x in split) != self.model.num_layers:
+                raise ValueError(f"pipeline_layer_split {tuple(split)} needs {chunks} positive entries that sum to "
+                                 f"num_layers = {self.model.num_layers}")
+
     def replace(self, **tables: dict[str, Any]) -> "RunConfig":
         """Return a copy with per-table field overrides, e.g. ``replace(train={"num_steps": 3})``."""
         out = {}

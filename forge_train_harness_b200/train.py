@@ -23,6 +23,9 @@ from .parallel.topology import init_distributed
 
 
 def _apply_sets(cfg, sets):
+    """``table.field=value`` overrides, all applied in ONE step (so a set of overrides that is only valid together, such as a
+    new pipeline size with a new layer split, does not trip the cross-table checks half-way)."""
+    tables: dict = {}
     for item in sets or []:
         key, val = item.split("=", 1)
         table, field = key.split(".", 1)
@@ -37,8 +40,8 @@ def _apply_sets(cfg, sets):
             v = tuple(int(x) for x in val.split(",") if x.strip()) if val not in ("", "none", "None") else ()
         else:
             v = None if val in ("", "none", "None") else val
-        cfg = cfg.replace(**{table: {field: v}})
-    return cfg
+        tables.setdefault(table, {})[field] = v
+    return cfg.replace(**tables) if tables else cfg
 
 
 def run_phases(cfg, recipe: dict, out=None):

@@ -118,3 +118,17 @@ def test_gate_sweep_runs_the_cpu_suites_in_milestone_order(tmp_path):
     lines = [ln for ln in table.splitlines() if ln.startswith("| ") and "---" not in ln]
     assert [ln.split("|")[1].strip() for ln in lines] == ["multistep", "dptp", "production-train"]   # milestone order
     assert "passed" in lines[0] and "skipped" in lines[1] and "needs 4 GPUs" in lines[1] and "passed" in lines[2]
+
+
+def test_set_overrides_parse_every_field_kind():
+    from forge_train_harness_b200.config import schema
+    from forge_train_harness_b200.train import _apply_sets
+    cfg = schema.load(os.path.join(ROOT, "configs", "minicpm4_8b_tp4pp2.toml"))
+    assert cfg.parallel.pipeline_layer_split == (17, 15)
+    c2 = _apply_sets(cfg, ["parallel.pipeline_layer_split=none", "parallel.pipeline_parallel_size=1", "parallel.sequence_parallel=false",
+                           "train.init_mode=device", "optim.lr=3e-4", "train.num_steps=7", "train.save_path=none"])
+    assert c2.parallel.pipeline_layer_split == () and c2.parallel.pipeline_parallel_size == 1 and c2.parallel.sequence_parallel is False
+    assert c2.train.init_mode == "device" and c2.optim.lr == 3e-4 and c2.train.num_steps == 7 and c2.train.save_path is None
+    assert _apply_sets(cfg, ["parallel.pipeline_layer_split=16,16"]).parallel.pipeline_layer_split == (16, 16)
+    with pytest.raises(ValueError):
+        _apply_sets(cfg, ["parallel.pipeline_layer_split=20,20"])      # must sum to the layer count
