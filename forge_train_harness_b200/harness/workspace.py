@@ -193,8 +193,8 @@ def sync_push(dest: str, src: str | None = None, ignore_file: str | None = None)
     """Copy the workspace to ``dest`` (a directory), skipping ignored paths; files that vanished locally are removed on the
     far side and stale ``__pycache__`` directories are cleaned.  Returns counts."""
     src = src or ROOT
-    pats = ["__pycache__", ".git", "gpurun_out", ".artifacts", "*.pyc"]
-    ig = ignore_file or os.path.join(src, ".gpurunignore")
+    pats = ["__pycache__", ".git", ".artifacts", "*.pyc"]
+    ig = ignore_file or os.path.join(src, ".syncignore")
     if os.path.isfile(ig):
         pats += [ln.strip() for ln in open(ig) if ln.strip() and not ln.startswith("#")]
     copied = removed = 0

@@ -42,7 +42,7 @@ def deviations(ref, got, name):
     import os
     dl = max(abs(l0 - l1) / abs(l0) for (l0, _), (l1, _) in zip(ref, got))
     dg = max(abs(g0 - g1) / abs(g0) for (_, g0), (_, g1) in zip(ref, got))
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    out = os.environ.get("FORGE_TEST_ARTIFACTS") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "test_artifacts")
     if os.path.isdir(out):
         with open(os.path.join(out, "engine_parity.jsonl"), "a") as f:
             f.write(json.dumps({"case": name, "max_rel_loss_dev": dl, "max_rel_grad_norm_dev": dg}) + "\n")

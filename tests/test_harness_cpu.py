@@ -215,12 +215,13 @@ def test_workspace_resources_sync_prefetch_retention(tmp_path):
     src = tmp_path / "tree"
     (src / "forge_train_harness_b200").mkdir(parents=True)
     (src / "forge_train_harness_b200" / "__init__.py").write_text("x = 1\n")
-    (src / "gpurun_out").mkdir()
-    (src / "gpurun_out" / "big.log").write_text("log")
+    (src / "scratch_out").mkdir()
+    (src / "scratch_out" / "big.log").write_text("log")
+    (src / ".syncignore").write_text("# stays behind\nscratch_out/\n")
     (src / "a.txt").write_text("a")
     dst = tmp_path / "remote"
     r1 = W.sync_push(str(dst), str(src))
-    assert r1["passed"] and r1["copied"] == 2 and not (dst / "gpurun_out").exists()
+    assert r1["passed"] and r1["copied"] == 3 and not (dst / "scratch_out").exists()
     (src / "a.txt").unlink()
     (dst / "forge_train_harness_b200" / "__pycache__").mkdir()
     r2 = W.sync_push(str(dst), str(src))

@@ -33,7 +33,7 @@ def ops():
     torch.cuda.synchronize()
     check_status()
     Sm100Ops.set_deterministic(False)
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    out = os.environ.get("FORGE_TEST_ARTIFACTS") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "test_artifacts")
     if os.path.isdir(out):  # keep the measured distributions next to the other run artefacts
         with open(os.path.join(out, "op_contract_stats.json"), "w") as f:
             json.dump(_STATS, f, indent=1)
