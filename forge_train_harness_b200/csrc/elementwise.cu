@@ -199,12 +199,18 @@ __global__ void qk_norm_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const 
   const int tph = d / 8, hpr = n_kv * (g + 2);
   const size_t total = (size_t)M * hpr * tph, stride = (size_t)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
-  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it - lane < total; it += stride) {
+  // (row, head slot) of this thread's first vector; advanced by the grid stride (a multiple of the lane-group size, so the
+  // vector position inside the head never changes) without a division per vector
+  size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const int vec = (int)(it % tph);
+  size_t row = (it / tph) / hpr;
+  int hs = (int)((it / tph) % hpr);
+  const size_t dslot = stride / tph, drow = dslot / hpr;
+  const int dhs = (int)(dslot % hpr);
+  for (; it - lane < total; it += stride, row += drow, hs += dhs) {
+    if (hs >= hpr) { hs -= hpr; ++row; }
     const bool live = it < total;
-    const size_t slot = live ? it / tph : 0;
-    const int vec = (int)(it % tph);
-    const size_t row = slot / hpr;
-    const int hs = (int)(slot % hpr), hh = hs % (g + 2);
+    const int hh = hs % (g + 2);
     const size_t off = (row * hpr + hs) * (size_t)d + vec * 8;
     float f[8];
     if (live) load8(qkv + off, f);
@@ -247,11 +253,15 @@ __global__ void qk_norm_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_
   load8(wk + vec * 8, wkv);
 #pragma unroll
   for (int i = 0; i < 8; ++i) accq[i] = acck[i] = 0.f;
-  for (size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x; it - lane < total; it += stride) {
+  size_t it = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  size_t row = (it / tph) / hpr;
+  int hs = (int)((it / tph) % hpr);
+  const size_t dslot = stride / tph, drow = dslot / hpr;
+  const int dhs = (int)(dslot % hpr);
+  for (; it - lane < total; it += stride, row += drow, hs += dhs) {
+    if (hs >= hpr) { hs -= hpr; ++row; }
     const bool live = it < total;
-    const size_t slot = live ? it / tph : 0;
-    const size_t row = slot / hpr;
-    const int hs = (int)(slot % hpr), hh = hs % (g + 2);
+    const int hh = hs % (g + 2);
     const bool normed = live && hh <= g;
     const size_t off = (row * hpr + hs) * (size_t)d + vec * 8;
     float gq[8], x[8];

@@ -124,9 +124,12 @@ __global__ void mxfp8_quant_row4_kernel(const __nv_bfloat16* __restrict__ x, lon
   const int vec_per_row = C / 8, k_chunks = (C / 32 + 3) / 4;
   const long long total = (long long)R * vec_per_row, stride = (long long)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
-  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it - lane < total; it += stride) {
+  // (row, vector-in-row) of this thread's first vector, then advanced by the grid stride without a division per vector
+  long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  int r = (int)(it / vec_per_row), vr = (int)(it % vec_per_row);
+  const int dr = (int)(stride / vec_per_row), dv = (int)(stride % vec_per_row);
+  for (; it - lane < total; it += stride) {
     const bool live = it < total;
-    const int r = live ? (int)(it / vec_per_row) : 0, vr = live ? (int)(it % vec_per_row) : 0;
     float v[8];
     if (live) load8(x + (size_t)r * ld + vr * 8, v);
     else {
@@ -138,14 +141,18 @@ __global__ void mxfp8_quant_row4_kernel(const __nv_bfloat16* __restrict__ x, lon
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    if (!live) continue;
-    const uint32_t e = e8m0_of_amax(amax);
-    const float inv = inv_scale_of_e8m0(e);
-    uint2 o;
-    o.x = pack4_e4m3(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-    o.y = pack4_e4m3(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-    *reinterpret_cast<uint2*>(q + (size_t)r * C + vr * 8) = o;
-    if ((vr & 3) == 0) sf[sf_offset(r, vr >> 2, k_chunks)] = (uint8_t)e;
+    if (live) {
+      const uint32_t e = e8m0_of_amax(amax);
+      const float inv = inv_scale_of_e8m0(e);
+      uint2 o;
+      o.x = pack4_e4m3(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+      o.y = pack4_e4m3(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+      *reinterpret_cast<uint2*>(q + (size_t)r * C + vr * 8) = o;
+      if ((vr & 3) == 0) sf[sf_offset(r, vr >> 2, k_chunks)] = (uint8_t)e;
+    }
+    r += dr;
+    vr += dv;
+    if (vr >= vec_per_row) { vr -= vec_per_row; ++r; }
   }
 }
 
