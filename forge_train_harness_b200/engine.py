@@ -35,7 +35,7 @@ from .ops import get_ops, rope_table
 from .optim.distributed import DistributedOptimizer
 from .optim.schedule import compute_lr
 from .parallel.pipeline import PipeLinks, build_schedule
-from .parallel.topology import Topology, build_topology, init_distributed
+from .parallel.topology import Topology, build_topology, init_distributed, spans_nodes
 from .parallel.tp import TPComm
 from .utils import wire
 from .utils.peaks import load_peaks, mfu_percent
@@ -74,7 +74,7 @@ class Trainer:
         self.tpc = TPComm(topo.tp_group, topo.tp, topo.tp_rank, par.sequence_parallel)
         want_tp = os.environ.get("FORGE_FUSED_TP", "1")  # "0" = NCCL collectives, "require" = fail instead of falling back
         if self.tpc.sp and self.device.type == "cuda" and par.fused_comm and self.dtype == torch.bfloat16 and par.fp8 == "off" \
-                and want_tp != "0":
+                and want_tp != "0" and not spans_nodes(topo.tp_ranks):
             from .parallel import fused_tp
             self.tpc.fused = fused_tp.try_create(topo.tp_group, topo.tp, topo.tp_rank, t.micro_batch_size * m.seq_length,
                                                  m.hidden_size, self.device, required=want_tp == "require")
@@ -93,7 +93,8 @@ class Trainer:
             c.debug_checks = t.debug_checks or os.environ.get("FORGE_DEBUG_CHECKS", "0") == "1"
         fused = None
         want_dp = os.environ.get("FORGE_FUSED_DP", "1")
-        if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 and want_dp != "0":
+        if self.device.type == "cuda" and par.fused_comm and par.use_distributed_optimizer and topo.dp > 1 and want_dp != "0" \
+                and not spans_nodes(topo.dp_ranks):     # a DP group that crosses nodes keeps NCCL
             from .parallel import fused_dp
             fused = fused_dp.try_create(self.store, topo, required=want_dp == "require")
         self.opt = DistributedOptimizer(self.store, topo, cfg.optim, self.ops, sharded=par.use_distributed_optimizer,

@@ -60,6 +60,25 @@ class Topology:
         return self.rank_of((self.pp_rank + 1) % self.pp, self.dp_rank, self.tp_rank)
 
 
+def ranks_per_node() -> int:
+    """Processes per node as the launcher states it (``LOCAL_WORLD_SIZE``; one node when it is not set)."""
+    v = os.environ.get("LOCAL_WORLD_SIZE")
+    if v:
+        return max(1, int(v))
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size()
+    return max(1, int(os.environ.get("WORLD_SIZE") or "1"))
+
+
+def spans_nodes(ranks) -> bool:
+    """True when ``ranks`` (global ranks of one process group) live on more than one node.  The peer-memory kernels (fused DP
+    reduce-scatter / parameter push, all-gather->GEMM, GEMM->reduce-scatter) read and write other GPUs' memory over NVLink and
+    so serve groups inside one NVSwitch domain; a group that crosses nodes keeps the library collectives.  Every rank
+    derives the same answer from the launcher's environment, so the choice of path cannot differ between ranks."""
+    n = ranks_per_node()
+    return len({int(r) // n for r in ranks}) > 1
+
+
 def build_topology(tp: int = 1, pp: int = 1, kv_replicas: int = 1) -> Topology:
     """Create all groups.  Works without an initialised process group (world size 1)."""
     if not (dist.is_available() and dist.is_initialized()):

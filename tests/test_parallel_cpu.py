@@ -172,3 +172,16 @@ def test_dp2_bucket_overlap_is_the_same_reduction(zero):
     assert on[0][0] == off[0][0] and on[0][0] == on[1][0]
     assert off[0][1] == 0
     assert on[0][2] > 2 and 0 < on[0][1] < on[0][2]
+
+
+def test_peer_memory_paths_are_for_groups_inside_one_node(monkeypatch):
+    """TP inside a node and DP across nodes is the usual multi-node layout: the DP group then keeps the library collectives."""
+    from forge_train_harness_b200.parallel import topology as T
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    assert not T.spans_nodes([0, 1, 2, 3]) and not T.spans_nodes(range(8)) and not T.spans_nodes([8, 9, 15])
+    assert T.spans_nodes([0, 8]) and T.spans_nodes([3, 11, 19]) and T.spans_nodes(range(16))
+    monkeypatch.delenv("LOCAL_WORLD_SIZE")
+    monkeypatch.setenv("WORLD_SIZE", "4")      # a launcher that only states the world size: one node
+    assert not T.spans_nodes([0, 1, 2, 3])
+    monkeypatch.delenv("WORLD_SIZE")
+    assert not T.spans_nodes([0])
