@@ -76,9 +76,13 @@ def long_train(ref_records, our_records, window: tuple[int, int], loss_rel_thres
     ok = m["mean_rel_diff"] < loss_rel_threshold
     out = {"passed": ok, "mean_rel_diff": m["mean_rel_diff"], "max_rel_diff": m["max_rel_diff"],
            "signed_mean_rel": m["signed_mean_rel"], "drift_warning": m["drift_warning"], "threshold": loss_rel_threshold}
+    mfus = [ours[s].mfu for s in steps if ours[s].mfu is not None]
+    if mfus:
+        # always reported (the MFU history and the review-side elastic bar read it); it only GATES when a floor is given
+        out["avg_mfu_e2e_standard"] = sum(mfus) / len(mfus)
     if mfu_floor is not None:
-        mfus = [ours[s].mfu for s in steps if ours[s].mfu is not None]
         out["mfu_avg"] = sum(mfus) / max(len(mfus), 1)
+        out["mfu_target"] = mfu_floor
         out["passed"] = ok and out["mfu_avg"] >= mfu_floor
     return out
 

@@ -220,6 +220,8 @@ def main(argv=None) -> int:
     with open(os.path.join(art, "request.json"), "w") as f:
         json.dump(req, f, indent=1)
     res = dispatcher.run_suite(req, reg, ROOT, art, cache_dir=os.path.join(ROOT, ".artifacts", "ref_cache"))
+    from . import mfu
+    mfu.record_result(res)
     RS.emit_result(res, sys.stdout)
     return 0 if res["status"] == "passed" else 1
 

@@ -224,11 +224,13 @@ def _supervise(jd: str) -> int:
 
 
 # ---- lifecycle ---------------------------------------------------------------------------------------------------------------
-def build_entry(*, suite: str, extra: list[str], loop_id: str = "", workdir: str | None = None) -> str:
+def build_entry(*, suite: str, extra: list[str], loop_id: str = "", workdir: str | None = None, loop_dir: str = "") -> str:
     """Shell line a job runs for a suite: the harness CLI from the synced workspace, with the loop id exported so the run's
     records land under the loop's directory."""
     import shlex
+    loop_dir = loop_dir or os.environ.get("FORGE_LOOP_DIR", "")
     parts = [f"cd {shlex.quote(workdir or ROOT)}", f"export FORGE_LOOP_ID={shlex.quote(loop_id)}" if loop_id else "true",
+             f"export FORGE_LOOP_DIR={shlex.quote(loop_dir)}" if loop_dir else "true",
              " ".join([shlex.quote(sys.executable), "-m", "forge_train_harness_b200.harness", "run", shlex.quote(suite)]
                       + [shlex.quote(x) for x in extra])]
     return " && ".join(parts)

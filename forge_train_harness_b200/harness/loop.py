@@ -334,7 +334,7 @@ class Loop:
         for name, gate in suites:
             outer = float(gate.get("timeout_s", 1800))
             entry = jobs.build_entry(suite=name, extra=["--registry", self.cfg.registry], loop_id=self.loop_id,
-                                     workdir=self.cfg.workspace)
+                                     workdir=self.cfg.workspace, loop_dir=self.dir)
             rc = jobs.run_suite(sched, suite=f"{self.loop_id}.{name}", entry=entry, gpus=int(gate.get("gpu_count", 0)),
                                 outer=outer, poll_interval_s=self.cfg.gate_poll_s, out=self.out)
             results[name] = rc

@@ -21,6 +21,41 @@ def record(path: str, suite: str, mfu: float, loss_passed: bool | None, extra: d
     return row
 
 
+def history_path(env: dict | None = None) -> str | None:
+    """Where a gate run's MFU sample belongs: the loop's own directory (``FORGE_LOOP_DIR``, exported to every worker and job
+    of a development loop), else an explicit ``FORGE_MFU_HISTORY`` file, else nowhere."""
+    env = os.environ if env is None else env
+    if env.get("FORGE_MFU_HISTORY"):
+        return env["FORGE_MFU_HISTORY"]
+    if env.get("FORGE_LOOP_DIR"):
+        return os.path.join(env["FORGE_LOOP_DIR"], "mfu_history.jsonl")
+    return None
+
+
+def record_result(result: dict, env: dict | None = None, out=None) -> dict | None:
+    """Append the MFU sample of a finished gate run, if it measured one (tools/mfu_record.py:33-95; called by the runner after
+    every suite, evals/runner.py:115).  Never raises and never changes the gate's verdict; a run that measured MFU but has no
+    history to go to says so on stderr, because the review-side bar silently starves otherwise."""
+    import sys
+    out = out or sys.stderr
+    metrics = result.get("metrics") or {}
+    avg = metrics.get("avg_mfu_e2e_standard")
+    if avg is None:
+        return None
+    path = history_path(env)
+    if path is None:
+        print("mfu_record: SKIPPED, no loop directory (set FORGE_LOOP_DIR or FORGE_MFU_HISTORY); this run will be missing "
+              "from the MFU history", file=out)
+        return None
+    loss_passed = None if "mean_rel_diff" not in metrics else bool(metrics["mean_rel_diff"] < metrics.get("threshold", 0.01))
+    try:
+        return record(path, str(result.get("suite") or ""), float(avg), loss_passed,
+                      {"mfu_target": metrics.get("mfu_target"), "status": result.get("status")})
+    except OSError as e:
+        print(f"mfu_record: persist failed: {e}", file=out)
+        return None
+
+
 def load(path: str) -> list[dict]:
     if not os.path.isfile(path):
         return []

@@ -307,3 +307,22 @@ def test_stage2_fan_out_bounds_concurrency_and_skips_exhausted_ops(tmp_path, mon
     assert max(int(open(marks / f).read()) for f in os.listdir(marks) if f.endswith(".end")) <= 2   # never more than 2 alive
     with pytest.raises(KeyError):
         stage2.fan_out(["true"], ops=["no_such_op"])
+
+
+def test_gate_runs_feed_the_mfu_history_of_their_loop(tmp_path, capsys):
+    """A long-train result carries the window's mean MFU; the runner appends it to the loop's history (and says so loudly when
+    there is no loop to record it for), and the elastic bar reads that history."""
+    from forge_train_harness_b200.gates import verdicts as V
+    from forge_train_harness_b200.utils import wire
+    lines = "\n".join(wire.format_loss_line(s, 5.0 - 0.01 * s, 1.0, 0.5, 40.0 + 0.1 * s) for s in range(1, 11))
+    recs = wire.parse_loss_lines(lines, strict=False)
+    m = V.long_train(recs, recs, (3, 9), 0.01)
+    assert m["passed"] and abs(m["avg_mfu_e2e_standard"] - 40.55) < 1e-6 and "mfu_target" not in m
+    assert not V.long_train(recs, recs, (3, 9), 0.01, mfu_floor=45.0)["passed"]          # a floor gates, its absence does not
+    res = RS.make_run_result("long-train", True, "ok", m, {})
+    assert mfu.record_result(res, env={}) is None and "SKIPPED" in capsys.readouterr().err
+    row = mfu.record_result(res, env={"FORGE_LOOP_DIR": str(tmp_path)})
+    assert row["suite"] == "long-train" and row["loss_passed"] is True and abs(row["mfu_avg"] - 40.55) < 1e-6
+    assert mfu.record_result(RS.make_run_result("resume-gate", True, "ok", {"passed": True}, {}), env={"FORGE_LOOP_DIR": str(tmp_path)}) is None
+    hist = mfu.load(str(tmp_path / "mfu_history.jsonl"))
+    assert len(hist) == 1 and mfu.evaluate(mfu.qualifying(hist), 40.0)[0]
