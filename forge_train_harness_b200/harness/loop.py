@@ -14,7 +14,8 @@ The reference drives its coding agents with ``agent-loop.sh`` (agent-loop.sh:677
 * **Advancing.**  The worker declares progress with a commit-message line ``MILESTONE_STATUS: <name> PASS``; after each round
   the last commits are scanned and the active milestone becomes the successor of the furthest declared one (capped at the
   last).  Milestones listed as review-gated ignore declarations and advance only when the review passes and writes
-  ``MILESTONE_OVERRIDE: <active milestone>``.  With ``advance = "gates"`` the loop does not trust declarations at all: it
+  ``MILESTONE_OVERRIDE: <active milestone>`` — or, with no review command and ``review_mfu_target`` set, when the loop's own
+  review finds the throughput bar met on the MFU history the gate runs wrote.  With ``advance = "gates"`` the loop does not trust declarations at all: it
   runs the active milestone's suites itself (as short-lived GPU jobs, ``harness/jobs.py``) and advances on their verdicts.
 * **Events.**  Every transition is one JSON line in ``<loop_dir>/events.jsonl``; ``report`` rebuilds the per-round table,
   the milestone table, the MFU trajectory and an error digest from files only, on a live or a dead loop.
@@ -120,6 +121,13 @@ class LoopConfig:
     remote: dict = field(default_factory=dict)
     prompt_dir: str = ""
     gate_poll_s: float = 30.0
+    # built-in review of a review-gated milestone when no review command is configured: the throughput bar on the MFU history
+    # the gate runs wrote (strict pass, or a plateau inside the tolerance band: harness/mfu.py).  0 = off.
+    review_mfu_target: float = 0.0
+    review_suite: str = "long-train"
+    mfu_elastic_tolerance: float = 2.0
+    mfu_elastic_rounds: int = 3
+    mfu_elastic_eps: float = 0.5
 
     @staticmethod
     def load(path: str) -> "LoopConfig":
@@ -323,6 +331,28 @@ class Loop:
         self._write("stage1.milestone", nxt)
         self.event("milestone_advanced", round=rnd, **{"from": cur, "to": nxt, "max": self.order[-1], "commit": sha})
 
+    def _builtin_review(self, rnd: int) -> bool:
+        """The review the reference leaves to its review agent for the long-horizon milestone (review_stage1.md; tools/
+        mfu_elastic_check.py): read the MFU history written by the gate runs, apply the elastic bar, and advance the ACTIVE
+        review-gated milestone on a pass.  Returns True when it advanced."""
+        cfg, cur = self.cfg, self.milestone
+        if cfg.review_cmd or cfg.review_mfu_target <= 0 or cur not in cfg.review_gated:
+            return False
+        samples = mfu.qualifying(mfu.load(os.path.join(self.dir, "mfu_history.jsonl")), cfg.review_suite)
+        ok, code = mfu.evaluate(samples, cfg.review_mfu_target, cfg.mfu_elastic_tolerance, cfg.mfu_elastic_rounds, cfg.mfu_elastic_eps)
+        self.event("review_finished", round=rnd, rc=0, verdict="PASS" if ok else "FAIL",
+                   contract={"by": "mfu-bar", "code": code, "samples": len(samples), "target": cfg.review_mfu_target})
+        if not ok:
+            return False
+        if cur == self.order[-1]:
+            self._write("stage1.status", "finished")
+            self.event("stage_finished", round=rnd, stage="stage1")
+        else:
+            nxt = self.order[self.order.index(cur) + 1]
+            self._write("stage1.milestone", nxt)
+            self.event("milestone_auto_advanced", round=rnd, **{"from": cur, "to": nxt, "max": self.order[-1], "text": code})
+        return True
+
     def _advance_by_gates(self, rnd: int, lease_env: dict) -> None:
         cur = self.milestone
         suites = suites_of_milestone(self.cfg.registry, cur)
@@ -433,6 +463,7 @@ class Loop:
                 else:
                     self._advance_declared(rnd, review_passed, ctx["review_file"])
                 self.backfill_mfu_events()
+                self._builtin_review(rnd)
                 self.event("round_finished", round=rnd, status="ok", attempts=attempts, duration_s=time.time() - t0,
                            review="PASS" if review_passed else "FAIL", commits=commits, milestone_after=self.milestone)
                 if self._read("stage1.status") == "finished":

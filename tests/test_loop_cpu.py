@@ -272,3 +272,31 @@ def test_fork_continues_from_the_milestone_after_the_anchor(tmp_path):
     assert loop.fork(cfg, "src", "bitwise-singlecard", new_loop_id="f3")["anchor_source"] == "git-fallback"
     with pytest.raises(ValueError, match="does not"):
         loop.fork(cfg, "src", "alignment", new_loop_id="f4", at_sha=lp.head())
+
+
+def test_builtin_review_applies_the_elastic_mfu_bar_to_the_gated_milestone(tmp_path):
+    ws, reg = _workspace(tmp_path)
+    cfg = _cfg(tmp_path, ws, reg, {}, review_mfu_target=40.0)
+    lp = loop.Loop(cfg, loop_id="R1")
+    lp._write("stage1.milestone", "long-horizon")
+    hist = os.path.join(lp.dir, "mfu_history.jsonl")
+    mfu.record(hist, "long-train", 36.0, True)                     # below the band
+    assert lp.run(max_rounds=1) == 0 and lp.milestone == "long-horizon"
+    mfu.record(hist, "long-train", 38.6, True)                     # in the band, too little history
+    assert lp.run(max_rounds=1) == 0 and lp.milestone == "long-horizon"
+    mfu.record(hist, "long-train", 38.9, True)
+    mfu.record(hist, "long-train", 38.7, True)                     # three in-band samples within 0.5: a plateau
+    assert lp.run(max_rounds=1) == 0 and lp.milestone == "production"
+    ev = _events(lp)
+    codes = [e["contract"]["code"] for e in ev if e["subtype"] == "review_finished"]
+    assert codes == ["BELOW_BAND", "IN_BAND_INSUFFICIENT_HISTORY", "ELASTIC_PASS"]
+    assert [e["text"] for e in ev if e["subtype"] == "milestone_auto_advanced"] == ["ELASTIC_PASS"]
+    assert [e["mfu_avg"] for e in ev if e["subtype"] == "mfu_record"] == [36.0, 38.6, 38.9, 38.7]
+    # a failed loss verdict disqualifies a sample; milestones that are not review-gated are never touched by the bar
+    lp2 = loop.Loop(_cfg(tmp_path, ws, reg, {}, review_mfu_target=40.0), loop_id="R2")
+    mfu.record(os.path.join(lp2.dir, "mfu_history.jsonl"), "long-train", 55.0, False)
+    lp2._write("stage1.milestone", "long-horizon")
+    assert lp2.run(max_rounds=1) == 0 and lp2.milestone == "long-horizon"
+    lp3 = loop.Loop(_cfg(tmp_path, ws, reg, {}, review_mfu_target=40.0), loop_id="R3")
+    mfu.record(os.path.join(lp3.dir, "mfu_history.jsonl"), "long-train", 55.0, True)
+    assert lp3.run(max_rounds=1) == 0 and lp3.milestone == "alignment"
