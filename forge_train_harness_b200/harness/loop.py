@@ -123,6 +123,10 @@ class LoopConfig:
     gate_poll_s: float = 30.0
     # built-in review of a review-gated milestone when no review command is configured: the throughput bar on the MFU history
     # the gate runs wrote (strict pass, or a plateau inside the tolerance band: harness/mfu.py).  0 = off.
+    # stage 2 (per-operator work) after stage 1 has finished: one worker per operator, fanned out under the registry's
+    # [automation] limits (harness/stage2.py::fan_out); {op} in the command is the operator's name.  Empty = no stage 2.
+    stage2_worker_cmd: list = field(default_factory=list)
+    stage2_max_rounds: int = 20
     review_mfu_target: float = 0.0
     review_suite: str = "long-train"
     mfu_elastic_tolerance: float = 2.0
@@ -331,6 +335,42 @@ class Loop:
         self._write("stage1.milestone", nxt)
         self.event("milestone_advanced", round=rnd, **{"from": cur, "to": nxt, "max": self.order[-1], "commit": sha})
 
+    def run_stage2(self, max_rounds: int | None = None, lease_env: dict | None = None) -> int:
+        """Stage 2: per round one worker per operator that is not yet ``merged`` (bounded concurrency, per-op failure budget),
+        until ``op-status`` has every registered operator merged or the round limit is reached.  The reference fans its
+        stage-2 sub-agents out the same way and re-fans each round (tools/stage2_config.py, agent-loop.sh)."""
+        from . import stage2
+        cfg = self.cfg
+        if not cfg.stage2_worker_cmd:
+            return 0
+        if self._read("stage2.status") == "finished":
+            return 0
+        self._write("stage2.status", "in-progress")
+        rnd = int(self._read("stage2.round", "0"))
+        for _ in range(max_rounds if max_rounds is not None else cfg.stage2_max_rounds):
+            rnd += 1
+            self._write("stage2.round", str(rnd))
+            st = stage2.op_status()
+            todo = sorted(n for n, o in st["ops"].items() if o["state"] != "merged")
+            self.event("stage2_round_started", round=rnd, pending=todo, counts=st["counts"])
+            if not todo:
+                self._write("stage2.status", "finished")
+                self.event("stage_finished", round=rnd, stage="stage2")
+                return 0
+            argv = [str(a).format(workspace=cfg.workspace, loop_dir=self.dir, loop_id=self.loop_id, python=sys.executable, op="{op}")
+                    for a in cfg.stage2_worker_cmd]
+            env_before = dict(os.environ)
+            os.environ.update(dict(lease_env or {}, FORGE_LOOP_ID=self.loop_id, FORGE_LOOP_DIR=self.dir, FORGE_ROUND=str(rnd)))
+            try:
+                res = stage2.fan_out(argv, ops=todo, timeout_s=cfg.round_timeout_s, log_dir=os.path.join(self.dir, f"stage2_round_{rnd:03d}"))
+            finally:
+                os.environ.clear()
+                os.environ.update(env_before)
+            self.event("stage2_round_finished", round=rnd, peak_running=res["peak_running"],
+                       ops={n: r["state"] for n, r in res["ops"].items()})
+        self.exit_cause = "stage 2 round limit reached"
+        return 0
+
     def _builtin_review(self, rnd: int) -> bool:
         """The review the reference leaves to its review agent for the long-horizon milestone (review_stage1.md; tools/
         mfu_elastic_check.py): read the MFU history written by the gate runs, apply the elastic bar, and advance the ACTIVE
@@ -412,7 +452,8 @@ class Loop:
                 self.event("lease_claimed", handle=handle, gpus=cfg.gpus)
             if self._read("stage1.status") == "finished":
                 self.exit_cause = "already finished"
-                return 0
+                rc_final = self.run_stage2(max_rounds, lease_env)
+                return rc_final
             self._write("stage1.status", "in-progress")
             rnd = int(self._read("stage1.round", "0"))
             limit = max_rounds if max_rounds is not None else cfg.max_rounds
@@ -468,8 +509,8 @@ class Loop:
                            review="PASS" if review_passed else "FAIL", commits=commits, milestone_after=self.milestone)
                 if self._read("stage1.status") == "finished":
                     self.exit_cause = "stage finished"
-                    rc_final = 0
-                    return 0
+                    rc_final = self.run_stage2(None, lease_env)
+                    return rc_final
             self.exit_cause = "round limit reached"
             rc_final = 0
             return 0

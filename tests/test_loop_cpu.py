@@ -300,3 +300,29 @@ def test_builtin_review_applies_the_elastic_mfu_bar_to_the_gated_milestone(tmp_p
     lp3 = loop.Loop(_cfg(tmp_path, ws, reg, {}, review_mfu_target=40.0), loop_id="R3")
     mfu.record(os.path.join(lp3.dir, "mfu_history.jsonl"), "long-train", 55.0, True)
     assert lp3.run(max_rounds=1) == 0 and lp3.milestone == "alignment"
+
+
+def test_stage2_fans_workers_out_per_operator_until_every_op_is_merged(tmp_path, monkeypatch):
+    """After stage 1 the loop re-fans one worker per not-yet-merged operator each round; a worker 'merges' its op here by
+    recording a passing op-long for it, the way the real gate does."""
+    from forge_train_harness_b200.harness import stage2
+    res_dir = tmp_path / "op_long"
+    monkeypatch.setattr(stage2, "_results_dir", lambda: str(res_dir))
+    ws, reg = _workspace(tmp_path)
+    worker = tmp_path / "s2.py"
+    worker.write_text("import json, os, sys\nop, d, rnd = sys.argv[1], sys.argv[2], int(os.environ['FORGE_ROUND'])\nos.makedirs(d, exist_ok=True)\n"
+                      "ok = not (op == os.environ.get('SLOW_OP') and rnd == 1)\n"
+                      "json.dump({'passed': ok, 'mean_rel_diff': 1e-4, 'steps': 200, 'consecutive_failures': 0 if ok else 1}, open(os.path.join(d, op + '.json'), 'w'))\n"
+                      "sys.exit(0 if ok else 1)\n")
+    ops = sorted(stage2.load_registry()["ops"])
+    monkeypatch.setenv("SLOW_OP", ops[3])
+    cfg = _cfg(tmp_path, ws, reg, {}, stage2_worker_cmd=[sys.executable, str(worker), "{op}", str(res_dir)])
+    lp = loop.Loop(cfg, loop_id="S2")
+    lp._write("stage1.status", "finished")
+    assert lp.run() == 0
+    ev = [e for e in _events(lp) if e["subtype"].startswith("stage2") or e["subtype"] == "stage_finished"]
+    assert [e["subtype"] for e in ev] == ["stage2_round_started", "stage2_round_finished", "stage2_round_started", "stage2_round_finished",
+                                          "stage2_round_started", "stage_finished"]
+    assert len(ev[0]["pending"]) == len(ops) and ev[2]["pending"] == [ops[3]] and ev[4]["pending"] == []   # only the failed op is re-run
+    assert ev[1]["ops"][ops[3]] == "failed" and ev[3]["ops"] == {ops[3]: "done"} and ev[1]["peak_running"] <= 6
+    assert lp._read("stage2.status") == "finished" and lp.run() == 0                                        # and it stays finished
