@@ -82,8 +82,19 @@ def main(argv=None):
     ap.add_argument("--recipe", default="")
     ap.add_argument("--set", action="append", default=[])
     ap.add_argument("--loss-tag", default=None)
+    ap.add_argument("--reference-env", action="store_true",
+                    help="apply the reference engine's environment variables (NUM_LAYERS ... LR ... ENABLE_CUDA_GRAPH, "
+                         "ENABLE_TRITON_*) on top of the config file: a launch environment written for the reference drives this engine")
     a = ap.parse_args(argv)
-    cfg = _apply_sets(schema.load(a.config), a.set)
+    cfg = schema.load(a.config)
+    if a.reference_env:
+        from .config.ref_env import apply_reference_env, op_env_from_reference
+        cfg = apply_reference_env(cfg, os.environ)
+        for k, v in op_env_from_reference(os.environ).items():
+            os.environ.setdefault(k, v)          # an explicit OP_<NAME> still wins
+            if v == "baseline":
+                os.environ.setdefault("FORGE_ALLOW_BASELINE", "1")
+    cfg = _apply_sets(cfg, a.set)
     created = init_distributed()
     if a.recipe:
         with open(a.recipe, "rb") as f:

@@ -132,3 +132,31 @@ def test_set_overrides_parse_every_field_kind():
     assert _apply_sets(cfg, ["parallel.pipeline_layer_split=16,16"]).parallel.pipeline_layer_split == (16, 16)
     with pytest.raises(ValueError):
         _apply_sets(cfg, ["parallel.pipeline_layer_split=20,20"])      # must sum to the layer count
+
+
+def test_reference_environment_surface_maps_onto_the_config():
+    from forge_train_harness_b200.config import schema
+    from forge_train_harness_b200.config.ref_env import apply_reference_env, op_env_from_reference
+    cfg = schema.load(os.path.join(ROOT, "configs", "tiny_cpu_dp2.toml"))
+    env = {"NUM_LAYERS": "3", "HIDDEN_SIZE": "128", "NUM_ATTENTION_HEADS": "2", "NUM_QUERY_GROUPS": "1", "HEAD_DIM": "64", "FFN_HIDDEN_SIZE": "256",
+           "PADDED_VOCAB_SIZE": "1024", "MAX_POSITION_EMBEDDINGS": "64", "SEQ_LENGTH": "64", "NORM_EPSILON": "1e-5", "ROTARY_BASE": "10000",
+           "LR": "3e-4", "MIN_LR": "3e-5", "LR_WARMUP_ITERS": "7", "CLIP_GRAD": "0.5", "DETERMINISTIC": "1", "ENABLE_ZERO_OPTIMIZER": "1",
+           "ENABLE_CUDA_GRAPH": "0", "ENABLE_DL_PREFETCH": "0", "DL_PREFETCH_SIZE": "128", "FORGE_INIT_ONES": "0", "MTP_NUM_LAYERS": "0",
+           "NCCL_ALGO": "Tree", "ENABLE_TRITON_ROPE_FWD": "0", "ENABLE_TRITON_RMSNORM_FWD": "1"}
+    c = apply_reference_env(cfg, env)
+    assert (c.model.num_layers, c.model.hidden_size, c.model.head_dim, c.model.padded_vocab_size, c.model.seq_length) == (3, 128, 64, 1024, 64)
+    assert c.optim.lr == 3e-4 and c.optim.min_lr == 3e-5 and c.optim.lr_warmup_iters == 7 and c.optim.clip_grad == 0.5
+    assert c.train.deterministic and not c.train.cuda_graph and not c.train.forge_init_ones and c.parallel.use_distributed_optimizer
+    assert c.data.prefetch_size == 0                         # prefetch switched off beats its size
+    assert c.optim.weight_decay == cfg.optim.weight_decay    # absent variables leave the file's value
+    assert apply_reference_env(cfg, {}) is cfg
+    assert op_env_from_reference(env) == {"OP_ROPE_FWD": "baseline", "OP_RMSNORM_FWD": "sm100", "OP_RESIDUAL_RMSNORM_FWD": "sm100"}
+    with pytest.raises(ValueError, match="HIDDEN_SIZE"):
+        apply_reference_env(cfg, {"HIDDEN_SIZE": "wide"})
+    # and the engine trains from such an environment through its public entry point
+    r = subprocess.run([sys.executable, "-m", "forge_train_harness_b200.train", "--config", os.path.join(ROOT, "configs", "tiny_cpu_dp2.toml"),
+                        "--reference-env", "--set", "train.num_steps=2", "--set", "parallel.use_distributed_optimizer=false"],
+                       cwd=ROOT, capture_output=True, text=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", NUM_LAYERS="1", LR="1e-3", SEQ_LENGTH="32",
+                                                                          MAX_POSITION_EMBEDDINGS="32"))
+    assert r.returncode == 0 and r.stdout.count("[LOSS]") == 2, r.stderr[-1500:]
+    assert "lr=0.001" in r.stdout                            # the [PHASE] banner shows the variable's value
