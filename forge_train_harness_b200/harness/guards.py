@@ -21,7 +21,7 @@ ENGINE_DIRS = ["models", "ops", "optim", "parallel", "data", "ckpt", "engine.py"
 # the corpus FORMAT is called Megatron binary, and the exporter writes checkpoints under Megatron-LM's state-dict names:
 # both name a file format, neither imports the framework
 ALLOW = {"ops/torch_ops.py": {"torch.nn.Module"}, "data/sources.py": {"megatron"}, "data/prepare.py": {"megatron"},
-         "ckpt/export_megatron.py": {"megatron"}}
+         "ckpt/export_megatron.py": {"megatron"}, "ckpt/import_weights.py": {"megatron"}}
 
 
 def _code_only(src: str) -> str:
