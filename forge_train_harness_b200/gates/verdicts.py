@@ -234,3 +234,46 @@ def classify_failure(text: str, timed_out: bool = False) -> str:
     if "command not found" in t or "permission denied" in t:
         return "script_setup"
     return "unknown"
+
+
+def profile(run_dir: str, require_kernels: bool = True, rank: int = 0) -> dict:
+    """Verdict of the ``profile-snapshot`` suite (evals/verdicts/profile.py; tools/profile_render.py:381-404): the one-step
+    profile of ``rank`` exists and parses, names at least one device kernel (unless the run had no GPU), and is compared with
+    the newest earlier snapshot of the same suite: step span, busy share and the kernels that moved most."""
+    import glob
+    import json
+    import os
+    found = sorted(glob.glob(os.path.join(run_dir, "ours", "profile", f"step_*_rank{rank}.json")))
+    if not found:
+        return {"passed": False, "reason": f"no step_*_rank{rank}.json under {os.path.join(run_dir, 'ours', 'profile')}"}
+    try:
+        with open(found[-1]) as f:
+            cur = json.load(f)
+    except (OSError, json.JSONDecodeError) as e:
+        return {"passed": False, "reason": f"unreadable snapshot: {e}"}
+    kernels = cur.get("kernels", {})
+    out = {"passed": bool(kernels) or not require_kernels, "snapshot": found[-1], "n_kernels": len(kernels),
+           "n_launches": cur.get("n_launches", 0), "span_ms": cur.get("span_us", 0.0) / 1e3,
+           "busy_pct": 100.0 * cur.get("busy_us", 0.0) / max(cur.get("span_us", 0.0), 1e-9),
+           "top": [[k, round(v["us"] / 1e3, 3)] for k, v in list(kernels.items())[:5]]}
+    if not out["passed"]:
+        out["reason"] = "the snapshot names no device kernel"
+    # newest earlier snapshot of the same suite (run directories are <suite>-<utc stamp>-<id>, so names sort by time)
+    parent, me = os.path.dirname(os.path.abspath(run_dir)), os.path.basename(os.path.abspath(run_dir))
+    suite = me.rsplit("-", 2)[0] if me.count("-") >= 2 else me
+    older = [d for d in sorted(os.listdir(parent)) if d.startswith(suite + "-") and d < me] if os.path.isdir(parent) else []
+    for d in reversed(older):
+        prev_files = sorted(glob.glob(os.path.join(parent, d, "ours", "profile", f"step_*_rank{rank}.json")))
+        if prev_files:
+            try:
+                with open(prev_files[-1]) as f:
+                    prev = json.load(f)
+            except (OSError, json.JSONDecodeError):
+                continue
+            moved = sorted(((k, (v["us"] - prev["kernels"].get(k, {"us": 0.0})["us"]) / 1e3) for k, v in kernels.items()),
+                           key=lambda kv: -abs(kv[1]))[:5]
+            out["previous"] = prev_files[-1]
+            out["delta_span_ms"] = (cur.get("span_us", 0.0) - prev.get("span_us", 0.0)) / 1e3
+            out["moved_most_ms"] = [[k, round(dv, 3)] for k, dv in moved]
+            break
+    return out

@@ -80,6 +80,8 @@ def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) ->
         r = V.resume_startup(rd(our_log), gate.get("resume_startup_budget_s", 18.0))
     elif kind == "wsd_sft":
         r = V.wsd_sft(rd(ref_log), rd(our_log))
+    elif kind == "profile":
+        r = V.profile(run_dir, bool(gate.get("require_kernels", True)))
     elif kind == "exit_code":
         # the runner judged itself (it exited 0, or run_suite would not have come here); its last JSON line, if any, is kept
         r = {"passed": ours_rc == 0}

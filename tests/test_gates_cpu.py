@@ -292,3 +292,26 @@ def test_prepare_corpus_matches_the_streaming_encode_contract(tmp_path):
     assert int((flat == 256).sum()) >= 10 and flat.max() <= 256          # one EOS per document, byte ids otherwise
     text = bytes(int(x) for x in flat[:9]).decode()
     assert text.startswith("Question")
+
+
+def test_profile_snapshot_verdict_compares_with_the_previous_snapshot(tmp_path):
+    import json
+    from forge_train_harness_b200.gates import verdicts as V
+
+    def snap(run, kernels, span):
+        d = tmp_path / run / "ours" / "profile"
+        d.mkdir(parents=True)
+        (d / "step_5_rank0.json").write_text(json.dumps({"kernels": kernels, "span_us": span, "busy_us": 0.9 * span, "idle_us": 0.1 * span,
+                                                          "n_launches": sum(k["launches"] for k in kernels.values())}))
+        return str(tmp_path / run)
+    old = snap("profile-snapshot-20260101T000000-aaaaaa", {"gemm": {"launches": 10, "us": 5000.0}, "attn": {"launches": 4, "us": 3000.0}}, 10000.0)
+    new = snap("profile-snapshot-20260102T000000-bbbbbb", {"gemm": {"launches": 10, "us": 4000.0}, "attn": {"launches": 4, "us": 3100.0},
+                                                           "norm": {"launches": 8, "us": 200.0}}, 9000.0)
+    first = V.profile(old)
+    assert first["passed"] and first["n_kernels"] == 2 and "previous" not in first and abs(first["busy_pct"] - 90.0) < 1e-6
+    r = V.profile(new)
+    assert r["passed"] and r["previous"].startswith(old) and abs(r["delta_span_ms"] + 1.0) < 1e-9
+    assert r["moved_most_ms"][0] == ["gemm", -1.0] and ["norm", 0.2] in r["moved_most_ms"] and r["top"][0][0] == "gemm"
+    empty = snap("profile-snapshot-20260103T000000-cccccc", {}, 0.0)
+    assert not V.profile(empty)["passed"] and V.profile(empty, require_kernels=False)["passed"]
+    assert not V.profile(str(tmp_path / "nothing"))["passed"]

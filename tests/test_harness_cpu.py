@@ -326,3 +326,23 @@ def test_gate_runs_feed_the_mfu_history_of_their_loop(tmp_path, capsys):
     assert mfu.record_result(RS.make_run_result("resume-gate", True, "ok", {"passed": True}, {}), env={"FORGE_LOOP_DIR": str(tmp_path)}) is None
     hist = mfu.load(str(tmp_path / "mfu_history.jsonl"))
     assert len(hist) == 1 and mfu.evaluate(mfu.qualifying(hist), 40.0)[0]
+
+
+def test_profile_snapshot_suite_runs_end_to_end_on_cpu(tmp_path):
+    """The suite's plumbing (environment prefix, profile directory inside the run directory, verdict) with the tiny CPU model;
+    on CPU the snapshot names no device kernel, which the registry entry has to allow explicitly."""
+    reg = {"evals": {"profile-snapshot": {
+        "needs_ref": False, "gpu_count": 0, "timeout_s": 300, "verdict": "profile", "require_kernels": False,
+        "ours_cmd": ["env", "FORGE_PROFILE_STEP=2", "FORGE_PROFILE_RANK=0", "FORGE_PROFILE_DIR={run_dir}/ours/profile", "CUDA_VISIBLE_DEVICES=",
+                     "{python}", "-m", "forge_train_harness_b200.train", "--config", "{repo}/configs/tiny_cpu_dp2.toml",
+                     "--set", "train.num_steps=3", "--set", "parallel.use_distributed_optimizer=false"]}}}
+    req = RS.make_run_request("profile-snapshot", {}, 0)
+    art = tmp_path / req["run_id"]
+    res = dispatcher.run_suite(req, reg, ROOT, str(art))
+    assert res["status"] == "passed", res
+    assert os.path.isfile(art / "ours" / "profile" / "step_2_rank0.json") and os.path.isfile(art / "ours" / "profile" / "step_2_rank0.md")
+    assert res["metrics"]["n_kernels"] == 0 and res["metrics"]["snapshot"].endswith("step_2_rank0.json")
+    reg["evals"]["profile-snapshot"]["require_kernels"] = True
+    req2 = RS.make_run_request("profile-snapshot", {}, 0)
+    res2 = dispatcher.run_suite(req2, reg, ROOT, str(tmp_path / req2["run_id"]))
+    assert res2["status"] != "passed" and "no device kernel" in json.dumps(res2)

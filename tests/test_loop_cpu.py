@@ -236,9 +236,9 @@ def test_every_eval_family_registry_is_routable():
             assert loop.suites_of_milestone(path, m), (fam, m)
         for name, gate in doc["evals"].items():
             assert gate["verdict"] in kinds, (fam, name, gate["verdict"])
-            assert gate.get("stage") in ("stage1", "stage2"), (fam, name)
+            assert gate.get("stage") in ("stage1", "stage2", "aux"), (fam, name)     # aux: not part of any milestone (profile snapshot)
             ms = gate.get("milestone", "")
-            assert gate["stage"] == "stage2" or ms.split(".")[0] in order, (fam, name, ms)
+            assert gate["stage"] != "stage1" or ms.split(".")[0] in order, (fam, name, ms)
     d8 = tomllib.load(open(os.path.join(loop.ROOT, "configs", "eval", "dense_training_8b.toml"), "rb"))
     assert "hf-oracle" in d8["evals"] and "dptp" in d8["evals"] and "--model" in d8["evals"]["long-train"]["ours_cmd"]
     dq = tomllib.load(open(os.path.join(loop.ROOT, "configs", "eval", "dense_training_qwen3.toml"), "rb"))
