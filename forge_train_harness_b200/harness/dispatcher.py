@@ -57,6 +57,11 @@ def _verdict(kind: str, gate: dict, run_dir: str, ours_rc: int | None = None) ->
     if kind == "long_train":
         r = V.long_train(wire.parse_loss_lines(rd(ref_log), strict=False), wire.parse_loss_lines(rd(our_log), strict=False),
                          tuple(gate["gate_window"]), gate.get("loss_rel_threshold", 0.01), gate.get("mfu_e2e_target"))
+    elif kind == "loss_gate":
+        # the loss-gate-200 rule (evals/verdicts/loss_gate.py): window-average relative loss difference below a threshold that
+        # MUST be given (a missing key raises instead of silently passing); the window's mean MFU is reported, never gated
+        r = V.long_train(wire.parse_loss_lines(rd(ref_log), strict=False), wire.parse_loss_lines(rd(our_log), strict=False),
+                         tuple(gate["gate_window"]), float(gate["max_avg_relative_loss_diff"]))
     elif kind == "trajectory":
         r = V.trajectory(wire.parse_loss_lines(rd(ref_log), strict=False), wire.parse_loss_lines(rd(our_log), strict=False),
                          tuple(gate["gate_window"]) if "gate_window" in gate else None, gate.get("atol", 0.0), gate.get("rtol", 0.0))

@@ -346,3 +346,17 @@ def test_profile_snapshot_suite_runs_end_to_end_on_cpu(tmp_path):
     req2 = RS.make_run_request("profile-snapshot", {}, 0)
     res2 = dispatcher.run_suite(req2, reg, ROOT, str(tmp_path / req2["run_id"]))
     assert res2["status"] != "passed" and "no device kernel" in json.dumps(res2)
+
+
+def test_loss_gate_verdict_needs_its_threshold(tmp_path):
+    from forge_train_harness_b200.utils import wire
+    run = tmp_path / "run"
+    for side, bias in (("ref", 0.0), ("ours", 0.002)):
+        (run / side).mkdir(parents=True)
+        (run / side / f"{side}.log").write_text("\n".join(wire.format_loss_line(s, 5.0 - 0.01 * s + bias, 1.0, 0.5, 41.0) for s in range(1, 21)))
+    gate = {"gate_window": [11, 21], "max_avg_relative_loss_diff": 0.01}
+    ok, m = dispatcher._verdict("loss_gate", gate, str(run))
+    assert ok and m["mean_rel_diff"] < 1e-3 and abs(m["avg_mfu_e2e_standard"] - 41.0) < 1e-9 and m["threshold"] == 0.01
+    assert not dispatcher._verdict("loss_gate", dict(gate, max_avg_relative_loss_diff=1e-5), str(run))[0]
+    with pytest.raises(KeyError, match="max_avg_relative_loss_diff"):
+        dispatcher._verdict("loss_gate", {"gate_window": [11, 21]}, str(run))
