@@ -477,7 +477,13 @@ def run_training_loop(cfg: RunConfig, *, trainer: Trainer | None = None, loss_ta
     out = out or sys.stdout
     t0_wall = time.time()
     created = init_distributed()
-    tr = trainer or Trainer(cfg, init_mode=cfg.train.init_mode)
+    sess = None
+    if trainer is None and cfg.train.hash_capture_level > 0 and cfg.train.hash_output:
+        # hash capture asked for by the configuration (a gate product's hash_capture_level / hash_output): per-rank dumps
+        # ``<hash_output>.rank<r>`` of the loss / gradient families (level 1) and of every module's output (level 2)
+        from .gates.capture import CaptureSession
+        sess = CaptureSession(cfg.train.hash_output, level=cfg.train.hash_capture_level, rank=dist.get_rank() if dist.is_initialized() else 0)
+    tr = trainer or Trainer(cfg, init_mode=cfg.train.init_mode, capture=sess)
     t, oc, m = cfg.train, cfg.optim, cfg.model
     tag = loss_tag or t.loss_tag
     rank0 = tr.rank == 0

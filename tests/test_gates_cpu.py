@@ -315,3 +315,19 @@ def test_profile_snapshot_verdict_compares_with_the_previous_snapshot(tmp_path):
     empty = snap("profile-snapshot-20260103T000000-cccccc", {}, 0.0)
     assert not V.profile(empty)["passed"] and V.profile(empty, require_kernels=False)["passed"]
     assert not V.profile(str(tmp_path / "nothing"))["passed"]
+
+
+def test_hash_capture_is_switched_on_by_the_configuration(tmp_path):
+    """train.hash_capture_level / train.hash_output (a gate product's keys) make the public entry point write per-rank hash dumps."""
+    import subprocess
+    import sys
+    ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "ours_hash_dump.json"
+    r = subprocess.run([sys.executable, "-m", "forge_train_harness_b200.train", "--config", os.path.join(ROOT, "configs", "tiny_cpu_dp2.toml"),
+                        "--set", "train.num_steps=2", "--set", "parallel.use_distributed_optimizer=false", "--set", "train.hash_capture_level=1",
+                        "--set", f"train.hash_output={out}"], cwd=ROOT, capture_output=True, text=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stderr[-1500:]
+    keys = cap.load_merged(str(out))
+    assert any(".grad." in k and k.endswith("preallreduce") for k in keys) and any("loss.scalar.postallreduce" in k for k in keys)
+    assert not any(".fwd." in k for k in keys)          # level 1: no per-module activations
+    assert {k.split(".")[0] for k in keys} == {"step_0", "step_1"}   # keyed by the number of completed steps
