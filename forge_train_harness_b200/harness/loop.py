@@ -538,6 +538,8 @@ def fork(cfg: LoopConfig, src_loop_id: str, at_milestone: str, new_loop_id: str 
     ``milestone_advanced`` event, else from the one commit that declares the milestone; several declarations without an event
     are ambiguous and need ``at_sha``.  The source loop is not touched; with ``workspace_dst`` the workspace history up to
     the anchor is cloned there (``git clone`` + ``reset --hard``) for the new loop to work in."""
+    if not os.path.isdir(os.path.join(cfg.loops_dir, src_loop_id)):
+        raise ValueError(f"no loop {src_loop_id!r} under {cfg.loops_dir}")
     src = Loop(cfg, loop_id=src_loop_id)
     order = src.order
     if at_milestone not in order:
