@@ -154,6 +154,17 @@ def _pid_alive(pid: int) -> bool:
     return True
 
 
+def _pid_start(pid: int) -> str:
+    """Start time of a process in clock ticks since boot (field 22 of /proc/<pid>/stat); "" where /proc is not available.
+    Recorded with a lease so that a recycled process id is not mistaken for the holder."""
+    try:
+        with open(f"/proc/{int(pid)}/stat", "rb") as f:
+            data = f.read().decode("ascii", "replace")
+        return data[data.rindex(")") + 2:].split()[19]
+    except (OSError, ValueError, IndexError):
+        return ""
+
+
 # ---- providers -------------------------------------------------------------------------------------------------------------
 class LocalGpuProvider:
     """GPU ordinals of this node.  The handle is ``gpu-<i>[-<j>...]``; the task id is the holder's pid.
@@ -190,7 +201,11 @@ class LocalGpuProvider:
         return [int(x) for x in handle[4:].split("-")]
 
     def live(self, row: dict) -> bool:
-        return _pid_alive(int(row.get("task_id", 0) or 0))
+        pid = int(row.get("task_id", 0) or 0)
+        if not _pid_alive(pid):
+            return False
+        born = row.get("task_start", "")
+        return not born or _pid_start(pid) in ("", born)     # same pid, other start time: the holder is gone, the pid was reused
 
     def allocate(self, spec: LeaseSpec, registry: dict) -> tuple[str, str, list[str]]:
         """Returns (handle, task_id, reclaimed handles).  Raises ``LeaseBusyError`` when too few ordinals are free."""
@@ -345,7 +360,8 @@ def claim(resource: str, *, spec: LeaseSpec, loop_id: str, provider=None, timeou
                             with contextlib.suppress(FileNotFoundError, LeaseError):
                                 os.unlink(_reverse_path(resource, dead.get("loop_id", "")))
                     key = handle if handle != "gpu-none" else f"gpu-none@{loop_id}"
-                    reg[key] = {"loop_id": loop_id, "task_id": task_id, "claimed_at": _now(), "gpu_count": spec.gpu_count}
+                    reg[key] = {"loop_id": loop_id, "task_id": task_id, "task_start": _pid_start(int(task_id)), "claimed_at": _now(),
+                                "gpu_count": spec.gpu_count}
                     _write_registry(resource, reg)
                     with open(rev, "w", encoding="utf-8") as f:
                         f.write(key + "\n")

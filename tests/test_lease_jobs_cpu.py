@@ -76,6 +76,10 @@ def test_dead_holder_is_reclaimed(lease_root):
     # the crashed loop's late release must not drop the new holder's row
     lease.release("gpu", loop_id="crashed", provider=pa)
     assert lease.holders("gpu")[h]["loop_id"] == "next"
+    # a recycled process id is not the holder: same pid, another start time -> reclaimable
+    row = dict(lease.holders("gpu")[h])
+    assert row["task_start"] and lease.LocalGpuProvider(2).live(row)
+    assert not lease.LocalGpuProvider(2).live(dict(row, task_start="1"))
 
 
 def _fake_scheduler(tmp_path, flake_first_create=False):
