@@ -168,6 +168,24 @@ def main(argv=None):
         if hasattr(ops, "attention_bwd"):
             do = r(M, cfg.q_dim)
             rec("attention_bwd", timeit(lambda: ops.attention_bwd(do, qkv, out, lse, S, nkv, g, d), flush=flush), 2.5 * fl)
+        # the library the reference calls (flash-attn 2: forward.py:233, backward.py:510), same shapes, where it is installed:
+        # comparison rows only; it needs q / k / v as separate [B, S, heads, d] tensors, so it is given contiguous copies
+        try:
+            from flash_attn import flash_attn_func
+        except Exception:  # noqa: BLE001  (not installed, or built for another architecture)
+            flash_attn_func = None
+        if flash_attn_func is not None:
+            v4 = qkv.view(a.mbs, S, nkv, g + 2, d)
+            q = v4[:, :, :, :g].reshape(a.mbs, S, nkv * g, d).contiguous().requires_grad_(True)
+            k = v4[:, :, :, g].contiguous().requires_grad_(True)
+            vv = v4[:, :, :, g + 1].contiguous().requires_grad_(True)
+            try:
+                o = flash_attn_func(q, k, vv, causal=True)
+                rec("flash_attn2_library_fwd", timeit(lambda: flash_attn_func(q, k, vv, causal=True), flush=flush), fl)
+                go = torch.randn_like(o)
+                rec("flash_attn2_library_bwd", timeit(lambda: torch.autograd.grad(o, (q, k, vv), go, retain_graph=True), flush=flush), 2.5 * fl)
+            except Exception as e:  # noqa: BLE001
+                print(json.dumps({"op": "flash_attn2_library", "skipped": f"{type(e).__name__}: {str(e)[:120]}"}), flush=True)
     torch.cuda.synchronize()
     check_status()
     if a.json:
