@@ -242,3 +242,42 @@ def test_local_scheduler_runs_queues_and_stops(lease_root):
     pg = int(jobs.LocalScheduler._get(sched._job(rec["job_id"]), "pgid"))
     time.sleep(0.2)
     assert not lease._pid_alive(pg)
+
+
+_CLAIMER = r'''
+import os, sys, time, random
+sys.path.insert(0, sys.argv[1])
+from forge_train_harness_b200.harness import lease
+me, marks, rounds = sys.argv[2], sys.argv[3], int(sys.argv[4])
+random.seed(int(me[1:]))
+prov = lease.LocalGpuProvider(total_gpus=8)
+for i in range(rounds):
+    n = random.choice([1, 2, 4])
+    h = lease.claim("gpu", spec=lease.LeaseSpec(n), loop_id=me, provider=prov, timeout=60, poll_s=0.01)
+    ords = prov.ordinals(h)
+    assert len(ords) == n
+    for o in ords:                      # exclusive create: a second holder of the same ordinal fails here
+        fd = os.open(os.path.join(marks, "gpu%d" % o), os.O_CREAT | os.O_EXCL | os.O_WRONLY)
+        os.write(fd, me.encode()); os.close(fd)
+    time.sleep(random.random() * 0.02)
+    for o in ords:
+        os.unlink(os.path.join(marks, "gpu%d" % o))
+    lease.release("gpu", loop_id=me, provider=prov)
+print("ok")
+'''
+
+
+def test_concurrent_claimers_never_share_a_gpu(lease_root):
+    """Six processes claim and release 1 / 2 / 4 of 8 ordinals in a tight loop; while a lease is held its holder owns an
+    exclusively-created marker per ordinal, so any double booking makes a claimer crash."""
+    marks = lease_root / "marks"
+    marks.mkdir()
+    script = lease_root / "claimer.py"
+    script.write_text(_CLAIMER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, FORGE_LEASE_DIR=str(lease_root / "lease"))
+    procs = [subprocess.Popen([sys.executable, str(script), root, f"c{i}", str(marks), "15"], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for i in range(6)]
+    outs = [p.communicate(timeout=240) for p in procs]
+    assert all(p.returncode == 0 and o[0].strip() == "ok" for p, o in zip(procs, outs)), [o[1][-400:] for o in outs]
+    assert lease.holders("gpu") == {} and os.listdir(marks) == []
