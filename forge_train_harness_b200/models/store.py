@@ -147,9 +147,14 @@ class ParamStore:
             self.load_full(spec.name, full)
 
     def init_device(self, seed: int, init_ones: bool = True) -> None:
-        for i, s in enumerate(self.specs):
+        """Every shard drawn on its own device.  The stream of a parameter is keyed by its NAME (not by its position in this
+        rank's list): two pipeline stages then never draw the same numbers for different layers, while the two copies of a
+        tied embedding (first and last stage), DP replicas and TP-replicated tensors still come out identical."""
+        import zlib
+        for s in self.specs:
             tmp = torch.empty(self.shapes[s.name], dtype=torch.float32, device=self.device)
-            P.device_init_(tmp, s, self.cfg, seed + 7919 * self.tp_rank * (s.kind != "replicated"), i, init_ones)
+            P.device_init_(tmp, s, self.cfg, seed + 7919 * self.tp_rank * (s.kind != "replicated"),
+                           zlib.crc32(s.name.encode()) & 0x7FFFFFFF, init_ones)
             self.params[s.name].copy_(tmp)
 
     def load_full(self, name: str, full: torch.Tensor) -> None:

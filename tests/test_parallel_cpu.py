@@ -185,3 +185,35 @@ def test_peer_memory_paths_are_for_groups_inside_one_node(monkeypatch):
     assert not T.spans_nodes([0, 1, 2, 3])
     monkeypatch.delenv("WORLD_SIZE")
     assert not T.spans_nodes([0])
+
+
+def _device_init_sums(rank, world, cfg):
+    tr = fth.Trainer(cfg, device="cpu", quiet=True, init_mode="device")
+    out = (tr.topo.pp_rank, tr.topo.dp_rank, tr.topo.tp_rank,
+           {k: (float(v.double().sum()), float(v.double().abs().sum())) for k, v in tr.store.params.items()})
+    tr.close()
+    return out
+
+
+def test_device_init_is_keyed_by_parameter_name():
+    """Per-shard initialisation: layers on different pipeline stages must not draw the same numbers (a position-keyed stream
+    made layer k of stage 1 a copy of layer k of stage 0), while the tied embedding's two copies, DP replicas and
+    TP-replicated tensors stay identical and TP shards differ."""
+    cfg = base_cfg(tensor_parallel_size=2, pipeline_parallel_size=2, sequence_parallel=True, use_distributed_optimizer=True, gbs=16)
+    res = run_ranks(8, _device_init_sums, cfg)
+    by = {(pp, dp, tp): st for pp, dp, tp, st in res}
+    s0, s1 = by[(0, 0, 0)], by[(1, 0, 0)]
+    assert s0["tok_embeddings.weight"] == s1["tok_embeddings.weight"]                       # tied copies
+    mats0 = sorted(v for k, v in s0.items() if k.endswith("wqkv.weight"))
+    mats1 = sorted(v for k, v in s1.items() if k.endswith("wqkv.weight"))
+    assert len(mats0) == 2 and len(mats1) == 2 and not set(mats0) & set(mats1)               # no layer duplicated across stages
+    assert len({v for st in (s0, s1) for k, v in st.items() if k.endswith("w2.weight")}) == 4
+    for pp in (0, 1):
+        for tp in (0, 1):
+            assert by[(pp, 0, tp)] == by[(pp, 1, tp)]                                        # DP replicas
+        a, b = by[(pp, 0, 0)], by[(pp, 0, 1)]
+        for k in a:
+            if k.endswith("norm.weight"):
+                assert a[k] == b[k]                                                          # TP-replicated
+            else:
+                assert a[k] != b[k], k                                                       # TP shards
