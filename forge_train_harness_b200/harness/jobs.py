@@ -28,7 +28,7 @@ import uuid
 
 from . import lease
 
-__all__ = ["LocalScheduler", "run_suite", "poll_suite", "build_entry", "main", "TIMEOUT_RC", "INFLIGHT_RC", "NO_JOB_RC"]
+__all__ = ["LocalScheduler", "CommandScheduler", "scheduler_from_config", "run_suite", "poll_suite", "build_entry", "main", "TIMEOUT_RC", "INFLIGHT_RC", "NO_JOB_RC"]
 
 TIMEOUT_RC, INFLIGHT_RC, NO_JOB_RC = 124, 75, 76
 SUCCESS_PHASES = frozenset({"succeeded"})
@@ -167,6 +167,69 @@ class LocalScheduler:
                 return f.read().decode("utf-8", "replace")
         except FileNotFoundError:
             return ""
+
+
+class CommandScheduler:
+    """An external job scheduler behind argv templates (the form the reference hard-codes for its cluster CLI,
+    tools/gpu_job.py:273-360)::
+
+        [remote.jobs]
+        submit = ["sched", "job", "create", "--gpus", "{gpus}", "--nodes", "{nodes}", "--entry", "{entry}"]
+        id_regex = "tasks/([0-9a-f]+)"
+        phase  = ["sched", "job", "get", "tasks/{job_id}", "--field", "phase"]
+        stop   = ["sched", "job", "stop", "--yes", "tasks/{job_id}"]
+        logs   = ["sched", "job", "logs", "tasks/{job_id}", "--tail", "200"]
+        phase_map = {Queued = "queued", Running = "running", Succeeded = "succeeded", Failed = "failed", Stopped = "stopped"}
+
+    Multi-node jobs are the scheduler's business: ``nodes`` pods of ``gpus`` GPUs each, rendezvous variables injected by it."""
+
+    def __init__(self, table: dict):
+        import re
+        for k in ("submit", "phase", "stop"):
+            if not isinstance(table.get(k), list) or not table[k]:
+                raise ValueError(f"[remote.jobs].{k} must be a non-empty argv list")
+        self.t = table
+        self.id_re = re.compile(table.get("id_regex", r"([A-Za-z0-9_.-]+)\s*$"))
+        self.phase_map = {str(k).lower(): str(v) for k, v in (table.get("phase_map") or {}).items()}
+
+    def _run(self, argv, **kw):
+        cmd = [a.format(**kw) for a in argv]
+        return subprocess.run(cmd, capture_output=True, text=True, timeout=float(self.t.get("call_timeout_s", 120)))
+
+    def submit(self, entry: str, *, gpus: int, nodes: int = 1, env: dict | None = None) -> str:
+        import shlex
+        if env:
+            entry = " ".join(f"{k}={shlex.quote(str(v))}" for k, v in env.items()) + " " + entry
+        r = self._run(self.t["submit"], entry=entry, gpus=gpus, nodes=nodes)
+        m = self.id_re.search(r.stdout) if r.returncode == 0 else None
+        if not m:
+            raise RuntimeError(f"job submission failed (rc {r.returncode}): {(r.stderr or r.stdout)[-400:]}")
+        return m.group(1)
+
+    def phase(self, job_id: str) -> str:
+        r = self._run(self.t["phase"], job_id=job_id)
+        if r.returncode != 0 or not r.stdout.strip():
+            return "unknown"
+        raw = r.stdout.strip().splitlines()[-1].strip().lower()
+        return self.phase_map.get(raw, raw)
+
+    def stop(self, job_id: str, reason: str = "") -> None:
+        self._run(self.t["stop"], job_id=job_id, reason=reason)
+
+    def logs(self, job_id: str) -> str:
+        if not self.t.get("logs"):
+            return ""
+        r = self._run(self.t["logs"], job_id=job_id)
+        return r.stdout[-65536:]
+
+
+def scheduler_from_config(remote: dict | None):
+    """``[remote]`` -> scheduler: ``kind = "local"`` (or no table) runs jobs on this node's GPUs, ``"job"`` / ``"scheduler"`` with a
+    ``[remote.jobs]`` table drives an external scheduler."""
+    remote = remote or {}
+    if remote.get("kind", "local") == "local" or not remote.get("jobs"):
+        return LocalScheduler(total_gpus=remote.get("total_gpus"))
+    return CommandScheduler(remote["jobs"])
 
 
 def _supervise(jd: str) -> int:
@@ -314,6 +377,8 @@ def main(argv=None) -> int:
     ap.add_argument("--poll-interval", type=float, default=30.0)
     ap.add_argument("--loop-id", default=os.environ.get("FORGE_LOOP_ID", ""))
     ap.add_argument("--entry", default="", help="shell line to run instead of `harness run <suite>`")
+    ap.add_argument("--remote-toml", default="", help="file with a [remote] table ([remote.jobs] = an external scheduler)")
+    ap.add_argument("--nodes", type=int, default=1)
     ap.add_argument("extra", nargs="*")
     a = ap.parse_args(argv)
     if a.outer <= 0:
@@ -322,11 +387,16 @@ def main(argv=None) -> int:
             print(f"gpu_job: no budget for suite {a.suite!r}: {r.stderr.strip()}", file=sys.stderr)
             return 64
         a.outer = float(r.stdout.strip()) + 120.0
-    sched = LocalScheduler()
+    remote = {}
+    if a.remote_toml:
+        import tomllib
+        with open(a.remote_toml, "rb") as f:
+            remote = tomllib.load(f).get("remote", {})
+    sched = scheduler_from_config(remote)
     if a.poll:
         return poll_suite(sched, suite=a.suite, outer=a.outer, poll_interval_s=a.poll_interval)
     entry = a.entry or build_entry(suite=a.suite, extra=a.extra, loop_id=a.loop_id)
-    return run_suite(sched, suite=a.suite, entry=entry, gpus=a.gpus, outer=a.outer, poll_interval_s=a.poll_interval)
+    return run_suite(sched, suite=a.suite, entry=entry, gpus=a.gpus, nodes=a.nodes, outer=a.outer, poll_interval_s=a.poll_interval)
 
 
 if __name__ == "__main__":

@@ -281,3 +281,47 @@ def test_concurrent_claimers_never_share_a_gpu(lease_root):
     outs = [p.communicate(timeout=240) for p in procs]
     assert all(p.returncode == 0 and o[0].strip() == "ok" for p, o in zip(procs, outs)), [o[1][-400:] for o in outs]
     assert lease.holders("gpu") == {} and os.listdir(marks) == []
+
+
+def test_external_job_scheduler_behind_argv_templates(lease_root):
+    """Submit / poll / logs / stop against a scripted scheduler executable, through the same lifecycle as local jobs."""
+    state = lease_root / "jobs_state.json"
+    state.write_text(json.dumps({"n": 0, "polls": {}, "stopped": [], "entries": []}))
+    exe = lease_root / "jsched"
+    exe.write_text(f"""#!{sys.executable}
+import json, sys
+p = {str(state)!r}
+s = json.load(open(p)); cmd = sys.argv[1]
+if cmd == "create":
+    s["n"] += 1; s["entries"].append(sys.argv[2:]); print("submitted tasks/%d" % s["n"])
+elif cmd == "get":
+    t = sys.argv[2].split("/")[1]; s["polls"][t] = s["polls"].get(t, 0) + 1
+    print("Stopped" if sys.argv[2] in s["stopped"] else ["Queued", "Queued", "Running", "Succeeded"][min(s["polls"][t] - 1, 3)])
+elif cmd == "logs":
+    print("remote log line")
+elif cmd == "stop":
+    s["stopped"].append(sys.argv[-1])
+json.dump(s, open(p, "w"))
+""")
+    exe.chmod(exe.stat().st_mode | stat.S_IEXEC)
+    table = {"submit": [str(exe), "create", "--gpus", "{gpus}", "--nodes", "{nodes}", "--entry", "{entry}"], "id_regex": r"tasks/(\d+)",
+             "phase": [str(exe), "get", "tasks/{job_id}"], "stop": [str(exe), "stop", "--yes", "tasks/{job_id}"],
+             "logs": [str(exe), "logs", "tasks/{job_id}"],
+             "phase_map": {"Queued": "queued", "Running": "running", "Succeeded": "succeeded", "Stopped": "stopped"}}
+    sched = jobs.scheduler_from_config({"kind": "job", "jobs": table})
+    assert isinstance(sched, jobs.CommandScheduler) and isinstance(jobs.scheduler_from_config({}), jobs.LocalScheduler)
+    out = io.StringIO()
+    rc = jobs.run_suite(sched, suite="long-train", entry="harness run long-train", gpus=8, nodes=2, outer=30, commit="c", poll_interval_s=0.01, out=out)
+    s = json.loads(state.read_text())
+    assert rc == 0 and s["entries"] == [["--gpus", "8", "--nodes", "2", "--entry", "harness run long-train"]] and "remote log line" in out.getvalue()
+    # an overrunning remote job is stopped through the scheduler
+    s["polls"] = {}
+    state.write_text(json.dumps(s))
+    table2 = dict(table, phase=[str(exe), "get", "tasks/{job_id}", "x"])
+    class Slow(jobs.CommandScheduler):
+        def phase(self, job_id):
+            return "running"
+    rc = jobs.run_suite(Slow(table2), suite="slow-remote", entry="e", gpus=1, outer=0.1, commit="c", poll_interval_s=0.02, out=out)
+    assert rc == jobs.TIMEOUT_RC and json.loads(state.read_text())["stopped"] == ["tasks/2"]
+    with pytest.raises(ValueError, match="submit"):
+        jobs.CommandScheduler({"phase": ["x"], "stop": ["x"]})
