@@ -399,7 +399,7 @@ class Loop:
         if not suites:
             self.event("milestone_has_no_suites", round=rnd, milestone=cur)
             return
-        sched = self.scheduler or jobs.LocalScheduler()
+        sched = self.scheduler or jobs.scheduler_from_config(self.cfg.remote)
         results = {}
         for name, gate in suites:
             outer = float(gate.get("timeout_s", 1800))
